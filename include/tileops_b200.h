@@ -1,0 +1,132 @@
+/*
+ * tileops_b200 — C ABI of the sm_100a GQA attention-forward kernels.
+ *
+ * Every entry point takes raw device pointers, plain integers and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t), launches asynchronously on that stream
+ * and returns a tb200_status.  Nothing here allocates device memory: callers
+ * pass a workspace obtained from the matching *_workspace_bytes() query, zeroed
+ * ONCE after allocation (the kernels leave it zeroed again when they finish).
+ * No entry point synchronises the host with the device.
+ *
+ * The functions replace, one for one, the TileLang kernels behind these
+ * reference operators (paths relative to the tile-ai/TileOPs tree):
+ *   tb200_gqa_decode        GQADecodeKernel.forward        src/tileops/kernels/attention/gqa_decode.py:555-615
+ *                           GQADecodePagedKernel.forward   src/tileops/kernels/attention/gqa_decode_paged.py:669-746
+ *   tb200_gqa_prefill       GQAPrefillFwdKernel / GQAPrefillFwdWsPersistentCausalKernel
+ *                                                          src/tileops/kernels/attention/gqa_fwd.py:519-597,
+ *                                                          src/tileops/kernels/attention/gqa_prefill_fwd_ws.py:436-520
+ *   tb200_gqa_lse_merge     the "combine" grid             src/tileops/kernels/attention/gqa_decode_paged.py:344-374
+ *                           (lifted across GPUs; the reference has no multi-GPU form)
+ */
+#ifndef TILEOPS_B200_H_
+#define TILEOPS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  TB200_OK = 0,
+  TB200_ERR_BAD_ARGUMENT = 1, /* null pointer, non-positive size, heads % heads_kv != 0 ... */
+  TB200_ERR_UNSUPPORTED = 2,  /* head dim / dtype combination with no kernel */
+  TB200_ERR_WORKSPACE = 3,    /* workspace too small or misaligned */
+  TB200_ERR_CUDA = 4,         /* a CUDA runtime call failed; see tb200_last_error() */
+  TB200_ERR_TIMEOUT = 5       /* a bounded device-side wait ran out */
+} tb200_status;
+
+typedef enum {
+  TB200_F16 = 0,
+  TB200_BF16 = 1,
+  TB200_E4M3 = 2, /* KV cache only */
+  TB200_F32 = 3   /* output only */
+} tb200_dtype;
+
+/* Human-readable text of the last error raised on the calling thread. */
+const char* tb200_last_error(void);
+
+/* Library version, major*100+minor. */
+int tb200_version(void);
+
+/* ---------------------------------------------------------------------------
+ * Single-token GQA decode over a contiguous or a paged KV cache.
+ *
+ * Replaces GQADecodeKernel.forward(Q, K, V, real_seqlen_kv:int)
+ *   (src/tileops/kernels/attention/gqa_decode.py:555-615) when block_table == NULL, and
+ * GQADecodePagedKernel.forward(Q, K, V, real_seqlen_kv, block_table)
+ *   (src/tileops/kernels/attention/gqa_decode_paged.py:669-746) otherwise.
+ *
+ *   q              [batch, heads, dim]            q_dtype (F16 | BF16), contiguous
+ *   k, v           paged:      [pool_tokens, heads_kv, dim]
+ *                  contiguous: [batch, kv_batch_stride / kv_token_stride tokens, heads_kv, dim]
+ *                  kv_dtype == q_dtype, or E4M3 with k_scale / v_scale
+ *   o              [batch, heads, dim]            o_dtype (q_dtype | F32), contiguous
+ *   lse            [batch, heads] fp32 or NULL    log2-domain: log2(sum_j exp(score_j)); -inf if empty
+ *   real_seqlen_kv [batch] int32 device, or NULL -> every sequence has uniform_seqlen tokens
+ *   block_table    [batch, block_table_stride] int32 device; logical page i of sequence b is
+ *                  physical page block_table[b*stride + i]; only ceil(len_b/page) entries are read
+ *   k_scale,v_scale [pool_tokens/page_size, heads_kv] fp32 (E4M3 only): x = float(x_fp8) * scale
+ *   kv_token_stride / kv_head_stride / kv_batch_stride: in ELEMENTS of the KV dtype; the last
+ *                  dim is contiguous.  kv_batch_stride is used only when block_table == NULL.
+ *   sm_scale       multiplies q.k ; softcap > 0 applies cap*tanh(score/cap) before the softmax
+ *   workspace      tb200_gqa_decode_workspace_bytes(...) bytes, 256-byte aligned, zeroed once.
+ *                  The kernel leaves its counters zeroed, so the same buffer serves every later
+ *                  call with the SAME (batch, heads, heads_kv, dim); zero it again before using
+ *                  it for another shape (the counters then sit elsewhere in the buffer), and
+ *                  never share it between launches that may overlap on the GPU.
+ *
+ * A sequence of length 0 produces a zero output row.  Page ids are not range checked.
+ * The kernel never blocks on another CTA: split-KV partials are merged by whichever CTA
+ * finishes a (sequence, KV head) last.
+ * ------------------------------------------------------------------------- */
+size_t tb200_gqa_decode_workspace_bytes(int batch, int heads, int heads_kv, int dim);
+
+int tb200_gqa_decode(const void* q, const void* k, const void* v, void* o, float* lse,
+                     const int32_t* real_seqlen_kv, int32_t uniform_seqlen,
+                     const int32_t* block_table, int32_t block_table_stride,
+                     const float* k_scale, const float* v_scale,
+                     int q_dtype, int kv_dtype, int o_dtype,
+                     int batch, int heads, int heads_kv, int dim, int page_size,
+                     int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
+                     float sm_scale, float softcap,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Merge R partial attention results over disjoint KV ranges (split-KV across GPUs).
+ *   o_parts   [R, rows, dim] fp32, each normalised by its own softmax sum; part r starts at
+ *             o_parts + r * o_part_stride floats (0 means packed: rows * dim)
+ *   lse_parts [R, rows] fp32 log2-domain (-inf or <= -1e29 marks an empty part); part r starts
+ *             at lse_parts + r * lse_part_stride floats (0 means packed: rows)
+ *   o         [rows, dim] o_dtype ; lse [rows] fp32 or NULL
+ * Same algebra as the reference's combine grid
+ * (src/tileops/kernels/attention/gqa_decode_paged.py:344-374), taken across ranks.
+ * ------------------------------------------------------------------------- */
+int tb200_gqa_lse_merge(const float* o_parts, const float* lse_parts, void* o, float* lse,
+                        int parts, int64_t rows, int dim, int64_t o_part_stride,
+                        int64_t lse_part_stride, int o_dtype, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Dense GQA prefill (flash attention forward), BSHD, bottom-right aligned causal mask.
+ *
+ * Replaces the forward of GQAPrefillFwdKernel (src/tileops/kernels/attention/gqa_fwd.py:519-597)
+ * and its Hopper-only specialisations (gqa_prefill_fwd_ws.py:436-520, gqa_fwd_ws.py:1075-1150)
+ * for a uniform batch:
+ *   q [batch, seqlen_q, heads, dim], k/v [batch, seqlen_kv, heads_kv, dim]  dtype (F16 | BF16)
+ *   o [batch, seqlen_q, heads, dim] dtype ; lse [batch, heads, seqlen_q] fp32 log2-domain or NULL
+ * dim must be 128 (tcgen05 path).  Rows with no visible key give o = 0, lse = -inf.
+ * workspace: tb200_gqa_prefill_workspace_bytes() bytes (may be 0 -> NULL allowed).
+ * ------------------------------------------------------------------------- */
+size_t tb200_gqa_prefill_workspace_bytes(int batch, int heads, int heads_kv, int seqlen_q,
+                                         int seqlen_kv, int dim);
+
+int tb200_gqa_prefill(const void* q, const void* k, const void* v, void* o, float* lse,
+                      int dtype, int batch, int seqlen_q, int seqlen_kv, int heads, int heads_kv,
+                      int dim, int is_causal, float sm_scale, float softcap,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TILEOPS_B200_H_ */

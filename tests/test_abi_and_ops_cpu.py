@@ -1,0 +1,306 @@
+"""CPU-only tests: the C-ABI library loads and exports every declared symbol; the op layer
+(validation, kernel selection, kernel_map overrides, plugin targets, roofline) behaves like the
+reference's, exercised with stand-in kernels that launch nothing."""
+
+import ctypes
+import json
+import os
+import re
+
+import pytest
+import torch
+
+import tileops_b200
+from tileops_b200 import _native, backend
+from tileops_b200.backend import registry
+from tileops_b200.kernels import Kernel, gqa_decode_paged_block_ns
+from tileops_b200.kernels.call_spec import AttentionCall
+from tileops_b200.ops import (
+    GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp,
+    GroupedQueryAttentionDecodePagedWithKVCacheFwdOp,
+    GroupedQueryAttentionDecodeWithKVCacheFwdOp,
+    GroupedQueryAttentionFwdOp,
+    GroupedQueryAttentionPrefillFwdOp,
+)
+from tileops_b200.ops.selection import PAGED_DECODE_KEYS
+from tileops_b200.perf import formulas, load_profile
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+# ---------------------------------------------------------------------------- C ABI
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "tileops_b200.h")).read()
+    declared = set(re.findall(r"\b(tb200_[a-z0-9_]+)\s*\(", header))
+    declared -= {"tb200_status", "tb200_dtype"}
+    assert declared == set(_native.SIGNATURES), (declared, set(_native.SIGNATURES))
+    lib = _native.lib()
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert lib.tb200_version() >= 1
+
+
+def test_abi_rejects_bad_arguments_without_touching_a_gpu():
+    lib = _native.lib()
+    assert lib.tb200_gqa_decode_workspace_bytes(0, 32, 8, 128) == 0
+    assert lib.tb200_gqa_decode_workspace_bytes(4, 30, 8, 128) == 0
+    assert lib.tb200_gqa_decode_workspace_bytes(64, 32, 8, 128) > 0
+    st = lib.tb200_gqa_decode(None, None, None, None, None, None, 0, None, 0, None, None, 1, 1, 1,
+                              1, 8, 2, 64, 16, 128, 64, 0, 1.0, 0.0, None, 0, None)
+    assert st == 1 and b"non-null" in lib.tb200_last_error()
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.addressof(buf)
+    st = lib.tb200_gqa_decode(p, p, p, p, None, None, 16, None, 0, None, None, 1, 1, 1,
+                              1, 8, 3, 64, 16, 128, 64, 0, 1.0, 0.0, None, 0, None)
+    assert st == 1 and b"divisible" in lib.tb200_last_error()
+    st = lib.tb200_gqa_decode(p, p, p, p, None, None, 16, None, 0, None, None, 1, 1, 1,
+                              1, 8, 2, 96, 16, 192, 96, 0, 1.0, 0.0, None, 0, None)
+    assert st == 2 and b"head dim" in lib.tb200_last_error()
+    st = lib.tb200_gqa_lse_merge(None, None, None, None, 2, 4, 64, 0, 0, 3, None)
+    assert st == 1
+
+
+# ---------------------------------------------------------------------------- op layer
+class _Recorder(Kernel):
+    """Stand-in kernel: answers selection, compiles and launches nothing."""
+    supported_archs = None
+    general = True
+    built = []
+
+    def __init__(self, *args, **kwargs):
+        self.args, self.kwargs = args, kwargs
+        self.config = {}
+        type(self).built.append(self)
+
+    def forward(self, q, *rest, **kw):
+        self.last = (q, rest)
+        return torch.zeros_like(q)
+
+
+def test_constructor_validation_messages():
+    with pytest.raises(ValueError, match="heads must be divisible by heads_kv"):
+        GroupedQueryAttentionDecodeWithKVCacheFwdOp(1, 30, 8, 128, 64)
+    with pytest.raises(ValueError, match="heads_kv must be positive"):
+        GroupedQueryAttentionDecodeWithKVCacheFwdOp(1, 8, 0, 128, 64)
+    with pytest.raises(ValueError, match="softcap must be non-negative"):
+        GroupedQueryAttentionDecodeWithKVCacheFwdOp(1, 8, 2, 128, 64, softcap=-1.0)
+    with pytest.raises(ValueError, match="page_size must be positive"):
+        GroupedQueryAttentionDecodePagedWithKVCacheFwdOp(1, 8, 2, 128, 64, 0)
+    with pytest.raises(ValueError, match="seq_len must be positive"):
+        GroupedQueryAttentionFwdOp(1, 8, 2, 0, 64)
+    with pytest.raises(ValueError, match="causal prefill requires max_seqlen_q <= max_seqlen_kv"):
+        GroupedQueryAttentionPrefillFwdOp(1, 8, 2, 64, 128, 64)
+    with pytest.raises(ValueError, match="backend must be one of"):
+        GroupedQueryAttentionPrefillFwdOp(1, 8, 2, 64, 64, 64, backend="nope")
+    with pytest.raises(ValueError, match="requires validate_uniform_cu_seqlens=True"):
+        GroupedQueryAttentionPrefillFwdOp(1, 8, 2, 64, 64, 64, validate_uniform_cu_seqlens=False)
+    op = GroupedQueryAttentionDecodeWithKVCacheFwdOp(2, 8, 2, 256, 64)
+    assert op.sm_scale == 64 ** -0.5 and op.softcap == 0.0
+
+
+def test_construction_needs_no_device_and_selection_reports_arch():
+    op = GroupedQueryAttentionDecodePagedWithKVCacheFwdOp(1, 16, 4, 1024, 128, 64)
+    assert set(op.kernel_map) == {"gqa_decode_paged_kernel"}
+    if not torch.cuda.is_available():
+        with pytest.raises(ValueError, match="no implementation serves this call"):
+            op._get_kernel((), torch.float16)
+    with pytest.raises(ValueError, match="Expected dtype torch.float16 or torch.bfloat16"):
+        op._get_kernel((), torch.float32)
+
+
+@pytest.mark.parametrize("page_size", [96, 160, 224])
+def test_paged_rejects_unsupported_page_tile(page_size):
+    # tests/ops/attention/test_gqa_decode_paged.py:143-151 in the reference
+    with pytest.raises(ValueError, match="matches no supported block_N"):
+        gqa_decode_paged_block_ns(page_size)
+    assert gqa_decode_paged_block_ns(192) == (64,)
+    assert gqa_decode_paged_block_ns(16) == (16,)
+    assert gqa_decode_paged_block_ns(256) == (64,)
+
+
+def test_kernel_map_override_is_what_gets_built_positionally():
+    _Recorder.built.clear()
+    op = GroupedQueryAttentionDecodePagedWithKVCacheFwdOp(
+        2, 8, 2, 256, 64, 16, sm_scale=0.25, softcap=2.0, kernel_map={"gqa_decode_paged_kernel": _Recorder})
+    assert op._overridden_keys == {"gqa_decode_paged_kernel"}
+    q = torch.zeros(2, 8, 64, dtype=torch.bfloat16)
+    k = torch.zeros(256, 2, 64, dtype=torch.bfloat16)
+    lens = torch.zeros(2, dtype=torch.int32)
+    bt = torch.zeros(2, 16, dtype=torch.int32)
+    out = op(q, k, k, lens, bt)
+    assert out.shape == q.shape
+    (kern,) = _Recorder.built
+    assert kern.args == (2, 8, 2, 256, 64, 16, torch.bfloat16)
+    assert kern.kwargs == {"sm_scale": 0.25, "softcap": 2.0, "tune": False}
+    op(q, k, k, lens, bt)
+    assert len(_Recorder.built) == 1                       # cached per dtype
+    op(q.half(), k.half(), k.half(), lens, bt)
+    assert len(_Recorder.built) == 2
+    assert op.eval_roofline() == formulas.gqa_decode_paged_roofline(
+        batch=2, heads=8, heads_kv=2, seqlen_kv=256, dim=64, page_size=16, dtype=torch.float16)
+
+
+def test_refused_override_is_an_error_never_replaced():
+    class Refuses(_Recorder):
+        supported_archs = [1]
+
+    op = GroupedQueryAttentionDecodeWithKVCacheFwdOp(1, 8, 2, 64, 64, kernel_map={"gqa_decode_kernel": Refuses})
+    with pytest.raises(ValueError, match="the kernel supplied for gqa_decode_kernel"):
+        op._get_kernel((), torch.float16)
+
+
+def test_ambiguous_dispatch_is_reported():
+    class Special(_Recorder):
+        general = False
+
+    op = GroupedQueryAttentionDecodePagedWithKVCacheFwdOp(1, 8, 2, 64, 64, 16)
+    op.kernel_map = {"gqa_decode_paged_bs1_kernel": Special, "gqa_decode_paged_kernel": Special}
+    with pytest.raises(ValueError, match="dispatch is ambiguous"):
+        op.select_kernel_key(PAGED_DECODE_KEYS, AttentionCall(arch=100, dtype=torch.float16))
+    op.kernel_map = {"gqa_decode_paged_bs1_kernel": Special, "gqa_decode_paged_kernel": _Recorder}
+    assert op.select_kernel_key(PAGED_DECODE_KEYS, AttentionCall(arch=100)) == "gqa_decode_paged_bs1_kernel"
+
+
+def test_decode_op_validates_dtypes_and_passes_live_length():
+    _Recorder.built.clear()
+    op = GroupedQueryAttentionDecodeWithKVCacheFwdOp(2, 8, 2, 256, 64, kernel_map={"gqa_decode_kernel": _Recorder})
+    q = torch.zeros(2, 8, 64, dtype=torch.float16)
+    k = torch.zeros(2, 100, 2, 64, dtype=torch.float16)
+    with pytest.raises(ValueError, match="input 'k' has dtype torch.bfloat16, expected 'same_as\\(q\\)'"):
+        op(q, k.bfloat16(), k)
+    with pytest.raises(ValueError, match="input 'q' has dtype torch.float32"):
+        op(q.float(), k.float(), k.float())
+    op(q, k, k)
+    assert _Recorder.built[-1].last[1][2] == 100           # real_seqlen_kv, no padding copy
+    assert _Recorder.built[-1].args == (2, 8, 2, 256, 64, torch.float16)
+
+
+def test_fwd_op_shape_errors_and_packed_views():
+    _Recorder.built.clear()
+    op = GroupedQueryAttentionFwdOp(2, 8, 2, 16, 64, kernel_map={"gqa_prefill_fwd_kernel": _Recorder})
+    q = torch.zeros(2, 16, 8, 64, dtype=torch.bfloat16)
+    k = torch.zeros(2, 16, 2, 64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match=r"q must have shape \(2, 16, 8, 64\)"):
+        op(q[:, :8], k, k)
+    with pytest.raises(ValueError, match=r"v must have shape"):
+        op(q, k, k[:1])
+    out = op(q, k, k)
+    assert out.shape == q.shape
+    kern = _Recorder.built[-1]
+    assert kern.kwargs["max_seqlen_q"] == 16 and kern.kwargs["is_causal"] is True
+    assert kern.kwargs["accum_dtype"] == torch.float32 and kern.kwargs["dtype"] == torch.bfloat16
+    packed_q, rest = kern.last
+    assert packed_q.shape == (32, 8, 64) and rest[0].shape == (32, 2, 64)
+    assert rest[2].tolist() == [0, 16, 32] and rest[2].dtype == torch.int32
+    assert op.eval_roofline() == formulas.gqa_fwd_roofline(
+        batch=2, seq_len=16, heads=8, heads_kv=2, dim=64, is_causal=True, dtype=torch.bfloat16)
+
+
+def test_fp8_paged_op_contract():
+    _Recorder.built.clear()
+    op = GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp(
+        1, 8, 2, 64, 64, 16, kernel_map={"gqa_decode_paged_fp8_kernel": _Recorder})
+    q = torch.zeros(1, 8, 64, dtype=torch.bfloat16)
+    kf = torch.zeros(64, 2, 64, dtype=torch.float8_e4m3fn)
+    sc = torch.ones(4, 2)
+    lens = torch.zeros(1, dtype=torch.int32)
+    bt = torch.zeros(1, 4, dtype=torch.int32)
+    with pytest.raises(ValueError, match="input 'k' has dtype torch.bfloat16"):
+        op(q, kf.to(torch.bfloat16), kf, sc, sc, lens, bt)
+    with pytest.raises(ValueError, match=r"k_scale must have shape \(4, 2\)"):
+        op(q, kf, kf, sc[:2], sc, lens, bt)
+    op(q, kf, kf, sc, sc, lens, bt)
+    flops, nbytes = op.eval_roofline()
+    assert nbytes == formulas.gqa_decode_paged_roofline(
+        batch=1, heads=8, heads_kv=2, seqlen_kv=64, dim=64, page_size=16, dtype=torch.float8_e4m3fn)[1]
+
+
+# ---------------------------------------------------------------------------- plugin seam
+@pytest.fixture
+def clean_registry():
+    state = registry.snapshot()
+    yield
+    registry.restore(state)
+
+
+def test_backend_target_builder_receives_specs_and_params(clean_registry):
+    calls = []
+
+    def build(q, k, v, real_seqlen_kv, block_table, *, page_size, sm_scale, softcap):
+        calls.append((q, k, block_table, page_size, sm_scale, softcap))
+        return lambda *tensors: torch.full_like(tensors[0], 7)
+
+    backend.register_detector("fake", lambda device: device.type == "cpu")
+    backend.register_kernel_builder("GroupedQueryAttentionDecodePagedWithKVCacheFwdOp", "fake", build)
+    with pytest.raises(backend.BackendError):
+        backend.register_kernel_builder("GroupedQueryAttentionDecodePagedWithKVCacheFwdOp", "fake", build)
+    op = GroupedQueryAttentionDecodePagedWithKVCacheFwdOp(1, 8, 2, 64, 64, 16, softcap=3.0)
+    q = torch.zeros(1, 8, 64, dtype=torch.float16)
+    k = torch.zeros(64, 2, 64, dtype=torch.float16)
+    out = op(q, k, k, torch.zeros(1, dtype=torch.int32), torch.zeros(1, 4, dtype=torch.int32))
+    assert float(out[0, 0, 0]) == 7 and op._settled_target == "fake"
+    spec_q, spec_k, spec_bt, page, scale, cap = calls[0]
+    assert spec_q == backend.TensorSpec(torch.device("cpu"), torch.float16, (1, 8, 64))
+    assert spec_bt.dtype == torch.int32 and page == 16 and cap == 3.0 and scale == 64 ** -0.5
+    op(q, k, k, torch.zeros(1, dtype=torch.int32), torch.zeros(1, 4, dtype=torch.int32))
+    assert len(calls) == 1                                  # memoised per (device, dtypes, shapes)
+    with pytest.raises(backend.UnknownTargetError):
+        backend.set_default_target("nobody")
+    op2 = GroupedQueryAttentionDecodeWithKVCacheFwdOp(1, 8, 2, 64, 64)
+    with pytest.raises(backend.OpNotAvailableError):
+        op2(q, torch.zeros(1, 64, 2, 64, dtype=torch.float16), torch.zeros(1, 64, 2, 64, dtype=torch.float16))
+    assert op2._settled_target is None                      # a failed first call settles nothing
+
+
+def test_manifest_and_profile():
+    m = tileops_b200.manifest.load_manifest()
+    for name in ("GroupedQueryAttentionFwdOp", "GroupedQueryAttentionPrefillFwdOp",
+                 "GroupedQueryAttentionDecodeWithKVCacheFwdOp",
+                 "GroupedQueryAttentionDecodePagedWithKVCacheFwdOp"):
+        assert m[name]["status"] == "implemented" and m[name]["roofline"]["func"].startswith("tileops.perf.formulas.")
+    assert list(m["GroupedQueryAttentionDecodePagedWithKVCacheFwdOp"]["signature"]["inputs"]) == [
+        "q", "k", "v", "real_seqlen_kv", "block_table"]
+    assert GroupedQueryAttentionDecodePagedWithKVCacheFwdOp.__manifest_param_names__ == (
+        "page_size", "sm_scale", "softcap")
+    prof = load_profile("b200")
+    assert prof["arch"] == 100 and float(prof["hbm"]["effective"]) > 6e12
+
+
+def test_product_formulas_match_reference_values():
+    R = json.load(open(os.path.join(ROOT, "tests", "golden", "roofline_golden.json")))
+    F = formulas
+    assert list(F.gqa_decode_roofline(q_shape=(2, 8, 64), kv_shape=(2, 256, 2, 64), dtype=torch.float32)) == R["cfg1_decode"]
+    assert list(F.gqa_fwd_roofline(q_shape=(4, 4096, 32, 128), kv_shape=(4, 4096, 8, 128), is_causal=True,
+                                   dtype=torch.bfloat16)) == R["cfg2_fwd"]
+    assert list(F.gqa_fwd_roofline(batch=2, seq_len=512, heads=64, heads_kv=8, dim=128, is_causal=False,
+                                   dtype=torch.float16)) == R["fwd_noncausal_fp16"]
+    assert list(F.gqa_decode_roofline(q_shape=(32, 32, 128), kv_shape=(32, 4096, 8, 128), dtype=torch.float16)) == R["decode_llama8b_4k"]
+    assert list(F.gqa_decode_paged_roofline(q_shape=(32, 32, 128), kv_shape=(4096, 8, 128), page_size=64,
+                                            dtype=torch.float16)) == R["paged_probe"]
+    assert list(F.gqa_decode_paged_roofline(q_shape=(128, 64, 128), kv_shape=(524288, 8, 128), page_size=64,
+                                            dtype=torch.float8_e4m3fn)) == R["cfg4_paged_fp8"]
+    assert list(F.gqa_decode_paged_roofline(q_shape=(8, 32, 128), kv_shape=(1048576, 8, 128), page_size=128,
+                                            dtype=torch.bfloat16)) == R["cfg5_paged"]
+    assert list(F.gqa_prefill_varlen_fwd_roofline(
+        q_shape=(1024, 32, 128), k_shape=(8192, 8, 128), batch=2, max_seqlen_q=512, max_seqlen_kv=4096,
+        q_lens=[512, 512], kv_lens=[4096, 4096], is_causal=True, dtype=torch.bfloat16)) == R["varlen_packed"]
+    assert list(F.gqa_prefill_varlen_fwd_roofline(
+        q_shape=(40, 4, 32), k_shape=(72, 2, 32), batch=2, max_seqlen_q=24, max_seqlen_kv=50,
+        q_lens=[24, 16], kv_lens=[50, 22], is_causal=True, dtype=torch.float16)) == R["varlen_ragged"]
+
+
+def test_workload_generator_shards_reproduce_the_full_problem():
+    from tileops_b200 import workloads as W
+    full = W.make_paged_decode(9, 2, 4, 2, 16, 8, lens=[50, 21], dtype=torch.float32, device="cpu")
+    from oracle import gqa_oracle as O
+    for b in range(2):
+        rows = O.physical_rows(full.block_table[b].numpy(), full.lens[b], 8)
+        logical = full.k[torch.from_numpy(rows)]
+        parts = []
+        for (p0, p1) in ((0, 3), (3, 7)):
+            sh = W.make_paged_decode(9, 2, 4, 2, 16, 8, lens=[50, 21], dtype=torch.float32, device="cpu",
+                                     page_begin=p0, page_end=p1)
+            r = O.physical_rows(sh.block_table[b].numpy(), sh.lens[b], 8)
+            parts.append(sh.k[torch.from_numpy(r)])
+            assert torch.equal(sh.q, full.q)
+        assert torch.equal(torch.cat(parts), logical)

@@ -1,0 +1,90 @@
+"""ctypes binding of ``libtileops_b200.so`` (the C ABI declared in ``include/tileops_b200.h``).
+
+There is no fallback: if the library has not been built, importing a kernel raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_lib", "libtileops_b200.so")
+
+OK = 0
+F16, BF16, E4M3, F32 = 0, 1, 2, 3
+
+_DTYPE_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
+if hasattr(torch, "float8_e4m3fn"):
+    _DTYPE_CODE[torch.float8_e4m3fn] = E4M3
+
+#: every symbol ``include/tileops_b200.h`` declares: (restype, argtypes)
+SIGNATURES = {
+    "tb200_last_error": (c_char_p, []),
+    "tb200_version": (c_int, []),
+    "tb200_gqa_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "tb200_gqa_decode": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,      # q k v o lse
+        c_void_p, c_int32, c_void_p, c_int32,                  # lens uniform bt bt_stride
+        c_void_p, c_void_p,                                    # k_scale v_scale
+        c_int, c_int, c_int,                                   # q/kv/o dtype
+        c_int, c_int, c_int, c_int, c_int,                     # batch heads heads_kv dim page
+        c_int64, c_int64, c_int64,                             # strides
+        c_float, c_float,                                      # sm_scale softcap
+        c_void_p, c_size_t, c_void_p]),                        # workspace bytes stream
+    "tb200_gqa_lse_merge": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int,
+                                    c_int64, c_int64, c_int, c_void_p]),
+    "tb200_gqa_prefill_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
+    "tb200_gqa_prefill": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,      # q k v o lse
+        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,  # dtype B Sq Skv H Hkv D causal
+        c_float, c_float, c_void_p, c_size_t, c_void_p]),
+}
+
+_lib = None
+
+
+class NativeLibraryError(RuntimeError):
+    """The CUDA library is missing or a call into it failed."""
+
+
+def lib() -> ctypes.CDLL:
+    """Load the shared library once; raise if it is not there."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise NativeLibraryError(
+                f"{_LIB_PATH} not found: build it with `python -m tileops_b200.build` "
+                "(there is no CPU or eager fallback)")
+        handle = ctypes.CDLL(_LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise ValueError(f"dtype {dtype} has no kernel") from None
+
+
+def check(status: int, what: str) -> None:
+    if status != OK:
+        msg = lib().tb200_last_error().decode(errors="replace")
+        if status in (1, 2):
+            raise ValueError(f"{what}: {msg}")
+        raise NativeLibraryError(f"{what} failed with status {status}: {msg}")
+
+
+def ptr(t: "torch.Tensor | None") -> "int | None":
+    return None if t is None else t.data_ptr()
+
+
+def current_stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream

@@ -1,0 +1,679 @@
+// Single-token GQA decode over a paged or contiguous KV cache, sm_100a.
+//
+// Role in the reference: replaces GQADecodeKernel and GQADecodePagedKernel
+// (src/tileops/kernels/attention/gqa_decode.py:23-306, gqa_decode_paged.py:44-395 in
+// tile-ai/TileOPs), including their split-KV combine grid, in ONE launch and without the
+// reference's per-call host synchronisation on real_seqlen_kv.max().
+//
+// The op is HBM bound: every K and V byte is read exactly once.  Design:
+//   * work item = (sequence, KV head, contiguous run of 64-token tiles); the runs are cut on
+//     the device from real_seqlen_kv so that all items carry about the same number of
+//     tokens, and CTAs pull items from an atomic counter (no host sync, no idle tail);
+//   * K/V rows are gathered through the block table with 16-byte cp.async into a 3/4-stage
+//     shared-memory ring (rows padded by 16 B so that ldmatrix is bank-conflict free);
+//   * tokens sit on the MMA M dimension and the q-head group on N=8
+//     (S^T = K Q^T, O^T = V^T P^T, mma.sync.m16n8k16), so no tensor-core row is padding;
+//   * each of the 4 warps owns 16 tokens of a tile and keeps its own running max/sum
+//     (register + shuffle reductions); the warps meet once per item;
+//   * FP8-e4m3 caches are expanded to f16 in registers between ldmatrix and mma, the
+//     per-(page, KV head) scales are applied to the fp32 scores (K) and to P (V);
+//   * partial (O, max, sum) of an item go to a workspace in fp32; the CTA that finishes a
+//     (sequence, KV head) last merges them (atomic ticket, nobody waits).
+#include "tb200_common.cuh"
+
+namespace tb200 {
+namespace {
+
+constexpr int kTile = 64;          // tokens per shared-memory tile
+constexpr int kThreads = 128;      // 4 warps x 16 tokens
+constexpr int kWarps = 4;
+constexpr int kMinChunkTiles = 2;  // never cut a sequence into runs shorter than this
+constexpr int kItemsPerCta = 8;    // target number of work items per resident CTA
+constexpr int kMaxBatch = 4096;
+
+struct DecodeParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* lse;
+  const int32_t* lens;
+  int32_t uniform_len;
+  const int32_t* bt;
+  int32_t bt_stride;
+  const float* k_scale;
+  const float* v_scale;
+  int batch, heads, heads_kv, group;
+  int hb;       // q heads handled by one item (<= 8*NT)
+  int n_hb;     // head blocks per KV head
+  int page_size;
+  int tile_in_page;  // 1 when page_size % 64 == 0: a tile never straddles two pages
+  int64_t tok_stride, head_stride, batch_stride;  // elements
+  float sm_scale, softcap;
+  int q_is_bf16;
+  int target_items;
+  int max_items;
+  int* counters;   // [0] next item, [1] CTAs done, [2 + (b*heads_kv + hk)*n_hb + hb] tickets
+  float* part_o;   // [max_items][hb][D]
+  float* part_ml;  // [max_items][hb][2]
+};
+
+template <int D, bool FP8>
+struct Cfg {
+  static constexpr int kEsize = FP8 ? 1 : 2;
+  static constexpr int kRowBytes = D * kEsize;
+  static constexpr int kRowStride = kRowBytes + 16;
+  static constexpr int kChunksPerRow = kRowBytes / 16;
+  static constexpr int kTileBytes = kTile * kRowStride;
+  static constexpr int kStageBytes = 2 * kTileBytes + (FP8 ? 2 * kTile * 4 : 0);
+  static constexpr int kStages = FP8 ? 4 : 3;
+  static constexpr int kMinBlocks = FP8 ? 3 : 2;
+  static constexpr int kOStride = D + 4;  // fp32 words per head in the cross-warp merge area
+};
+
+template <int D, bool FP8>
+size_t smem_bytes(int batch, int nt) {
+  using C = Cfg<D, FP8>;
+  size_t ring = size_t(C::kStages) * C::kStageBytes;
+  size_t merge = size_t(kWarps) * (8 * nt) * (C::kOStride + 2) * 4;
+  size_t a = ring > merge ? ring : merge;
+  return a + size_t(batch + 1) * 4 + 64;
+}
+
+__device__ __forceinline__ float apply_softcap(float x, float cap, float inv_cap) {
+  return cap * fast_tanh(x * inv_cap);
+}
+
+// T  : MMA element type (bf16 or f16).  For FP8 caches T is f16 and q is converted.
+// TO : output element type.
+template <int D, bool FP8, typename T, int NT, typename TO>
+__global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_kernel(DecodeParams p) {
+  using C = Cfg<D, FP8>;
+  constexpr int kKSteps = D / 16;  // MMAs per 16 tokens for S^T, and m-tiles of O^T
+  extern __shared__ __align__(128) unsigned char smem[];
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int g8 = lane >> 2;  // "groupID" of the mma fragment layouts
+  const int t4 = lane & 3;   // "threadID_in_group"
+
+  unsigned char* ring = smem;
+  constexpr size_t kRing = size_t(C::kStages) * C::kStageBytes;
+  constexpr size_t kMerge = size_t(kWarps) * (8 * NT) * (C::kOStride + 2) * 4;
+  constexpr size_t kArea = kRing > kMerge ? kRing : kMerge;
+  int* s_prefix = reinterpret_cast<int*>(smem + kArea);  // [batch + 1] run counts, exclusive scan
+  int* s_misc = s_prefix + p.batch + 1;                   // [0] item, [1] ticket, [2..5] scratch
+
+  const int lanes_per_run = p.heads_kv * p.n_hb;
+
+  // ---- plan: cut every sequence into runs of tiles (identical in every CTA) -------------
+  {
+    int local = 0;
+    for (int b = tid; b < p.batch; b += kThreads) {
+      int len = p.lens ? p.lens[b] : p.uniform_len;
+      local += (max(len, 0) + kTile - 1) / kTile;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+    if (lane == 0) s_misc[2 + warp] = local;
+    __syncthreads();
+    const long long total_tiles = (long long)s_misc[2] + s_misc[3] + s_misc[4] + s_misc[5];
+    long long want = (total_tiles * lanes_per_run + p.target_items - 1) / p.target_items;
+    const int chunk = (int)max((long long)kMinChunkTiles, want);
+    __syncthreads();
+
+    const int per = (p.batch + kThreads - 1) / kThreads;
+    const int b0 = tid * per;
+    int sum = 0;
+    for (int i = 0; i < per; ++i) {
+      int b = b0 + i;
+      if (b < p.batch) {
+        int len = p.lens ? p.lens[b] : p.uniform_len;
+        int tiles = (max(len, 0) + kTile - 1) / kTile;
+        sum += max(1, (tiles + chunk - 1) / chunk);
+      }
+    }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    if (lane == 31) s_misc[2 + warp] = incl;
+    __syncthreads();
+    int base = 0;
+    for (int w = 0; w < warp; ++w) base += s_misc[2 + w];
+    int run = base + incl - sum;
+    for (int i = 0; i < per; ++i) {
+      int b = b0 + i;
+      if (b < p.batch) {
+        s_prefix[b] = run;
+        int len = p.lens ? p.lens[b] : p.uniform_len;
+        int tiles = (max(len, 0) + kTile - 1) / kTile;
+        run += max(1, (tiles + chunk - 1) / chunk);
+      }
+      if (b == p.batch - 1) s_prefix[p.batch] = run;
+    }
+    __syncthreads();
+  }
+  const int total_items = s_prefix[p.batch] * lanes_per_run;
+
+  const float qk_scale = p.softcap > 0.f ? p.sm_scale : p.sm_scale * kLog2e;
+  const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+
+  // per-lane ldmatrix offsets (bytes within a tile, before the k/d step is added)
+  //   K (both paths) and FP8 V: row = (l&7) + ((l>>3)&1)*8, 16-byte column block = l>>4
+  //   16-bit V (trans):         row = (l&7) + ((l>>4)&1)*8, 16-byte column block = (l>>3)&1
+  const int ld_row_a = (lane & 7) + ((lane >> 3) & 1) * 8;
+  const int ld_col_a = lane >> 4;
+  const int ld_row_v = FP8 ? ld_row_a : (lane & 7) + ((lane >> 4) & 1) * 8;
+  const int ld_col_v = FP8 ? ld_col_a : (lane >> 3) & 1;
+  const uint32_t ring_u32 = smem_u32(ring);
+  const uint32_t k_lane_off = (warp * 16 + ld_row_a) * C::kRowStride + ld_col_a * 16;
+  const uint32_t v_lane_off = C::kTileBytes + (warp * 16 + ld_row_v) * C::kRowStride + ld_col_v * 16;
+
+  while (true) {
+    __syncthreads();  // previous item's use of the ring / merge area and s_misc is over
+    if (tid == 0) s_misc[0] = atomicAdd(&p.counters[0], 1);
+    __syncthreads();
+    const int item = s_misc[0];
+    if (item >= total_items) break;
+
+    // ---- decode the item ------------------------------------------------------------
+    const int run = item / lanes_per_run;
+    const int rem = item - run * lanes_per_run;
+    const int hk = rem / p.n_hb;
+    const int hbi = rem - hk * p.n_hb;
+    int lo = 0, hi = p.batch - 1;  // largest b with s_prefix[b] <= run
+    while (lo < hi) {
+      int mid = (lo + hi + 1) >> 1;
+      if (s_prefix[mid] <= run) lo = mid; else hi = mid - 1;
+    }
+    const int b = lo;
+    const int len = max(p.lens ? p.lens[b] : p.uniform_len, 0);
+    const int tiles_b = (len + kTile - 1) / kTile;
+    const int n_runs = s_prefix[b + 1] - s_prefix[b];
+    const int j = run - s_prefix[b];
+    const int run_tiles = (tiles_b + n_runs - 1) / n_runs;
+    const int tile0 = min(j * run_tiles, tiles_b);
+    const int tile1 = min(tile0 + run_tiles, tiles_b);
+    const int n_tiles = tile1 - tile0;
+    const int head0 = hk * p.group + hbi * p.hb;           // first q head of this item
+    const int n_heads = min(p.hb, p.group - hbi * p.hb);   // q heads of this item
+
+    // ---- q fragments (B operand of S^T = K Q^T) ---------------------------------------
+    uint32_t qf[NT][kKSteps][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int hn = nt * 8 + g8;
+      const bool ok = hn < n_heads;
+      const size_t qoff = (size_t(b) * p.heads + head0 + (ok ? hn : 0)) * D;
+#pragma unroll
+      for (int ks = 0; ks < kKSteps; ++ks) {
+        if constexpr (!FP8) {
+          const T* qp = reinterpret_cast<const T*>(p.q) + qoff + ks * 16 + t4 * 2;
+          qf[nt][ks][0] = ok ? *reinterpret_cast<const uint32_t*>(qp) : 0u;
+          qf[nt][ks][1] = ok ? *reinterpret_cast<const uint32_t*>(qp + 8) : 0u;
+        } else {
+          // k index 2t,2t+1 <-> d = 16ks+4t+{0,1}; k index 2t+8,2t+9 <-> d = 16ks+4t+{2,3}
+          float f[4] = {0.f, 0.f, 0.f, 0.f};
+          if (ok) {
+            if (p.q_is_bf16) {
+              const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(p.q) + qoff + ks * 16 + t4 * 4;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) f[e] = __bfloat162float(qp[e]);
+            } else {
+              const __half* qp = reinterpret_cast<const __half*>(p.q) + qoff + ks * 16 + t4 * 4;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) f[e] = __half2float(qp[e]);
+            }
+          }
+          qf[nt][ks][0] = pack2<__half>(f[0], f[1]);
+          qf[nt][ks][1] = pack2<__half>(f[2], f[3]);
+        }
+      }
+    }
+
+    // ---- tile loader -----------------------------------------------------------------
+    const unsigned char* kbase = reinterpret_cast<const unsigned char*>(p.k) +
+                                 (size_t(hk) * p.head_stride + (p.bt ? 0 : size_t(b) * p.batch_stride)) * C::kEsize;
+    const unsigned char* vbase = reinterpret_cast<const unsigned char*>(p.v) +
+                                 (size_t(hk) * p.head_stride + (p.bt ? 0 : size_t(b) * p.batch_stride)) * C::kEsize;
+    const int32_t* bt_row = p.bt ? p.bt + size_t(b) * p.bt_stride : nullptr;
+    const size_t tok_bytes = size_t(p.tok_stride) * C::kEsize;
+    const int ld_chunk = tid % C::kChunksPerRow;
+    const int ld_row0 = tid / C::kChunksPerRow;
+    constexpr int kRowsPerPass = kThreads / C::kChunksPerRow;
+    constexpr int kPasses = kTile / kRowsPerPass;
+
+    // block-table entry of the next tile to be issued, fetched one tile ahead (fast path)
+    int32_t next_entry = 0;
+    auto fetch_entry = [&](int tile) {
+      if (bt_row && p.tile_in_page && tile < tile1) next_entry = bt_row[(tile * kTile) / p.page_size];
+    };
+    fetch_entry(tile0);
+
+    auto issue_tile = [&](int tile, int stage) {
+      const int tok0 = tile * kTile;
+      const uint32_t sk = ring_u32 + stage * C::kStageBytes;
+      const uint32_t sv = sk + C::kTileBytes;
+      int64_t phys0 = tok0;  // contiguous cache: physical == logical
+      int32_t page_entry = 0;
+      if (bt_row && p.tile_in_page) {
+        page_entry = next_entry;
+        phys0 = int64_t(page_entry) * p.page_size + (tok0 % p.page_size);
+        fetch_entry(tile + 1);
+      }
+#pragma unroll
+      for (int i = 0; i < kPasses; ++i) {
+        const int row = ld_row0 + i * kRowsPerPass;
+        const int tok = tok0 + row;
+        const bool ok = tok < len;
+        int64_t phys = phys0 + row;
+        if (bt_row && !p.tile_in_page) {
+          phys = ok ? int64_t(bt_row[tok / p.page_size]) * p.page_size + (tok % p.page_size) : 0;
+        }
+        const size_t off = ok ? size_t(phys) * tok_bytes + ld_chunk * 16 : 0;
+        const uint32_t d = row * C::kRowStride + ld_chunk * 16;
+        cp_async_16(sk + d, kbase + off, ok ? 16 : 0);
+        cp_async_16(sv + d, vbase + off, ok ? 16 : 0);
+      }
+      if constexpr (FP8) {
+        if (tid < kTile) {
+          const int tok = tok0 + tid;
+          const bool ok = tok < len;
+          int32_t pg = page_entry;
+          if (!p.tile_in_page || !bt_row) {
+            pg = ok ? (bt_row ? bt_row[tok / p.page_size]
+                              : int32_t((size_t(b) * (p.batch_stride / p.tok_stride) + tok) / p.page_size))
+                    : 0;
+          }
+          const size_t so = ok ? size_t(pg) * p.heads_kv + hk : 0;
+          const uint32_t ss = sk + 2 * C::kTileBytes + tid * 4;
+          cp_async_4(ss, p.k_scale + so, ok ? 4 : 0);
+          cp_async_4(ss + kTile * 4, p.v_scale + so, ok ? 4 : 0);
+        }
+      }
+    };
+
+    // ---- running state ----------------------------------------------------------------
+    float oacc[NT][kKSteps][4];
+    float m_run[NT][2], l_run[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      m_run[nt][0] = m_run[nt][1] = kNegFloor;
+      l_run[nt][0] = l_run[nt][1] = 0.f;
+#pragma unroll
+      for (int mt = 0; mt < kKSteps; ++mt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oacc[nt][mt][e] = 0.f;
+    }
+
+#pragma unroll
+    for (int s = 0; s < C::kStages - 1; ++s) {
+      if (s < n_tiles) issue_tile(tile0 + s, s);
+      cp_async_commit();
+    }
+
+    for (int it = 0; it < n_tiles; ++it) {
+      cp_async_wait<C::kStages - 2>();
+      __syncthreads();
+      {
+        const int nx = it + C::kStages - 1;
+        if (nx < n_tiles) issue_tile(tile0 + nx, nx % C::kStages);
+        cp_async_commit();
+      }
+      const int stage = it % C::kStages;
+      const uint32_t st_base = ring_u32 + stage * C::kStageBytes;
+      const int tok_a = (tile0 + it) * kTile + warp * 16 + g8;  // token of c0/c1; c2/c3 is +8
+
+      // ---- S^T = K Q^T  (16 tokens x 8*NT heads per warp) ---------------------------
+      float sacc[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sacc[nt][e] = 0.f;
+
+      if constexpr (!FP8) {
+#pragma unroll
+        for (int ks = 0; ks < kKSteps; ++ks) {
+          uint32_t a[4];
+          ldmatrix_x4(a, st_base + k_lane_off + ks * 32);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) mma_16816<T>(sacc[nt], a, qf[nt][ks]);
+        }
+      } else {
+#pragma unroll
+        for (int jj = 0; jj < D / 32; ++jj) {
+          uint32_t r[4];
+          ldmatrix_x4(r, st_base + k_lane_off + jj * 32);
+          uint32_t a0[4] = {e4m3x2_to_f16x2_scaled<0x1404>(r[0]), e4m3x2_to_f16x2_scaled<0x1404>(r[1]),
+                            e4m3x2_to_f16x2_scaled<0x3424>(r[0]), e4m3x2_to_f16x2_scaled<0x3424>(r[1])};
+          uint32_t a1[4] = {e4m3x2_to_f16x2_scaled<0x1404>(r[2]), e4m3x2_to_f16x2_scaled<0x1404>(r[3]),
+                            e4m3x2_to_f16x2_scaled<0x3424>(r[2]), e4m3x2_to_f16x2_scaled<0x3424>(r[3])};
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            mma_16816<T>(sacc[nt], a0, qf[nt][2 * jj]);
+            mma_16816<T>(sacc[nt], a1, qf[nt][2 * jj + 1]);
+          }
+        }
+      }
+
+      // ---- scale, softcap, mask, online softmax ----------------------------------------
+      float sc_lo = qk_scale, sc_hi = qk_scale;  // per-token score scale (rows g8 and g8+8)
+      float vs_lo = 1.f, vs_hi = 1.f;
+      if constexpr (FP8) {
+        const float* s_ks = reinterpret_cast<const float*>(ring + stage * C::kStageBytes + 2 * C::kTileBytes);
+        const float* s_vs = s_ks + kTile;
+        sc_lo *= s_ks[warp * 16 + g8] * 256.f;
+        sc_hi *= s_ks[warp * 16 + g8 + 8] * 256.f;
+        vs_lo = s_vs[warp * 16 + g8] * 256.f;
+        vs_hi = s_vs[warp * 16 + g8 + 8] * 256.f;
+      }
+      const bool ok_lo = tok_a < len, ok_hi = tok_a + 8 < len;
+      uint32_t pb[NT][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        float s0 = sacc[nt][0] * sc_lo, s1 = sacc[nt][1] * sc_lo;
+        float s2 = sacc[nt][2] * sc_hi, s3 = sacc[nt][3] * sc_hi;
+        if (p.softcap > 0.f) {
+          s0 = apply_softcap(s0, p.softcap, inv_cap) * kLog2e;
+          s1 = apply_softcap(s1, p.softcap, inv_cap) * kLog2e;
+          s2 = apply_softcap(s2, p.softcap, inv_cap) * kLog2e;
+          s3 = apply_softcap(s3, p.softcap, inv_cap) * kLog2e;
+        }
+        if (!ok_lo) { s0 = -INFINITY; s1 = -INFINITY; }
+        if (!ok_hi) { s2 = -INFINITY; s3 = -INFINITY; }
+        float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+        }
+        const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);
+        const float al0 = fast_exp2(m_run[nt][0] - mn0), al1 = fast_exp2(m_run[nt][1] - mn1);
+        m_run[nt][0] = mn0; m_run[nt][1] = mn1;
+        const float p0 = fast_exp2(s0 - mn0), p1 = fast_exp2(s1 - mn1);
+        const float p2 = fast_exp2(s2 - mn0), p3 = fast_exp2(s3 - mn1);
+        l_run[nt][0] = l_run[nt][0] * al0 + p0 + p2;
+        l_run[nt][1] = l_run[nt][1] * al1 + p1 + p3;
+#pragma unroll
+        for (int mt = 0; mt < kKSteps; ++mt) {
+          oacc[nt][mt][0] *= al0; oacc[nt][mt][1] *= al1;
+          oacc[nt][mt][2] *= al0; oacc[nt][mt][3] *= al1;
+        }
+        // P^T as the B operand: transpose the two 8x8 (token x head) blocks across the warp
+        pb[nt][0] = movmatrix_trans(pack2<T>(p0 * vs_lo, p1 * vs_lo));
+        pb[nt][1] = movmatrix_trans(pack2<T>(p2 * vs_hi, p3 * vs_hi));
+      }
+
+      // ---- O^T += V^T P^T ------------------------------------------------------------------
+      if constexpr (!FP8) {
+#pragma unroll
+        for (int mt = 0; mt < kKSteps; ++mt) {
+          uint32_t a[4];
+          ldmatrix_x4_trans(a, st_base + v_lane_off + mt * 32);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) mma_16816<T>(oacc[nt][mt], a, pb[nt]);
+        }
+      } else {
+#pragma unroll
+        for (int ii = 0; ii < D / 32; ++ii) {
+          uint32_t r[4];
+          ldmatrix_x4_trans(r, st_base + v_lane_off + ii * 32);
+          // register = 2 tokens x 2 dims; bytes (0,2) are dim 2*g8, bytes (1,3) dim 2*g8+1
+          uint32_t a0[4] = {e4m3x2_to_f16x2_scaled<0x2404>(r[0]), e4m3x2_to_f16x2_scaled<0x3414>(r[0]),
+                            e4m3x2_to_f16x2_scaled<0x2404>(r[1]), e4m3x2_to_f16x2_scaled<0x3414>(r[1])};
+          uint32_t a1[4] = {e4m3x2_to_f16x2_scaled<0x2404>(r[2]), e4m3x2_to_f16x2_scaled<0x3414>(r[2]),
+                            e4m3x2_to_f16x2_scaled<0x2404>(r[3]), e4m3x2_to_f16x2_scaled<0x3414>(r[3])};
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            mma_16816<T>(oacc[nt][2 * ii], a0, pb[nt]);
+            mma_16816<T>(oacc[nt][2 * ii + 1], a1, pb[nt]);
+          }
+        }
+      }
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // ring is free: reuse it as the cross-warp merge area
+
+    // ---- the 4 warps meet: per-warp (m, l, O^T) -> shared memory ---------------------------
+    float* s_o = reinterpret_cast<float*>(smem);                          // [warp][8*NT][kOStride]
+    float* s_ml = s_o + kWarps * (8 * NT) * C::kOStride;                  // [warp][8*NT][2]
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      float l0 = l_run[nt][0], l1 = l_run[nt][1];
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+      }
+      const int h0 = nt * 8 + t4 * 2;
+      if (g8 == 0) {
+        float* ml = s_ml + (warp * (8 * NT) + h0) * 2;
+        ml[0] = m_run[nt][0]; ml[1] = l0; ml[2] = m_run[nt][1]; ml[3] = l1;
+      }
+      float* so0 = s_o + (warp * (8 * NT) + h0) * C::kOStride;
+      float* so1 = so0 + C::kOStride;
+#pragma unroll
+      for (int mt = 0; mt < kKSteps; ++mt) {
+        // fragment rows -> head dims: 16-bit path rows g8, g8+8 of the m-tile; FP8 path the
+        // ldmatrix on byte pairs interleaves them: rows g8, g8+8 are dims 2*g8, 2*g8+1
+        const int d_lo = FP8 ? mt * 16 + 2 * g8 : mt * 16 + g8;
+        const int d_hi = FP8 ? d_lo + 1 : d_lo + 8;
+        so0[d_lo] = oacc[nt][mt][0]; so1[d_lo] = oacc[nt][mt][1];
+        so0[d_hi] = oacc[nt][mt][2]; so1[d_hi] = oacc[nt][mt][3];
+      }
+    }
+    __syncthreads();
+
+    const bool single = (n_runs == 1);
+    float* po = p.part_o + size_t(item) * p.hb * D;
+    float* pml = p.part_ml + size_t(item) * p.hb * 2;
+    TO* out = reinterpret_cast<TO*>(p.o);
+    for (int idx = tid; idx < n_heads * D; idx += kThreads) {
+      const int hn = idx / D, d = idx - hn * D;
+      float mw[kWarps], M = kNegFloor;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        mw[w] = s_ml[(w * (8 * NT) + hn) * 2];
+        M = fmaxf(M, mw[w]);
+      }
+      float acc = 0.f, L = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const float e = fast_exp2(mw[w] - M);
+        acc += e * s_o[(w * (8 * NT) + hn) * C::kOStride + d];
+        L += e * s_ml[(w * (8 * NT) + hn) * 2 + 1];
+      }
+      if (single) {
+        store_out<TO>(out + (size_t(b) * p.heads + head0 + hn) * D + d, L > 0.f ? acc / L : 0.f);
+        if (d == 0 && p.lse) p.lse[size_t(b) * p.heads + head0 + hn] = L > 0.f ? M + log2f(L) : -INFINITY;
+      } else {
+        po[hn * D + d] = acc;
+        if (d == 0) { pml[hn * 2] = M; pml[hn * 2 + 1] = L; }
+      }
+    }
+    if (single) continue;
+
+    // ---- split-KV: whoever finishes this (sequence, KV head, head block) last merges ----
+    __threadfence();
+    __syncthreads();
+    int* ticket = p.counters + 2 + (size_t(b) * p.heads_kv + hk) * p.n_hb + hbi;
+    if (tid == 0) s_misc[1] = atomicAdd(ticket, 1);
+    __syncthreads();
+    if (s_misc[1] != n_runs - 1) continue;
+    __threadfence();
+    const int first_item = s_prefix[b] * lanes_per_run + rem;
+    for (int idx = tid; idx < n_heads * D; idx += kThreads) {
+      const int hn = idx / D, d = idx - hn * D;
+      float M = kNegFloor;
+      for (int r = 0; r < n_runs; ++r)
+        M = fmaxf(M, __ldcg(p.part_ml + (size_t(first_item) + size_t(r) * lanes_per_run) * p.hb * 2 + hn * 2));
+      float acc = 0.f, L = 0.f;
+      for (int r = 0; r < n_runs; ++r) {
+        const size_t it2 = size_t(first_item) + size_t(r) * lanes_per_run;
+        const float* ml = p.part_ml + it2 * p.hb * 2 + hn * 2;
+        const float e = fast_exp2(__ldcg(ml) - M);
+        acc += e * __ldcg(p.part_o + it2 * p.hb * D + hn * D + d);
+        L += e * __ldcg(ml + 1);
+      }
+      store_out<TO>(out + (size_t(b) * p.heads + head0 + hn) * D + d, L > 0.f ? acc / L : 0.f);
+      if (d == 0 && p.lse) p.lse[size_t(b) * p.heads + head0 + hn] = L > 0.f ? M + log2f(L) : -INFINITY;
+    }
+    if (tid == 0) *ticket = 0;  // leave the workspace zeroed for the next launch
+  }
+
+  // ---- the last CTA to leave resets the scheduler counters ------------------------------
+  if (tid == 0) {
+    __threadfence();
+    const int done = atomicAdd(&p.counters[1], 1);
+    if (done == int(gridDim.x) - 1) {
+      p.counters[0] = 0;
+      p.counters[1] = 0;
+      __threadfence();
+    }
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+struct Layout {
+  size_t counters_bytes, part_o_bytes, part_ml_bytes, total;
+  int hb, n_hb, nt, target_items, max_items, grid;
+};
+
+Layout make_layout(int batch, int heads, int heads_kv, int dim, bool fp8) {
+  Layout L{};
+  const int group = heads / heads_kv;
+  L.hb = group < 16 ? group : 16;
+  L.nt = L.hb <= 8 ? 1 : 2;
+  L.n_hb = (group + L.hb - 1) / L.hb;
+  const int blocks_per_sm = fp8 ? 3 : 2;
+  L.grid = sm_count() * blocks_per_sm;
+  L.target_items = sm_count() * 3 * kItemsPerCta;  // independent of the cache dtype
+  L.max_items = batch * heads_kv * L.n_hb + L.target_items;
+  auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+  L.counters_bytes = up(size_t(2 + size_t(batch) * heads_kv * L.n_hb) * 4);
+  L.part_o_bytes = up(size_t(L.max_items) * L.hb * dim * 4);
+  L.part_ml_bytes = up(size_t(L.max_items) * L.hb * 2 * 4);
+  L.total = L.counters_bytes + L.part_o_bytes + L.part_ml_bytes;
+  return L;
+}
+
+template <int D, bool FP8, typename T, int NT, typename TO>
+int launch(const DecodeParams& p, int grid, cudaStream_t stream) {
+  auto kern = gqa_decode_kernel<D, FP8, T, NT, TO>;
+  const size_t smem = smem_bytes<D, FP8>(p.batch, NT);
+  static thread_local size_t configured[16] = {0};
+  int dev = 0;
+  TB200_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 16 && configured[dev] < smem) {
+    TB200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev] = smem;
+  } else if (dev >= 16) {
+    TB200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
+  kern<<<grid, kThreads, smem, stream>>>(p);
+  TB200_CUDA_CHECK(cudaGetLastError());
+  return TB200_OK;
+}
+
+template <int D, bool FP8, typename T, int NT>
+int launch_o(const DecodeParams& p, int o_dtype, int grid, cudaStream_t s) {
+  switch (o_dtype) {
+    case TB200_F32: return launch<D, FP8, T, NT, float>(p, grid, s);
+    case TB200_BF16: return launch<D, FP8, T, NT, __nv_bfloat16>(p, grid, s);
+    case TB200_F16: return launch<D, FP8, T, NT, __half>(p, grid, s);
+  }
+  TB200_FAIL(TB200_ERR_UNSUPPORTED, "o_dtype %d is not F16, BF16 or F32", o_dtype);
+}
+
+template <int D, int NT>
+int launch_t(const DecodeParams& p, int q_dtype, int kv_dtype, int o_dtype, int grid, cudaStream_t s) {
+  if (kv_dtype == TB200_E4M3) return launch_o<D, true, __half, NT>(p, o_dtype, grid, s);
+  if (q_dtype == TB200_BF16) return launch_o<D, false, __nv_bfloat16, NT>(p, o_dtype, grid, s);
+  return launch_o<D, false, __half, NT>(p, o_dtype, grid, s);
+}
+
+}  // namespace
+}  // namespace tb200
+
+using namespace tb200;
+
+extern "C" size_t tb200_gqa_decode_workspace_bytes(int batch, int heads, int heads_kv, int dim) {
+  if (batch <= 0 || heads <= 0 || heads_kv <= 0 || dim <= 0 || heads % heads_kv != 0) return 0;
+  return make_layout(batch, heads, heads_kv, dim, false).total;
+}
+
+extern "C" int tb200_gqa_decode(const void* q, const void* k, const void* v, void* o, float* lse,
+                                const int32_t* real_seqlen_kv, int32_t uniform_seqlen,
+                                const int32_t* block_table, int32_t block_table_stride,
+                                const float* k_scale, const float* v_scale,
+                                int q_dtype, int kv_dtype, int o_dtype,
+                                int batch, int heads, int heads_kv, int dim, int page_size,
+                                int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
+                                float sm_scale, float softcap,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  if (!q || !k || !v || !o) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k, v and o must be non-null");
+  if (batch <= 0 || heads <= 0 || heads_kv <= 0 || dim <= 0)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "batch, heads, heads_kv and dim must be positive");
+  if (heads % heads_kv != 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "heads must be divisible by heads_kv");
+  if (batch > kMaxBatch) TB200_FAIL(TB200_ERR_UNSUPPORTED, "batch %d exceeds %d", batch, kMaxBatch);
+  if (q_dtype != TB200_F16 && q_dtype != TB200_BF16)
+    TB200_FAIL(TB200_ERR_UNSUPPORTED, "q_dtype must be F16 or BF16");
+  if (kv_dtype != q_dtype && kv_dtype != TB200_E4M3)
+    TB200_FAIL(TB200_ERR_UNSUPPORTED, "kv_dtype must equal q_dtype or be E4M3");
+  if (o_dtype != q_dtype && o_dtype != TB200_F32)
+    TB200_FAIL(TB200_ERR_UNSUPPORTED, "o_dtype must equal q_dtype or be F32");
+  if (kv_dtype == TB200_E4M3 && (!k_scale || !v_scale))
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "an E4M3 cache needs k_scale and v_scale");
+  if (block_table || kv_dtype == TB200_E4M3) {
+    if (page_size <= 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "page_size must be positive");
+  }
+  if (block_table && block_table_stride <= 0)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "block_table_stride must be positive");
+  if (!real_seqlen_kv && uniform_seqlen < 0)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "uniform_seqlen must be non-negative");
+  if (softcap < 0.f) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "softcap must be non-negative");
+  if (dim != 64 && dim != 128) TB200_FAIL(TB200_ERR_UNSUPPORTED, "head dim %d (supported: 64, 128)", dim);
+  const int esize = kv_dtype == TB200_E4M3 ? 1 : 2;
+  if ((kv_token_stride * esize) % 16 != 0 || (kv_head_stride * esize) % 16 != 0 ||
+      (kv_batch_stride * esize) % 16 != 0 || (reinterpret_cast<uintptr_t>(k) & 15) ||
+      (reinterpret_cast<uintptr_t>(v) & 15) || (reinterpret_cast<uintptr_t>(q) & 7))
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "k/v base and strides must be 16-byte aligned (q 8-byte)");
+  if (!block_table && kv_token_stride <= 0)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "kv_token_stride must be positive");
+
+  const bool fp8 = kv_dtype == TB200_E4M3;
+  const Layout L = make_layout(batch, heads, heads_kv, dim, fp8);
+  if (!workspace || workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    TB200_FAIL(TB200_ERR_WORKSPACE, "workspace must be 256-byte aligned and hold %zu bytes (got %zu)",
+               L.total, workspace_bytes);
+
+  DecodeParams p{};
+  p.q = q; p.k = k; p.v = v; p.o = o; p.lse = lse;
+  p.lens = real_seqlen_kv; p.uniform_len = uniform_seqlen;
+  p.bt = block_table; p.bt_stride = block_table_stride;
+  p.k_scale = k_scale; p.v_scale = v_scale;
+  p.batch = batch; p.heads = heads; p.heads_kv = heads_kv; p.group = heads / heads_kv;
+  p.hb = L.hb; p.n_hb = L.n_hb;
+  p.page_size = page_size > 0 ? page_size : 1;
+  p.tile_in_page = (block_table && page_size % kTile == 0) ? 1 : 0;
+  p.tok_stride = kv_token_stride; p.head_stride = kv_head_stride; p.batch_stride = kv_batch_stride;
+  p.sm_scale = sm_scale; p.softcap = softcap;
+  p.q_is_bf16 = q_dtype == TB200_BF16;
+  p.target_items = L.target_items; p.max_items = L.max_items;
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  p.counters = reinterpret_cast<int*>(ws);
+  p.part_o = reinterpret_cast<float*>(ws + L.counters_bytes);
+  p.part_ml = reinterpret_cast<float*>(ws + L.counters_bytes + L.part_o_bytes);
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dim == 128)
+    return L.nt == 1 ? launch_t<128, 1>(p, q_dtype, kv_dtype, o_dtype, L.grid, s)
+                     : launch_t<128, 2>(p, q_dtype, kv_dtype, o_dtype, L.grid, s);
+  return L.nt == 1 ? launch_t<64, 1>(p, q_dtype, kv_dtype, o_dtype, L.grid, s)
+                   : launch_t<64, 2>(p, q_dtype, kv_dtype, o_dtype, L.grid, s);
+}

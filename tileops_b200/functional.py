@@ -1,0 +1,206 @@
+"""Tensor-level wrappers over the C ABI: argument checks, workspace cache, launch.
+
+These are what the kernel classes (``tileops_b200.kernels``) call.  They allocate the output
+with torch, hand raw pointers and the current torch CUDA stream to the library, and never
+synchronise with the device.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _native as N
+
+# One workspace per (device, stream, problem shape).  The kernel leaves its counters zeroed, so
+# the buffer is zero-filled only when it is created.  Keyed by stream because two launches that
+# overlap on the GPU must not share scheduler counters, and by shape because the position of
+# the counters inside the buffer depends on (batch, heads, heads_kv, dim): partial results of
+# one shape would otherwise land on the counters of another.
+_WORKSPACES: dict = {}
+
+
+def _decode_workspace(device: torch.device, batch: int, heads: int, heads_kv: int, dim: int) -> torch.Tensor:
+    need = N.lib().tb200_gqa_decode_workspace_bytes(batch, heads, heads_kv, dim)
+    if need == 0:
+        raise ValueError("invalid decode problem size")
+    key = (device, torch.cuda.current_stream(device).cuda_stream, "decode", batch, heads, heads_kv, dim)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def release_workspaces() -> None:
+    """Drop every cached workspace (e.g. before measuring memory)."""
+    _WORKSPACES.clear()
+
+
+def _require_cuda(**tensors: Optional[torch.Tensor]) -> None:
+    for name, t in tensors.items():
+        if t is not None and not t.is_cuda:
+            raise ValueError(f"{name} must be on a cuda device, got {t.device}")
+
+
+def gqa_decode(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    real_seqlen_kv: "torch.Tensor | int",
+    block_table: Optional[torch.Tensor] = None,
+    page_size: int = 0,
+    k_scale: Optional[torch.Tensor] = None,
+    v_scale: Optional[torch.Tensor] = None,
+    sm_scale: Optional[float] = None,
+    softcap: float = 0.0,
+    out_dtype: Optional[torch.dtype] = None,
+    return_lse: bool = False,
+    out: Optional[torch.Tensor] = None,
+    lse_out: Optional[torch.Tensor] = None,
+) -> "torch.Tensor | Tuple[torch.Tensor, torch.Tensor]":
+    """Single-token GQA decode.
+
+    q ``[B,H,D]``; paged cache (``block_table`` given): k/v ``[N,Hkv,D]``; contiguous cache:
+    k/v ``[B,S,Hkv,D]``.  ``real_seqlen_kv`` is an int32 device tensor ``[B]`` or one int for
+    all sequences.  An e4m3 cache needs ``k_scale``/``v_scale`` ``[N/page,Hkv]`` fp32.
+    Returns o ``[B,H,D]`` (and the log2-domain LSE ``[B,H]`` fp32 when asked).  ``out`` /
+    ``lse_out`` are optional preallocated contiguous destinations (e.g. slices of a
+    communication buffer).
+    """
+    _require_cuda(q=q, k=k, v=v, block_table=block_table, k_scale=k_scale, v_scale=v_scale)
+    if q.dim() != 3:
+        raise ValueError(f"q must have shape [B, H, D], got {tuple(q.shape)}")
+    B, H, D = q.shape
+    paged = block_table is not None
+    if paged:
+        if k.dim() != 3 or v.shape != k.shape or k.shape[2] != D:
+            raise ValueError(f"paged k/v must have shape [N, Hkv, {D}], got {tuple(k.shape)} / {tuple(v.shape)}")
+        Hkv = k.shape[1]
+        if block_table.dtype != torch.int32 or block_table.dim() != 2 or block_table.shape[0] != B:
+            raise ValueError("block_table must be int32 with shape [B, num_pages]")
+        if page_size <= 0:
+            raise ValueError("page_size must be positive")
+        block_table = block_table.contiguous()
+    else:
+        if k.dim() != 4 or v.shape != k.shape or k.shape[0] != B or k.shape[3] != D:
+            raise ValueError(f"k/v must have shape [{B}, S, Hkv, {D}], got {tuple(k.shape)} / {tuple(v.shape)}")
+        Hkv = k.shape[2]
+    if H % Hkv != 0:
+        raise ValueError("heads must be divisible by heads_kv")
+    q = q.contiguous()
+    k = k.contiguous()
+    v = v.contiguous()
+    fp8 = k.dtype == getattr(torch, "float8_e4m3fn", None)
+    if fp8:
+        if k_scale is None or v_scale is None:
+            raise ValueError("an float8_e4m3fn cache needs k_scale and v_scale")
+        if k_scale.dtype != torch.float32 or v_scale.dtype != torch.float32:
+            raise ValueError("k_scale/v_scale must be torch.float32")
+        k_scale, v_scale = k_scale.contiguous(), v_scale.contiguous()
+    elif k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError(f"k/v dtype {k.dtype} must equal q dtype {q.dtype} (or be float8_e4m3fn)")
+
+    lens_t = None
+    uniform = 0
+    if isinstance(real_seqlen_kv, torch.Tensor):
+        _require_cuda(real_seqlen_kv=real_seqlen_kv)
+        if real_seqlen_kv.dtype != torch.int32 or tuple(real_seqlen_kv.shape) != (B,):
+            raise ValueError("real_seqlen_kv must be int32 with shape [B]")
+        lens_t = real_seqlen_kv.contiguous()
+    else:
+        uniform = int(real_seqlen_kv)
+        if not paged and uniform > k.shape[1]:
+            raise ValueError(f"real_seqlen_kv {uniform} exceeds the cache length {k.shape[1]}")
+
+    if out is not None:
+        if tuple(out.shape) != (B, H, D) or not out.is_contiguous() or out.device != q.device:
+            raise ValueError("out must be a contiguous [B, H, D] tensor on q's device")
+        out_dtype = out.dtype
+    out_dtype = q.dtype if out_dtype is None else out_dtype
+    o = torch.empty((B, H, D), dtype=out_dtype, device=q.device) if out is None else out
+    if lse_out is not None:
+        if tuple(lse_out.shape) != (B, H) or lse_out.dtype != torch.float32 or not lse_out.is_contiguous():
+            raise ValueError("lse_out must be a contiguous float32 [B, H] tensor")
+        return_lse = True
+    lse = lse_out if lse_out is not None else (
+        torch.empty((B, H), dtype=torch.float32, device=q.device) if return_lse else None)
+    ws = _decode_workspace(q.device, B, H, Hkv, D)
+    scale = D ** -0.5 if sm_scale is None else float(sm_scale)
+    if paged:
+        tok_stride, head_stride, batch_stride = k.stride(0), k.stride(1), 0
+    else:
+        tok_stride, head_stride, batch_stride = k.stride(1), k.stride(2), k.stride(0)
+    with torch.cuda.device(q.device):
+        st = N.lib().tb200_gqa_decode(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), N.ptr(lse),
+            N.ptr(lens_t), uniform, N.ptr(block_table), block_table.shape[1] if paged else 0,
+            N.ptr(k_scale) if fp8 else None, N.ptr(v_scale) if fp8 else None,
+            N.dtype_code(q.dtype), N.dtype_code(k.dtype), N.dtype_code(out_dtype),
+            B, H, Hkv, D, int(page_size),
+            tok_stride, head_stride, batch_stride,
+            scale, float(softcap or 0.0),
+            ws.data_ptr(), ws.numel(), N.current_stream(q.device))
+    N.check(st, "tb200_gqa_decode")
+    return (o, lse) if return_lse else o
+
+
+def gqa_lse_merge(o_parts: torch.Tensor, lse_parts: torch.Tensor, out_dtype: torch.dtype,
+                  return_lse: bool = False):
+    """o_parts ``[R, ..., D]`` fp32 and lse_parts ``[R, ...]`` fp32 (log2 domain) -> merged o.
+
+    Each part must be contiguous; the parts themselves may be strided along dim 0 (views into
+    an all-gather buffer)."""
+    _require_cuda(o_parts=o_parts, lse_parts=lse_parts)
+    if o_parts.dtype != torch.float32 or lse_parts.dtype != torch.float32:
+        raise ValueError("o_parts and lse_parts must be torch.float32")
+    if tuple(o_parts.shape[:-1]) != tuple(lse_parts.shape):
+        raise ValueError("o_parts must have shape lse_parts.shape + [D]")
+    if not o_parts[0].is_contiguous():
+        o_parts = o_parts.contiguous()
+    if not lse_parts[0].is_contiguous():
+        lse_parts = lse_parts.contiguous()
+    R, D = o_parts.shape[0], o_parts.shape[-1]
+    rows = lse_parts[0].numel()
+    o_stride = o_parts.stride(0) if R > 1 else 0
+    l_stride = lse_parts.stride(0) if R > 1 else 0
+    o = torch.empty(o_parts.shape[1:], dtype=out_dtype, device=o_parts.device)
+    lse = torch.empty(lse_parts.shape[1:], dtype=torch.float32, device=o_parts.device) if return_lse else None
+    with torch.cuda.device(o_parts.device):
+        st = N.lib().tb200_gqa_lse_merge(o_parts.data_ptr(), lse_parts.data_ptr(), o.data_ptr(), N.ptr(lse),
+                                         R, rows, D, o_stride, l_stride, N.dtype_code(out_dtype),
+                                         N.current_stream(o_parts.device))
+    N.check(st, "tb200_gqa_lse_merge")
+    return (o, lse) if return_lse else o
+
+
+def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal: bool = True,
+                sm_scale: Optional[float] = None, softcap: float = 0.0, return_lse: bool = False):
+    """Dense BSHD prefill: q ``[B,Sq,H,D]``, k/v ``[B,Skv,Hkv,D]`` -> o ``[B,Sq,H,D]`` (+ LSE
+    ``[B,H,Sq]`` fp32, log2 domain)."""
+    _require_cuda(q=q, k=k, v=v)
+    if q.dim() != 4 or k.dim() != 4 or v.shape != k.shape:
+        raise ValueError("q must be [B,Sq,H,D] and k/v [B,Skv,Hkv,D]")
+    B, Sq, H, D = q.shape
+    Skv, Hkv = k.shape[1], k.shape[2]
+    if k.shape[0] != B or k.shape[3] != D:
+        raise ValueError("k/v batch and head dim must match q")
+    if H % Hkv != 0:
+        raise ValueError("heads must be divisible by heads_kv")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("q/k/v dtypes must match")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    o = torch.empty_like(q)
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device) if return_lse else None
+    need = N.lib().tb200_gqa_prefill_workspace_bytes(B, H, Hkv, Sq, Skv, D)
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device=q.device) if need else None
+    scale = D ** -0.5 if sm_scale is None else float(sm_scale)
+    with torch.cuda.device(q.device):
+        st = N.lib().tb200_gqa_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), N.ptr(lse),
+                                       N.dtype_code(q.dtype), B, Sq, Skv, H, Hkv, D, int(bool(is_causal)),
+                                       scale, float(softcap or 0.0), N.ptr(ws), need,
+                                       N.current_stream(q.device))
+    N.check(st, "tb200_gqa_prefill")
+    return (o, lse) if return_lse else o

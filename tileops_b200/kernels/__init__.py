@@ -1,0 +1,14 @@
+from .call_spec import AttentionCall, CallSpec
+from .gqa_decode import (
+    GQADecodePagedFp8Sm100Kernel,
+    GQADecodePagedSm100Kernel,
+    GQADecodeSm100Kernel,
+    gqa_decode_paged_block_ns,
+)
+from .gqa_prefill import GQAPrefillSm100Kernel
+from .kernel_base import Kernel
+
+__all__ = [
+    "AttentionCall", "CallSpec", "Kernel", "GQADecodeSm100Kernel", "GQADecodePagedSm100Kernel",
+    "GQADecodePagedFp8Sm100Kernel", "GQAPrefillSm100Kernel", "gqa_decode_paged_block_ns",
+]

@@ -1,0 +1,67 @@
+"""sm_100a kernel class for dense GQA prefill (L1 of the operator stack).
+
+Replaces, in the ``gqa_prefill_fwd_kernel`` slot, the reference's ``GQAPrefillFwdKernel``
+(``src/tileops/kernels/attention/gqa_fwd.py:519-597``) and stands in for its two Hopper-only
+specialisations (``gqa_prefill_fwd_ws.py:436``, ``gqa_fwd_ws.py:1075``), none of which runs on
+sm_100.  Keyword constructor and packed ``forward`` follow the reference
+(``src/tileops/ops/attention/gqa.py:113-128``, ``kernels/attention/packed_prefill.py:71-83``):
+the packed THD tensors of a uniform batch are viewed as BSHD and handed to the tcgen05 kernel
+through the C ABI (``tb200_gqa_prefill``).
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import functional as F
+from .call_spec import ATTENTION_DTYPES, dense_prefill_region
+from .kernel_base import Kernel
+
+__all__ = ["GQAPrefillSm100Kernel"]
+
+
+class GQAPrefillSm100Kernel(Kernel):
+    supported_archs = [100]
+    general = True
+
+    @classmethod
+    def applies(cls, call) -> bool:
+        return dense_prefill_region(call) and call.dim == 128 and call.dtype in ATTENTION_DTYPES
+
+    def __init__(self, batch, heads, heads_kv, max_seqlen_q, max_seqlen_kv, dim, is_causal, dtype,
+                 sm_scale=None, softcap=0.0, window_size_left=-1, window_size_right=-1,
+                 accum_dtype=torch.float32, config: Optional[dict] = None, tune: bool = False,
+                 device_index=None) -> None:
+        super().__init__(device_index=device_index)
+        if dim != 128:
+            raise ValueError(f"GQAPrefillSm100Kernel supports head dim 128, got {dim}")
+        if window_size_left != -1 or window_size_right != -1:
+            raise ValueError("GQAPrefillSm100Kernel does not serve sliding-window calls")
+        self.batch, self.heads, self.heads_kv, self.dim = batch, heads, heads_kv, dim
+        self.max_seqlen_q, self.max_seqlen_kv = max_seqlen_q, max_seqlen_kv
+        self.is_causal, self.dtype = is_causal, dtype
+        self.sm_scale = dim ** -0.5 if sm_scale is None else sm_scale
+        self.softcap = 0.0 if softcap is None else softcap
+        self.tune = tune
+        self.init_config(config, tune)
+
+    @property
+    def default_config(self) -> dict:
+        return {"block_M": 128, "block_N": 128, "threads": 192}
+
+    def forward(self, q, k, v, cu_seqlens_q=None, cu_seqlens_kv=None, q_scale=None, k_scale=None,
+                v_scale=None, return_lse: bool = False):
+        """q ``[B*Sq,H,D]``, k/v ``[B*Skv,Hkv,D]`` of a uniform batch -> o ``[B*Sq,H,D]``."""
+        self._require_cuda(q=q, k=k, v=v)
+        B, Sq, Skv = self.batch, self.max_seqlen_q, self.max_seqlen_kv
+        if q.shape[0] != B * Sq or k.shape[0] != B * Skv:
+            raise ValueError(
+                f"packed q/k must hold {B}x{Sq} and {B}x{Skv} tokens, got {q.shape[0]} and {k.shape[0]}")
+        out = F.gqa_prefill(q.view(B, Sq, self.heads, self.dim), k.view(B, Skv, self.heads_kv, self.dim),
+                            v.view(B, Skv, self.heads_kv, self.dim), is_causal=self.is_causal,
+                            sm_scale=self.sm_scale, softcap=self.softcap, return_lse=return_lse)
+        if return_lse:
+            return out[0].view(q.shape), out[1]
+        return out.view(q.shape)

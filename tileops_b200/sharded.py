@@ -1,0 +1,99 @@
+"""KV-sequence sharded paged decode across GPUs: local split-KV decode, one all-gather of
+(O, LSE), local merge.
+
+The reference has no multi-GPU attention; it scales the KV length only inside one GPU with
+split-KV plus a combine grid (``src/tileops/kernels/attention/gqa_decode_paged.py:176-395``).
+This lifts the same algebra one level: rank ``r`` owns a range of every sequence's LOGICAL
+pages in a local pool with a local block table and local lengths, runs the ordinary decode
+kernel to a normalised fp32 partial ``O_r`` and a log2-domain ``LSE_r``, and the ranks
+exchange ``B*H*(D+1)`` floats each (132 KB at B=8, H=32, D=128).  The merge
+``O = sum_r 2^(LSE_r - LSE) O_r`` is associative, so intra-GPU and inter-GPU merges compose.
+
+The decode kernel writes its partial straight into the send half of one communication
+buffer; the all-gather lands every rank's partial in local memory and the merge kernel reads
+only local memory (no kernel here ever loads from a peer).
+
+``decode_fn`` / ``merge_fn`` default to the CUDA kernels; they are injectable so that the
+protocol (packing, gather layout, empty shards) can be exercised by CPU ranks over gloo.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import functional as F
+
+
+def shard_page_range(num_pages: int, rank: int, world: int) -> "tuple[int, int]":
+    """Logical pages ``[begin, end)`` of a sequence with ``num_pages`` pages owned by ``rank``
+    (contiguous, remainder spread over the first ranks)."""
+    base, rem = divmod(num_pages, world)
+    begin = rank * base + min(rank, rem)
+    return begin, begin + base + (1 if rank < rem else 0)
+
+
+class KVSequenceShardedPagedDecode:
+    """Paged GQA decode whose KV cache is split by sequence position across a process group.
+
+    ``forward(q, k_local, v_local, local_seqlen_kv, local_block_table)``: ``q`` is replicated;
+    the other arguments describe only this rank's slice.  Every rank returns the full result.
+    """
+
+    def __init__(self, batch: int, heads: int, heads_kv: int, dim: int, page_size: int,
+                 sm_scale: Optional[float] = None, softcap: Optional[float] = None,
+                 group: Optional[dist.ProcessGroup] = None,
+                 decode_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None) -> None:
+        if heads % heads_kv != 0:
+            raise ValueError("heads must be divisible by heads_kv")
+        self.batch, self.heads, self.heads_kv, self.dim = batch, heads, heads_kv, dim
+        self.page_size = page_size
+        self.sm_scale = dim ** -0.5 if sm_scale is None else sm_scale
+        self.softcap = 0.0 if softcap is None else softcap
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self._decode = decode_fn or self._cuda_decode
+        self._merge = merge_fn or self._cuda_merge
+        self._buffers: dict = {}
+
+    # default compute: the CUDA kernels
+    def _cuda_decode(self, q, k, v, lens, bt, out, lse_out):
+        F.gqa_decode(q, k, v, real_seqlen_kv=lens, block_table=bt, page_size=self.page_size,
+                     sm_scale=self.sm_scale, softcap=self.softcap, out=out, lse_out=lse_out)
+
+    @staticmethod
+    def _cuda_merge(o_parts, lse_parts, out_dtype):
+        return F.gqa_lse_merge(o_parts, lse_parts, out_dtype)
+
+    def _comm_buffers(self, device: torch.device):
+        bufs = self._buffers.get(device)
+        if bufs is None:
+            n = self.batch * self.heads * (self.dim + 1)
+            send = torch.empty(n, dtype=torch.float32, device=device)
+            recv = torch.empty(self.world * n, dtype=torch.float32, device=device)
+            bufs = (send, recv)
+            self._buffers[device] = bufs
+        return bufs
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                local_seqlen_kv: torch.Tensor, local_block_table: torch.Tensor) -> torch.Tensor:
+        B, H, D = self.batch, self.heads, self.dim
+        if tuple(q.shape) != (B, H, D):
+            raise ValueError(f"q must have shape {(B, H, D)}, got {tuple(q.shape)}")
+        send, recv = self._comm_buffers(q.device)
+        n_o = B * H * D
+        o_part = send[:n_o].view(B, H, D)
+        lse_part = send[n_o:].view(B, H)
+        self._decode(q, k, v, local_seqlen_kv, local_block_table, o_part, lse_part)
+        if self.world == 1:
+            return self._merge(o_part.unsqueeze(0), lse_part.unsqueeze(0), q.dtype)
+        dist.all_gather_into_tensor(recv, send, group=self.group)
+        parts = recv.view(self.world, B * H * (D + 1))
+        o_parts = parts[:, :n_o].unflatten(1, (B, H, D))      # strided over ranks, each part contiguous
+        lse_parts = parts[:, n_o:].unflatten(1, (B, H))
+        return self._merge(o_parts, lse_parts, q.dtype)
+
+    __call__ = forward
