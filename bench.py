@@ -119,16 +119,26 @@ def dist_env():
 
 def time_steps(fn, steps: int, warmup: int, world: int, sampler=None):
     """W untimed steps, then exactly K steps between a barrier+synchronize on both sides, timed
-    with CUDA events on the launching (current) stream.  Returns this rank's elapsed ms."""
+    with CUDA events on the launching (current) stream.  Returns this rank's elapsed ms.
+
+    With a clock sampler the untimed part is stretched to about 1.5 s of the same step, the
+    sampler running from its start to the end of the timed region: the timed region itself
+    lasts only milliseconds, far less than one nvidia-smi sampling period, so the samples
+    describe the clocks the GPU holds under this load when the timed steps run."""
     import torch.distributed as dist
+    if sampler:
+        sampler.start()
+        t_end = time.perf_counter() + 1.5
+        while time.perf_counter() < t_end:
+            for _ in range(20):
+                fn()
+            torch.cuda.synchronize()
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    if sampler:
-        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
@@ -250,7 +260,13 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-others", action="store_true", help="time only the headline workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None,
+                    choices=["decode_small", "decode_fp8_small", "prefill_small"],
+                    help="run only a reduced case of one kernel (a few hundred MB on the device: the "
+                         "size an ncu capture of all sections can handle) and print its timing")
     a = ap.parse_args()
+    if a.case:
+        return run_small_case(a.case, a.steps, max(a.warmup, 1))
     rank, world, local = dist_env()
     warmup = max(a.warmup, 3)
     workload = ("BASELINE config 3: GQA paged decode bf16, batch 64, 32 q heads / 8 KV heads, head_dim 128, "
@@ -324,6 +340,37 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
+
+
+def run_small_case(case: str, steps: int, warmup: int):
+    """Reduced single-kernel cases for profiler captures: same kernels and code path as the
+    BASELINE configurations, a quarter of the batch (inputs still exceed the L2)."""
+    from tileops_b200 import workloads as W
+    from tileops_b200.ops import (GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp,
+                                  GroupedQueryAttentionDecodePagedWithKVCacheFwdOp,
+                                  GroupedQueryAttentionFwdOp)
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    if case == "decode_small":
+        inp = W.make_paged_decode(3, 16, 32, 8, 128, 64, len_range=(512, 8192), device=device)
+        op = GroupedQueryAttentionDecodePagedWithKVCacheFwdOp(16, 32, 8, inp.k.shape[0], 128, 64)
+        fn = lambda: op(inp.q, inp.k, inp.v, inp.real_seqlen_kv, inp.block_table)  # noqa: E731
+        work, unit = inp.algorithmic_bytes(), "GB/s"
+    elif case == "decode_fp8_small":
+        inp = W.make_paged_decode(4, 32, 64, 8, 128, 64, lens=[4096] * 32, fp8_cache=True, device=device)
+        op = GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp(32, 64, 8, inp.k.shape[0], 128, 64)
+        fn = lambda: op(inp.q, inp.k, inp.v, inp.k_scale, inp.v_scale, inp.real_seqlen_kv, inp.block_table)  # noqa: E731
+        work, unit = inp.algorithmic_bytes(), "GB/s"
+    else:
+        q, k, v = W.make_prefill(2, 1, 4096, 4096, 32, 8, 128, torch.bfloat16, device)
+        op = GroupedQueryAttentionFwdOp(1, 32, 8, 4096, 128, is_causal=True)
+        fn = lambda: op(q, k, v)  # noqa: E731
+        fn()
+        work, unit = op.eval_roofline()[0], "TFLOP/s"
+    ms = time_steps(fn, steps, warmup, 1) / steps
+    rate = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
+    print(json.dumps({"case": case, "ms_per_step": ms, "work_per_step": work, "rate": rate, "unit": unit,
+                      "steps": steps, "warmup": warmup}))
 
 
 def run_others(rank, world, device, steps, warmup, peaks):

@@ -210,7 +210,7 @@ def test_fp8_expansion_is_exact_for_every_byte():
     v8 = v.view(torch.float8_e4m3fn).cuda()
     k8 = torch.zeros_like(v8)
     scale = torch.tensor([[0.5], [0.015625]], device="cuda")
-    q = torch.zeros(1, H, D, device="cuda", dtype=torch.bfloat16); q[..., 0] = 1
+    q = torch.zeros(1, H, D, device="cuda", dtype=torch.bfloat16); q[..., 0] = 64  # score >= 448: one-hot
     for r in (0, 63, 64, 127):
         kk = k8.clone().view(torch.uint8); kk[r, 0, 0] = 0x7E            # 448: wins the softmax
         out = F.gqa_decode(q, kk.view(torch.float8_e4m3fn), v8, real_seqlen_kv=torch.tensor([rows], dtype=torch.int32, device="cuda"),
