@@ -44,8 +44,8 @@ FALLBACK_BF16_TFLOPS = 1590.0
 
 # DRAM traffic per launch relative to the algorithmic bytes, from the ncu capture summarised in
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum of gqa_decode_kernel on a scaled-down
-# config-3 case; traffic grows in proportion to the live tokens).  None until captured.
-NCU_TRAFFIC_RATIO = {"cfg3": None}
+# config-3 case; traffic grows in proportion to the live tokens).
+NCU_TRAFFIC_RATIO = {"cfg3": 1.026}
 
 
 def measured_peaks():

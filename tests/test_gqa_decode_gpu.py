@@ -242,7 +242,9 @@ def test_split_merge_property_at_config3_size():
     o2, l2 = F.gqa_decode(inp.q, inp.k, inp.v, real_seqlen_kv=(inp.real_seqlen_kv - half).to(torch.int32),
                           block_table=bt2, page_size=64, return_lse=True, out_dtype=torch.float32)
     merged, ml = F.gqa_lse_merge(torch.stack([o1, o2]), torch.stack([l1, l2]), torch.float32, return_lse=True)
-    torch.testing.assert_close(merged, o, atol=2e-5, rtol=1e-4)
+    # P is rounded to bf16 before the PV product, differently for different running maxima,
+    # so the two evaluations agree to bf16-P noise, not to fp32 round-off
+    torch.testing.assert_close(merged, o, atol=2e-3, rtol=1e-2)
     torch.testing.assert_close(ml, lse, atol=1e-4, rtol=1e-5)
     mo, _ = O.merge_partials_ref(torch.stack([o1, o2]).cpu(), torch.stack([l1, l2]).cpu())
     torch.testing.assert_close(merged.cpu(), mo, atol=1e-5, rtol=1e-5)

@@ -1,8 +1,542 @@
-// placeholder until the tcgen05 prefill kernel lands
+// Dense GQA prefill (flash-attention forward) for sm_100a: tcgen05 MMAs with TMEM accumulators,
+// TMA-fed shared memory, online softmax in registers.
+//
+// Role in the reference: replaces GQAPrefillFwdKernel (src/tileops/kernels/attention/gqa_fwd.py:
+// 309-468, 519-597 in tile-ai/TileOPs) and its Hopper-only warp-specialised variants
+// (gqa_prefill_fwd_ws.py:59-433, gqa_fwd_ws.py:503-1030), none of which runs on sm_100.  Same
+// math: S = Q K^T, bottom-right aligned causal mask, exp2-domain online softmax with fp32
+// accumulation, O = P V, optional softcap, log2-domain LSE.
+//
+// One CTA = one 128-row Q tile of one (batch, q head); 6 warps:
+//   warps 0-3  softmax / correction / epilogue: thread r owns row r (TMEM lane r), no shuffles
+//   warp  4    TMA producer (one lane): Q once, then K_j, V_j into 2-stage rings
+//   warp  5    MMA issuer (one lane) and TMEM allocator
+// TMEM (512 columns): S0 [0,128) | S1 [128,256) | O [256,384).  P_j (bf16) overwrites the first
+// 64 columns of S_j and feeds the second MMA straight from TMEM.  The issue order
+// QK_0, QK_1, PV_0, QK_2, PV_1, ... lets the tensor core compute S_{j+1} while the softmax
+// warps work on S_j.
+//
+// Shared memory operands are [128 rows x 64 elements] panels (128-byte rows, 128B swizzle), two
+// panels per 128x128 tile, written by TMA and described to the MMA by 64-bit matrix descriptors:
+// Q and K are K-major (rows = M/N, 128 B = 64 K-elements), V is MN-major (rows = tokens = K).
+//
+// Every mbarrier wait is bounded; on a timeout the CTA records an error code, stops issuing work,
+// lets its copies drain, frees its TMEM and returns.
+#include <cuda.h>
+
 #include "tb200_common.cuh"
+
+namespace tb200 {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBN = 128;
+constexpr int kHD = 128;
+constexpr int kStages = 2;
+constexpr int kPanelBytes = 128 * 128;       // 128 rows x 128 B
+constexpr int kTileBytes = 2 * kPanelBytes;  // 128 x 128 bf16
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256;
+constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
+
+struct SmemLayout {
+  // offsets from the 1024-aligned base
+  static constexpr int q = 0;
+  static constexpr int k = q + kTileBytes;
+  static constexpr int v = k + kStages * kTileBytes;
+  static constexpr int bars = v + kStages * kTileBytes;
+  static constexpr int total = bars + 256;
+};
+// barrier indices
+enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PREADY = 11, B_ODONE = 13, B_COUNT = 14 };
+
+struct PrefillParams {
+  void* o;
+  float* lse;
+  int* status;
+  int batch, heads, heads_kv, seqlen_q, seqlen_kv;
+  int is_causal;
+  float sm_scale, softcap;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this wait ran out, or another role's did).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                            int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// 64-bit shared-memory matrix descriptor, 128B swizzle, version 1 (sm_100).
+//   [0,14) start address >> 4 | [16,30) leading byte offset >> 4 | [32,46) stride byte offset >> 4
+//   [46,48) version = 1 | [61,64) layout type (2 = SWIZZLE_128B)
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) |
+         (uint64_t(sbo_bytes >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+
+// Instruction descriptor of kind::f16: fp32 accumulate, A/B format fmt (0 = f16, 1 = bf16),
+// M = 128, N = 128, A K-major; B K-major (b_mn = 0) or MN-major (b_mn = 1).
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t b_mn) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi) { return pack2<T>(lo, hi); }
+
+// ---- kernel --------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, PrefillParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SmemLayout::bars);
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + B_COUNT);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  auto bar = [&](int i) { return smem_u32(bars + i); };
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+
+  // ---- which tile ---------------------------------------------------------------------
+  const int n_m = (p.seqlen_q + kBM - 1) / kBM;
+  const int per_m = p.heads * p.batch;
+  const int mt = n_m - 1 - int(blockIdx.x) / per_m;        // heaviest (last) row tiles first
+  const int rest = int(blockIdx.x) % per_m;
+  const int b = rest / p.heads, h = rest % p.heads;
+  const int hk = h / (p.heads / p.heads_kv);
+  const int m0 = mt * kBM;
+  const int off = p.seqlen_kv - p.seqlen_q;                // bottom-right alignment
+  int n_kv = (p.seqlen_kv + kBN - 1) / kBN;
+  if (p.is_causal) {
+    const int last_key = m0 + kBM - 1 + off;               // last key the tile's last row may see
+    n_kv = last_key < 0 ? 0 : min(n_kv, last_key / kBN + 1);
+  }
+
+  if (tid == 0) {
+    mbar_init(bar(B_QFULL), 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar(B_KFULL + s), 1);
+      mbar_init(bar(B_KEMPTY + s), 1);
+      mbar_init(bar(B_VFULL + s), 1);
+      mbar_init(bar(B_VEMPTY + s), 1);
+      mbar_init(bar(B_SFULL + s), 1);
+      mbar_init(bar(B_PREADY + s), 128);
+    }
+    mbar_init(bar(B_ODONE), 1);
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+
+  constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+  constexpr uint32_t idesc_qk = make_idesc(fmt, 0);
+  constexpr uint32_t idesc_pv = make_idesc(fmt, 1);
+
+  if (n_kv > 0) {
+    if (warp == 4) {
+      // ================= TMA producer =================
+      if (lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+        mbar_expect_tx(bar(B_QFULL), kTileBytes);
+        tma_load_4d(sbase + SmemLayout::q, &map_q, bar(B_QFULL), 0, h, m0, b);
+        tma_load_4d(sbase + SmemLayout::q + kPanelBytes, &map_q, bar(B_QFULL), 64, h, m0, b);
+        for (int j = 0; j < n_kv; ++j) {
+          const int s = j % kStages;
+          const uint32_t par = (j / kStages) & 1;
+          if (!mbar_wait(bar(B_KEMPTY + s), par ^ 1, s_abort, p.status, 101)) break;
+          mbar_expect_tx(bar(B_KFULL + s), kTileBytes);
+          const uint32_t kd = sbase + SmemLayout::k + s * kTileBytes;
+          tma_load_4d(kd, &map_k, bar(B_KFULL + s), 0, hk, j * kBN, b);
+          tma_load_4d(kd + kPanelBytes, &map_k, bar(B_KFULL + s), 64, hk, j * kBN, b);
+          if (!mbar_wait(bar(B_VEMPTY + s), par ^ 1, s_abort, p.status, 102)) break;
+          mbar_expect_tx(bar(B_VFULL + s), kTileBytes);
+          const uint32_t vd = sbase + SmemLayout::v + s * kTileBytes;
+          tma_load_4d(vd, &map_v, bar(B_VFULL + s), 0, hk, j * kBN, b);
+          tma_load_4d(vd + kPanelBytes, &map_v, bar(B_VFULL + s), 64, hk, j * kBN, b);
+        }
+      }
+    } else if (warp == 5) {
+      // ================= MMA issuer =================
+      if (lane == 0) {
+        bool ok = mbar_wait(bar(B_QFULL), 0, s_abort, p.status, 201);
+        auto issue_pv = [&](int t) -> bool {
+          const int s = t % kStages;
+          const uint32_t par = (t / kStages) & 1;
+          if (!mbar_wait(bar(B_VFULL + s), par, s_abort, p.status, 203)) return false;
+          if (!mbar_wait(bar(B_PREADY + s), par, s_abort, p.status, 204)) return false;
+          tc_fence_after();
+          const uint32_t vbase = sbase + SmemLayout::v + s * kTileBytes;
+          const uint32_t p_tmem = tmem + (s == 0 ? kColS0 : kColS1);
+#pragma unroll
+          for (int ks = 0; ks < kBN / 16; ++ks) {
+            // B = V: MN-major, 16 tokens per step = 16 rows of 128 B; the two 64-wide d panels
+            // are kPanelBytes apart (leading offset), 8-row groups 1024 B apart (stride offset)
+            const uint64_t bd = make_desc(vbase + ks * 2048, kPanelBytes, 1024);
+            tc_mma_ts(tmem + kColO, p_tmem + ks * 8, bd, idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
+          }
+          tc_commit(bar(B_VEMPTY + s));
+          tc_commit(bar(B_ODONE));
+          return true;
+        };
+        for (int j = 0; ok && j < n_kv; ++j) {
+          const int s = j % kStages;
+          const uint32_t par = (j / kStages) & 1;
+          if (!mbar_wait(bar(B_KFULL + s), par, s_abort, p.status, 202)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t qbase = sbase + SmemLayout::q;
+          const uint32_t kbase = sbase + SmemLayout::k + s * kTileBytes;
+#pragma unroll
+          for (int ks = 0; ks < kHD / 16; ++ks) {
+            // K-major operands: 16 elements per step = 32 B inside the 128 B swizzled row;
+            // after 4 steps move to the second 64-element panel
+            const uint32_t o = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
+            tc_mma_ss(tmem + (s == 0 ? kColS0 : kColS1), make_desc(qbase + o, 16, 1024),
+                      make_desc(kbase + o, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+          }
+          tc_commit(bar(B_SFULL + s));
+          tc_commit(bar(B_KEMPTY + s));
+          if (j >= 1) ok = issue_pv(j - 1);
+        }
+        if (ok) issue_pv(n_kv - 1);
+      }
+    } else {
+      // ================= softmax / correction / epilogue (thread = row) =================
+      const int row = tid;                                  // 0..127 == TMEM lane
+      const uint32_t lane_addr = uint32_t(warp * 32) << 16;
+      const float cap = p.softcap;
+      const bool use_cap = cap > 0.f;
+      const float c = use_cap ? kLog2e : p.sm_scale * kLog2e;   // multiplies the raw (or capped) score
+      const float pre = use_cap ? p.sm_scale / cap : 0.f;
+      const int q_idx = m0 + row;
+      const int key_limit = p.is_causal ? q_idx + off : 0x7fffffff;  // last visible key of this row
+      float m_run = -INFINITY, l_run = 0.f;
+      bool ok = true;
+
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j % kStages;
+        const uint32_t par = (j / kStages) & 1;
+        if (!mbar_wait(bar(B_SFULL + s), par, s_abort, p.status, 301)) { ok = false; break; }
+        __syncwarp();
+        tc_fence_after();
+        const uint32_t s_addr = tmem + lane_addr + (s == 0 ? kColS0 : kColS1);
+        uint32_t sv[4][32];
+#pragma unroll
+        for (int cgi = 0; cgi < 4; ++cgi) tc_ld32(s_addr + cgi * 32, sv[cgi]);
+        tc_wait_ld();
+
+        const int k0 = j * kBN;
+        const bool need_mask = (k0 + kBN - 1 > m0 + off && p.is_causal) || (k0 + kBN > p.seqlen_kv);
+        float mx = -INFINITY;
+#pragma unroll
+        for (int cgi = 0; cgi < 4; ++cgi) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            float x = __uint_as_float(sv[cgi][e]);
+            if (use_cap) x = cap * fast_tanh(x * pre);
+            if (need_mask) {
+              const int key = k0 + cgi * 32 + e;
+              if (key > key_limit || key >= p.seqlen_kv) x = -INFINITY;
+            }
+            sv[cgi][e] = __float_as_uint(x);
+            mx = fmaxf(mx, x);
+          }
+        }
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        const float alpha = fast_exp2((m_run - m_use) * c);     // m_run = -inf -> 0
+        const float neg_mc = -m_use * c;
+        float lsum = 0.f;
+#pragma unroll
+        for (int cgi = 0; cgi < 4; ++cgi) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[cgi][2 * e]), c, neg_mc));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[cgi][2 * e + 1]), c, neg_mc));
+            lsum += p0 + p1;
+            pk[e] = pack_pair<T>(p0, p1);
+          }
+          tc_st16(s_addr + cgi * 16, pk);                     // P overwrites S (already in registers)
+        }
+        l_run = l_run * alpha + lsum;
+        m_run = m_new;
+
+        if (j > 0) {
+          // O holds sum over tiles < j, scaled to the old max: wait for PV_{j-1}, then rescale
+          if (!mbar_wait(bar(B_ODONE), (j - 1) & 1, s_abort, p.status, 302)) { ok = false; break; }
+          __syncwarp();
+          tc_fence_after();
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+            const uint32_t o_addr = tmem + lane_addr + kColO;
+#pragma unroll
+            for (int cgi = 0; cgi < 4; ++cgi) {
+              uint32_t ov[32];
+              tc_ld32(o_addr + cgi * 32, ov);
+              tc_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+              tc_st32(o_addr + cgi * 32, ov);
+            }
+          }
+        }
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(B_PREADY + s));
+      }
+
+      // ---- epilogue: O / l -> global, LSE ----
+      if (ok) ok = mbar_wait(bar(B_ODONE), (n_kv - 1) & 1, s_abort, p.status, 303);
+      __syncwarp();
+      if (ok) {
+        tc_fence_after();
+        const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+        const uint32_t o_addr = tmem + lane_addr + kColO;
+        T* orow = reinterpret_cast<T*>(p.o) + ((size_t(b) * p.seqlen_q + q_idx) * p.heads + h) * kHD;
+#pragma unroll
+        for (int cgi = 0; cgi < 4; ++cgi) {
+          uint32_t ov[32];
+          tc_ld32(o_addr + cgi * 32, ov);
+          tc_wait_ld();
+          if (q_idx < p.seqlen_q) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 w;
+              w.x = pack_pair<T>(__uint_as_float(ov[e]) * inv_l, __uint_as_float(ov[e + 1]) * inv_l);
+              w.y = pack_pair<T>(__uint_as_float(ov[e + 2]) * inv_l, __uint_as_float(ov[e + 3]) * inv_l);
+              w.z = pack_pair<T>(__uint_as_float(ov[e + 4]) * inv_l, __uint_as_float(ov[e + 5]) * inv_l);
+              w.w = pack_pair<T>(__uint_as_float(ov[e + 6]) * inv_l, __uint_as_float(ov[e + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow + cgi * 32 + e) = w;
+            }
+          }
+        }
+        if (p.lse && q_idx < p.seqlen_q)
+          p.lse[(size_t(b) * p.heads + h) * p.seqlen_q + q_idx] =
+              l_run > 0.f ? m_run * c + log2f(l_run) : -INFINITY;
+      }
+    }
+  } else if (warp < 4) {
+    // the whole row tile is masked: zeros, LSE = -inf
+    const int q_idx = m0 + tid;
+    if (q_idx < p.seqlen_q) {
+      T* orow = reinterpret_cast<T*>(p.o) + ((size_t(b) * p.seqlen_q + q_idx) * p.heads + h) * kHD;
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int e = 0; e < kHD; e += 8) *reinterpret_cast<uint4*>(orow + e) = z;
+      if (p.lse) p.lse[(size_t(b) * p.heads + h) * p.seqlen_q + q_idx] = -INFINITY;
+    }
+  }
+
+  // ---- teardown -----------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*s_abort) {
+    // give copies still in flight time to land before the shared memory is released
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  if (warp == 5) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// [batch, seq, heads, 128] contiguous 16-bit tensor -> 4-D map (d, head, seq, batch), box 64 x 1 x 128 x 1
+int make_map(CUtensorMap* map, const void* base, int dtype, int batch, int seq, int heads) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) TB200_FAIL(TB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[4] = {cuuint64_t(kHD), cuuint64_t(heads), cuuint64_t(seq), cuuint64_t(batch)};
+  cuuint64_t strides[3] = {cuuint64_t(kHD) * 2, cuuint64_t(heads) * kHD * 2, cuuint64_t(seq) * heads * kHD * 2};
+  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, dtype == TB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) TB200_FAIL(TB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+  return TB200_OK;
+}
+
+template <typename T>
+int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p,
+                   cudaStream_t stream) {
+  auto kern = gqa_prefill_kernel<T>;
+  const int smem = SmemLayout::total + 1024;
+  static thread_local bool configured = false;
+  if (!configured) {
+    TB200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  const int n_m = (p.seqlen_q + kBM - 1) / kBM;
+  const long long grid = (long long)n_m * p.heads * p.batch;
+  if (grid > 0x7fffffffLL) TB200_FAIL(TB200_ERR_UNSUPPORTED, "problem too large for one launch");
+  kern<<<unsigned(grid), kThreads, smem, stream>>>(mq, mk, mv, p);
+  TB200_CUDA_CHECK(cudaGetLastError());
+  return TB200_OK;
+}
+
+}  // namespace
+}  // namespace tb200
+
 using namespace tb200;
-extern "C" size_t tb200_gqa_prefill_workspace_bytes(int, int, int, int, int, int) { return 0; }
-extern "C" int tb200_gqa_prefill(const void*, const void*, const void*, void*, float*, int, int, int, int, int,
-                                 int, int, int, float, float, void*, size_t, void*) {
-  TB200_FAIL(TB200_ERR_UNSUPPORTED, "prefill kernel not built yet");
+
+extern "C" size_t tb200_gqa_prefill_workspace_bytes(int batch, int heads, int heads_kv, int seqlen_q,
+                                                    int seqlen_kv, int dim) {
+  (void)batch; (void)heads; (void)heads_kv; (void)seqlen_q; (void)seqlen_kv; (void)dim;
+  return 256;  // one status word (0 = ok; otherwise the code of the wait that ran out)
+}
+
+extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, void* o, float* lse, int dtype,
+                                 int batch, int seqlen_q, int seqlen_kv, int heads, int heads_kv, int dim,
+                                 int is_causal, float sm_scale, float softcap, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+  if (!q || !k || !v || !o) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k, v and o must be non-null");
+  if (batch <= 0 || seqlen_q <= 0 || seqlen_kv <= 0 || heads <= 0 || heads_kv <= 0)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "batch, seqlen_q, seqlen_kv, heads and heads_kv must be positive");
+  if (heads % heads_kv != 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "heads must be divisible by heads_kv");
+  if (dim != kHD) TB200_FAIL(TB200_ERR_UNSUPPORTED, "head dim %d (the tcgen05 prefill kernel serves 128)", dim);
+  if (dtype != TB200_BF16 && dtype != TB200_F16) TB200_FAIL(TB200_ERR_UNSUPPORTED, "dtype must be F16 or BF16");
+  if (!(sm_scale > 0.f)) TB200_FAIL(TB200_ERR_UNSUPPORTED, "sm_scale must be positive");
+  if (softcap < 0.f) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "softcap must be non-negative");
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(o)) & 15)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k, v and o must be 16-byte aligned");
+  if (!workspace || workspace_bytes < 256) TB200_FAIL(TB200_ERR_WORKSPACE, "workspace must hold 256 bytes");
+
+  CUtensorMap mq, mk, mv;
+  int st;
+  if ((st = make_map(&mq, q, dtype, batch, seqlen_q, heads)) != TB200_OK) return st;
+  if ((st = make_map(&mk, k, dtype, batch, seqlen_kv, heads_kv)) != TB200_OK) return st;
+  if ((st = make_map(&mv, v, dtype, batch, seqlen_kv, heads_kv)) != TB200_OK) return st;
+
+  PrefillParams p{};
+  p.o = o; p.lse = lse; p.status = static_cast<int*>(workspace);
+  p.batch = batch; p.heads = heads; p.heads_kv = heads_kv; p.seqlen_q = seqlen_q; p.seqlen_kv = seqlen_kv;
+  p.is_causal = is_causal; p.sm_scale = sm_scale; p.softcap = softcap;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return dtype == TB200_BF16 ? launch_prefill<__nv_bfloat16>(mq, mk, mv, p, s)
+                             : launch_prefill<__half>(mq, mk, mv, p, s);
 }
