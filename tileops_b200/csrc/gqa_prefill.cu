@@ -38,7 +38,7 @@ constexpr int kTileBytes = 2 * kPanelBytes;  // 128 x 128 bf16
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256;
-constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
+constexpr long long kWaitCycles = 1000000000LL;  // ~0.5 s at 2 GHz
 
 struct SmemLayout {
   // offsets from the 1024-aligned base
@@ -195,6 +195,12 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
+  // an earlier CTA of this launch gave up on a wait: do not start more work (one thread reads
+  // the flag so that the whole CTA takes the same decision)
+  __shared__ int s_skip;
+  if (tid == 0) s_skip = *reinterpret_cast<volatile int*>(p.status);
+  __syncthreads();
+  if (s_skip != 0) return;
 
   // ---- which tile ---------------------------------------------------------------------
   const int n_m = (p.seqlen_q + kBM - 1) / kBM;
@@ -434,6 +440,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   }
 
   // ---- teardown -----------------------------------------------------------------------
+  __syncwarp();   // the single-lane roles rejoin their warps before the block-wide barrier
   tc_fence_before();
   __syncthreads();
   if (*s_abort) {
@@ -485,11 +492,7 @@ int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
                    cudaStream_t stream) {
   auto kern = gqa_prefill_kernel<T>;
   const int smem = SmemLayout::total + 1024;
-  static thread_local bool configured = false;
-  if (!configured) {
-    TB200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
-  }
+  TB200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int n_m = (p.seqlen_q + kBM - 1) / kBM;
   const long long grid = (long long)n_m * p.heads * p.batch;
   if (grid > 0x7fffffffLL) TB200_FAIL(TB200_ERR_UNSUPPORTED, "problem too large for one launch");

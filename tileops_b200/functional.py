@@ -176,6 +176,26 @@ def gqa_lse_merge(o_parts: torch.Tensor, lse_parts: torch.Tensor, out_dtype: tor
     return (o, lse) if return_lse else o
 
 
+def _prefill_status(device: torch.device, need: int) -> torch.Tensor:
+    """Zeroed status buffer of the prefill kernel, one per device (the kernel writes it only when
+    a bounded device-side wait runs out)."""
+    key = (device, "prefill_status")
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 256), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def prefill_status(device: "torch.device | str" = "cuda") -> int:
+    """0 if no prefill launch on ``device`` has timed out on a device-side wait, else the code of
+    the wait that gave up (synchronises with the device)."""
+    ws = _WORKSPACES.get((torch.device(device) if not isinstance(device, torch.device) else device, "prefill_status"))
+    if ws is None:
+        return 0
+    return int(ws[:4].view(torch.int32).item())
+
+
 def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal: bool = True,
                 sm_scale: Optional[float] = None, softcap: float = 0.0, return_lse: bool = False):
     """Dense BSHD prefill: q ``[B,Sq,H,D]``, k/v ``[B,Skv,Hkv,D]`` -> o ``[B,Sq,H,D]`` (+ LSE
@@ -195,7 +215,7 @@ def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal:
     o = torch.empty_like(q)
     lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device) if return_lse else None
     need = N.lib().tb200_gqa_prefill_workspace_bytes(B, H, Hkv, Sq, Skv, D)
-    ws = torch.empty(max(need, 1), dtype=torch.uint8, device=q.device) if need else None
+    ws = _prefill_status(q.device, need)
     scale = D ** -0.5 if sm_scale is None else float(sm_scale)
     with torch.cuda.device(q.device):
         st = N.lib().tb200_gqa_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), N.ptr(lse),
