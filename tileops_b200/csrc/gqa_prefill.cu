@@ -329,8 +329,8 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       for (int j = 0; j < n_kv; ++j) {
         const int s = j % kStages;
         const uint32_t par = (j / kStages) & 1;
-        if (!mbar_wait(bar(B_SFULL + s), par, s_abort, p.status, 301)) { ok = false; break; }
-        __syncwarp();
+        // the warp leaves the loop together: the TMEM loads below are warp-collective
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(B_SFULL + s), par, s_abort, p.status, 301))) { ok = false; break; }
         tc_fence_after();
         const uint32_t s_addr = tmem + lane_addr + (s == 0 ? kColS0 : kColS1);
         uint32_t sv[4][32];
@@ -377,8 +377,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
         if (j > 0) {
           // O holds sum over tiles < j, scaled to the old max: wait for PV_{j-1}, then rescale
-          if (!mbar_wait(bar(B_ODONE), (j - 1) & 1, s_abort, p.status, 302)) { ok = false; break; }
-          __syncwarp();
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(B_ODONE), (j - 1) & 1, s_abort, p.status, 302))) { ok = false; break; }
           tc_fence_after();
           if (__any_sync(0xffffffffu, alpha != 1.f)) {
             const uint32_t o_addr = tmem + lane_addr + kColO;
@@ -400,7 +399,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
       // ---- epilogue: O / l -> global, LSE ----
       if (ok) ok = mbar_wait(bar(B_ODONE), (n_kv - 1) & 1, s_abort, p.status, 303);
-      __syncwarp();
+      ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after();
         const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
