@@ -94,6 +94,43 @@ int tb200_gqa_decode(const void* q, const void* k, const void* v, void* o, float
                      void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * tb200_gqa_decode for callers that cannot allocate device memory.  (No counterpart in the
+ * reference: its kernels allocate their split-KV buffers with torch on every call,
+ * src/tileops/kernels/attention/gqa_decode_paged.py:711-721.)
+ *
+ * Who needs it: a serving runtime that gives the whole device to its own pool allocator at
+ * start-up and forbids cudaMalloc afterwards, or a plugin inside another framework whose
+ * allocator it may not bypass.  Such a caller has nowhere to get the workspace from, so this
+ * variant keeps the split-KV scratch (scheduler counters, merge tickets, fp32 partials) in a
+ * fixed array inside the library: TB200_DECODE_STATIC_SCRATCH_BYTES of device memory on every
+ * GPU that loads the library, held until the process exits.
+ *
+ * Arguments and results are those of tb200_gqa_decode without workspace / workspace_bytes; q, k,
+ * v, o (and lse, tables, scales) are still the caller's.  The call itself allocates nothing
+ * (no cudaMalloc / cudaFree, no allocating library routine): it clears the counters of the
+ * shared array with cudaMemsetAsync on `stream` and launches the same kernel.
+ *
+ *   - A problem whose scratch need (tb200_gqa_decode_workspace_bytes) exceeds
+ *     TB200_DECODE_STATIC_SCRATCH_BYTES is refused with TB200_ERR_WORKSPACE and a message
+ *     naming both sizes; nothing is launched.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current) and loads the kernels; make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  Calls that may overlap on the GPU (different
+ *     streams, or different host threads) race on it and give wrong results; serialise them on
+ *     one stream or use tb200_gqa_decode with separate workspaces.
+ * ------------------------------------------------------------------------- */
+#define TB200_DECODE_STATIC_SCRATCH_BYTES ((size_t)24 << 20)
+
+int tb200_gqa_decode_noalloc(const void* q, const void* k, const void* v, void* o, float* lse,
+                             const int32_t* real_seqlen_kv, int32_t uniform_seqlen,
+                             const int32_t* block_table, int32_t block_table_stride,
+                             const float* k_scale, const float* v_scale,
+                             int q_dtype, int kv_dtype, int o_dtype,
+                             int batch, int heads, int heads_kv, int dim, int page_size,
+                             int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
+                             float sm_scale, float softcap, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Merge R partial attention results over disjoint KV ranges (split-KV across GPUs).
  *   o_parts   [R, rows, dim] fp32, each normalised by its own softmax sum; part r starts at
  *             o_parts + r * o_part_stride floats (0 means packed: rows * dim)

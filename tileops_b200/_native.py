@@ -34,6 +34,15 @@ SIGNATURES = {
         c_int64, c_int64, c_int64,                             # strides
         c_float, c_float,                                      # sm_scale softcap
         c_void_p, c_size_t, c_void_p]),                        # workspace bytes stream
+    "tb200_gqa_decode_noalloc": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_int32, c_void_p, c_int32,
+        c_void_p, c_void_p,
+        c_int, c_int, c_int,
+        c_int, c_int, c_int, c_int, c_int,
+        c_int64, c_int64, c_int64,
+        c_float, c_float,
+        c_void_p]),                                            # stream (no workspace arguments)
     "tb200_gqa_lse_merge": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int,
                                     c_int64, c_int64, c_int, c_void_p]),
     "tb200_gqa_prefill_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),

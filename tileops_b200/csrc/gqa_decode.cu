@@ -677,3 +677,55 @@ extern "C" int tb200_gqa_decode(const void* q, const void* k, const void* v, voi
   return L.nt == 1 ? launch_t<64, 1>(p, q_dtype, kv_dtype, o_dtype, L.grid, s)
                    : launch_t<64, 2>(p, q_dtype, kv_dtype, o_dtype, L.grid, s);
 }
+
+
+// ---- decode for callers that cannot allocate device memory ---------------------------------------
+//
+// Some hosts of this library are not allowed to call cudaMalloc at the point where they decode: a
+// serving runtime that hands every byte of the device to its own pool allocator at start-up and
+// forbids driver allocations afterwards, or a plugin running inside somebody else's framework whose
+// allocator it must not bypass.  For them the split-KV scratch (scheduler counters, merge tickets and
+// fp32 partials) lives in a fixed array inside the library image instead of a caller-provided
+// workspace.  The array costs kDecodeStaticScratchBytes of device memory on every GPU that loads the
+// library, for the life of the process, whether this entry point is used or not.
+constexpr size_t kDecodeStaticScratchBytes = size_t(24) << 20;
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kDecodeStaticScratchBytes];
+
+namespace {
+// Device address of g_decode_static_scratch on each device.  In host code the array's name is only
+// a handle for the runtime, not an address a kernel can use; the real address differs per device
+// and is looked up once, with that device current.
+void* g_scratch_addr[64] = {nullptr};
+}  // namespace
+
+extern "C" int tb200_gqa_decode_noalloc(const void* q, const void* k, const void* v, void* o, float* lse,
+                                        const int32_t* real_seqlen_kv, int32_t uniform_seqlen,
+                                        const int32_t* block_table, int32_t block_table_stride,
+                                        const float* k_scale, const float* v_scale,
+                                        int q_dtype, int kv_dtype, int o_dtype,
+                                        int batch, int heads, int heads_kv, int dim, int page_size,
+                                        int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
+                                        float sm_scale, float softcap, void* stream) {
+  if (batch <= 0 || heads <= 0 || heads_kv <= 0 || dim <= 0 || heads % heads_kv != 0)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "batch, heads, heads_kv and dim must be positive and heads divisible by heads_kv");
+  const Layout L = make_layout(batch, heads, heads_kv, dim, kv_dtype == TB200_E4M3);
+  if (L.total > kDecodeStaticScratchBytes)
+    TB200_FAIL(TB200_ERR_WORKSPACE,
+               "this problem needs %zu bytes of scratch but the built-in scratch holds %zu; use "
+               "tb200_gqa_decode with a caller-provided workspace", L.total, kDecodeStaticScratchBytes);
+  int dev = 0;
+  TB200_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) TB200_FAIL(TB200_ERR_UNSUPPORTED, "device index %d is outside [0, 64)", dev);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* addr = nullptr;
+    TB200_CUDA_CHECK(cudaGetSymbolAddress(&addr, g_decode_static_scratch));
+    g_scratch_addr[dev] = addr;
+  }
+  // The array keeps whatever the previous call left: partials of another shape may sit where this
+  // shape has its counters and tickets, and those must start at zero.
+  TB200_CUDA_CHECK(cudaMemsetAsync(g_scratch_addr[dev], 0, L.counters_bytes, static_cast<cudaStream_t>(stream)));
+  return tb200_gqa_decode(q, k, v, o, lse, real_seqlen_kv, uniform_seqlen, block_table, block_table_stride,
+                          k_scale, v_scale, q_dtype, kv_dtype, o_dtype, batch, heads, heads_kv, dim, page_size,
+                          kv_token_stride, kv_head_stride, kv_batch_stride, sm_scale, softcap,
+                          g_scratch_addr[dev], kDecodeStaticScratchBytes, stream);
+}
