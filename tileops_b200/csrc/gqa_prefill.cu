@@ -9,12 +9,21 @@
 //
 // One CTA = one 128-row Q tile of one (batch, q head); 6 warps:
 //   warps 0-3  softmax / correction / epilogue: thread r owns row r (TMEM lane r), no shuffles
-//   warp  4    TMA producer (one lane): Q once, then K_j, V_j into 2-stage rings
+//   warp  4    TMA producer (one lane): Q once, then K_j and V_j, one buffer each
 //   warp  5    MMA issuer (one lane) and TMEM allocator
-// TMEM (512 columns): S0 [0,128) | S1 [128,256) | O [256,384).  P_j (bf16) overwrites the first
-// 64 columns of S_j and feeds the second MMA straight from TMEM.  The issue order
-// QK_0, QK_1, PV_0, QK_2, PV_1, ... lets the tensor core compute S_{j+1} while the softmax
-// warps work on S_j.
+// TMEM (256 columns per CTA): S [0,128) | O [128,256).  P_j (bf16) overwrites the first 64 columns
+// of S_j and feeds the second MMA straight from TMEM.  A CTA by itself alternates between the
+// tensor core (PV_j, QK_{j+1} back to back) and the softmax warps; TWO CTAs are resident per SM
+// (100 KB of shared memory, 256 TMEM columns and at most 168 registers per thread each), so one
+// CTA's MMAs run under the other's softmax, and prologue/epilogue of one hide under the main
+// loop of the other.  K_{j+1} is fetched while softmax_j runs, V_{j+1} while QK_{j+1} and
+// softmax_{j+1} run, so single buffers do not expose TMA latency.
+//
+// Softmax is two passes over the S tile in TMEM (row max, then exp2 / sum / pack) to keep the
+// register footprint small.  O in TMEM is rescaled only when some row of the warp saw its maximum
+// grow by more than 2^8 since the value it is scaled to; until then the stale maximum is kept
+// (P entries up to 256 are harmless in bf16 and fp32), and the final 1/l normalisation and the
+// LSE use the same stale maximum, so the result is unchanged.
 //
 // Shared memory operands are [128 rows x 64 elements] panels (128-byte rows, 128B swizzle), two
 // panels per 128x128 tile, written by TMA and described to the MMA by 64-bit matrix descriptors:
@@ -32,12 +41,13 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kBN = 128;
 constexpr int kHD = 128;
-constexpr int kStages = 2;
+constexpr int kStages = 1;
 constexpr int kPanelBytes = 128 * 128;       // 128 rows x 128 B
 constexpr int kTileBytes = 2 * kPanelBytes;  // 128 x 128 bf16
 constexpr int kThreads = 192;
-constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256;
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS = 0, kColO = 128;
+constexpr float kRescaleThreshold = 8.f;   // log2 of the growth of the row maximum that forces a rescale
 constexpr long long kWaitCycles = 1000000000LL;  // ~0.5 s at 2 GHz
 
 struct SmemLayout {
@@ -49,7 +59,7 @@ struct SmemLayout {
   static constexpr int total = bars + 256;
 };
 // barrier indices
-enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PREADY = 11, B_ODONE = 13, B_COUNT = 14 };
+enum { B_QFULL = 0, B_KFULL, B_KEMPTY, B_VFULL, B_VEMPTY, B_SFULL, B_PREADY, B_ODONE, B_COUNT };
 
 struct PrefillParams {
   void* o;
@@ -181,8 +191,8 @@ template <typename T>
 __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) { return pack2<T>(lo, hi); }
 
 // ---- kernel --------------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(kThreads, 1)
+template <typename T, bool kSoftcap>
+__global__ void __launch_bounds__(kThreads, 2)
 gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, PrefillParams p) {
   extern __shared__ unsigned char smem_raw[];
@@ -219,14 +229,12 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   if (tid == 0) {
     mbar_init(bar(B_QFULL), 1);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar(B_KFULL + s), 1);
-      mbar_init(bar(B_KEMPTY + s), 1);
-      mbar_init(bar(B_VFULL + s), 1);
-      mbar_init(bar(B_VEMPTY + s), 1);
-      mbar_init(bar(B_SFULL + s), 1);
-      mbar_init(bar(B_PREADY + s), 128);
-    }
+    mbar_init(bar(B_KFULL), 1);
+    mbar_init(bar(B_KEMPTY), 1);
+    mbar_init(bar(B_VFULL), 1);
+    mbar_init(bar(B_VEMPTY), 1);
+    mbar_init(bar(B_SFULL), 1);
+    mbar_init(bar(B_PREADY), 128);
     mbar_init(bar(B_ODONE), 1);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -255,132 +263,120 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tma_load_4d(sbase + SmemLayout::q, &map_q, bar(B_QFULL), 0, h, m0, b);
         tma_load_4d(sbase + SmemLayout::q + kPanelBytes, &map_q, bar(B_QFULL), 64, h, m0, b);
         for (int j = 0; j < n_kv; ++j) {
-          const int s = j % kStages;
-          const uint32_t par = (j / kStages) & 1;
-          if (!mbar_wait(bar(B_KEMPTY + s), par ^ 1, s_abort, p.status, 101)) break;
-          mbar_expect_tx(bar(B_KFULL + s), kTileBytes);
-          const uint32_t kd = sbase + SmemLayout::k + s * kTileBytes;
-          tma_load_4d(kd, &map_k, bar(B_KFULL + s), 0, hk, j * kBN, b);
-          tma_load_4d(kd + kPanelBytes, &map_k, bar(B_KFULL + s), 64, hk, j * kBN, b);
-          if (!mbar_wait(bar(B_VEMPTY + s), par ^ 1, s_abort, p.status, 102)) break;
-          mbar_expect_tx(bar(B_VFULL + s), kTileBytes);
-          const uint32_t vd = sbase + SmemLayout::v + s * kTileBytes;
-          tma_load_4d(vd, &map_v, bar(B_VFULL + s), 0, hk, j * kBN, b);
-          tma_load_4d(vd + kPanelBytes, &map_v, bar(B_VFULL + s), 64, hk, j * kBN, b);
+          const uint32_t par = j & 1;
+          if (!mbar_wait(bar(B_KEMPTY), par ^ 1, s_abort, p.status, 101)) break;
+          mbar_expect_tx(bar(B_KFULL), kTileBytes);
+          const uint32_t kd = sbase + SmemLayout::k;
+          tma_load_4d(kd, &map_k, bar(B_KFULL), 0, hk, j * kBN, b);
+          tma_load_4d(kd + kPanelBytes, &map_k, bar(B_KFULL), 64, hk, j * kBN, b);
+          if (!mbar_wait(bar(B_VEMPTY), par ^ 1, s_abort, p.status, 102)) break;
+          mbar_expect_tx(bar(B_VFULL), kTileBytes);
+          const uint32_t vd = sbase + SmemLayout::v;
+          tma_load_4d(vd, &map_v, bar(B_VFULL), 0, hk, j * kBN, b);
+          tma_load_4d(vd + kPanelBytes, &map_v, bar(B_VFULL), 64, hk, j * kBN, b);
         }
       }
     } else if (warp == 5) {
       // ================= MMA issuer =================
       if (lane == 0) {
         bool ok = mbar_wait(bar(B_QFULL), 0, s_abort, p.status, 201);
-        auto issue_pv = [&](int t) -> bool {
-          const int s = t % kStages;
-          const uint32_t par = (t / kStages) & 1;
-          if (!mbar_wait(bar(B_VFULL + s), par, s_abort, p.status, 203)) return false;
-          if (!mbar_wait(bar(B_PREADY + s), par, s_abort, p.status, 204)) return false;
-          tc_fence_after();
-          const uint32_t vbase = sbase + SmemLayout::v + s * kTileBytes;
-          const uint32_t p_tmem = tmem + (s == 0 ? kColS0 : kColS1);
-#pragma unroll
-          for (int ks = 0; ks < kBN / 16; ++ks) {
-            // B = V: MN-major, 16 tokens per step = 16 rows of 128 B; the two 64-wide d panels
-            // are kPanelBytes apart (leading offset), 8-row groups 1024 B apart (stride offset)
-            const uint64_t bd = make_desc(vbase + ks * 2048, kPanelBytes, 1024);
-            tc_mma_ts(tmem + kColO, p_tmem + ks * 8, bd, idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
-          }
-          tc_commit(bar(B_VEMPTY + s));
-          tc_commit(bar(B_ODONE));
-          return true;
-        };
+        const uint32_t qbase = sbase + SmemLayout::q;
+        const uint32_t kbase = sbase + SmemLayout::k;
+        const uint32_t vbase = sbase + SmemLayout::v;
         for (int j = 0; ok && j < n_kv; ++j) {
-          const int s = j % kStages;
-          const uint32_t par = (j / kStages) & 1;
-          if (!mbar_wait(bar(B_KFULL + s), par, s_abort, p.status, 202)) { ok = false; break; }
+          const uint32_t par = j & 1;
+          if (!mbar_wait(bar(B_KFULL), par, s_abort, p.status, 202)) break;
           tc_fence_after();
-          const uint32_t qbase = sbase + SmemLayout::q;
-          const uint32_t kbase = sbase + SmemLayout::k + s * kTileBytes;
+          // S = Q K^T.  It overwrites P_{j-1}, which PV_{j-1} (issued just before) still reads:
+          // the tensor core executes this thread's MMAs in issue order, so no wait is needed.
 #pragma unroll
           for (int ks = 0; ks < kHD / 16; ++ks) {
             // K-major operands: 16 elements per step = 32 B inside the 128 B swizzled row;
             // after 4 steps move to the second 64-element panel
             const uint32_t o = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
-            tc_mma_ss(tmem + (s == 0 ? kColS0 : kColS1), make_desc(qbase + o, 16, 1024),
-                      make_desc(kbase + o, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+            tc_mma_ss(tmem + kColS, make_desc(qbase + o, 16, 1024), make_desc(kbase + o, 16, 1024), idesc_qk,
+                      ks > 0 ? 1u : 0u);
           }
-          tc_commit(bar(B_SFULL + s));
-          tc_commit(bar(B_KEMPTY + s));
-          if (j >= 1) ok = issue_pv(j - 1);
+          tc_commit(bar(B_SFULL));
+          tc_commit(bar(B_KEMPTY));
+          if (!mbar_wait(bar(B_VFULL), par, s_abort, p.status, 203)) break;
+          if (!mbar_wait(bar(B_PREADY), par, s_abort, p.status, 204)) break;
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < kBN / 16; ++ks) {
+            // B = V: MN-major, 16 tokens per step = 16 rows of 128 B; the two 64-wide d panels
+            // are kPanelBytes apart (leading offset), 8-row groups 1024 B apart (stride offset)
+            const uint64_t bd = make_desc(vbase + ks * 2048, kPanelBytes, 1024);
+            tc_mma_ts(tmem + kColO, tmem + kColS + ks * 8, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          }
+          tc_commit(bar(B_VEMPTY));
+          tc_commit(bar(B_ODONE));
         }
-        if (ok) issue_pv(n_kv - 1);
       }
     } else {
       // ================= softmax / correction / epilogue (thread = row) =================
       const int row = tid;                                  // 0..127 == TMEM lane
       const uint32_t lane_addr = uint32_t(warp * 32) << 16;
       const float cap = p.softcap;
-      const bool use_cap = cap > 0.f;
-      const float c = use_cap ? kLog2e : p.sm_scale * kLog2e;   // multiplies the raw (or capped) score
-      const float pre = use_cap ? p.sm_scale / cap : 0.f;
+      const float c = kSoftcap ? kLog2e : p.sm_scale * kLog2e;   // multiplies the raw (or capped) score
+      const float pre = kSoftcap ? p.sm_scale / cap : 0.f;
       const int q_idx = m0 + row;
       const int key_limit = p.is_causal ? q_idx + off : 0x7fffffff;  // last visible key of this row
-      float m_run = -INFINITY, l_run = 0.f;
+      const uint32_t s_addr = tmem + lane_addr + kColS;
+      const uint32_t o_addr = tmem + lane_addr + kColO;
+      float m_run = -INFINITY, l_run = 0.f;   // m_run: the maximum O and l are currently scaled to
       bool ok = true;
 
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j % kStages;
-        const uint32_t par = (j / kStages) & 1;
-        // the warp leaves the loop together: the TMEM loads below are warp-collective
-        if (!__all_sync(0xffffffffu, mbar_wait(bar(B_SFULL + s), par, s_abort, p.status, 301))) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t s_addr = tmem + lane_addr + (s == 0 ? kColS0 : kColS1);
-        uint32_t sv[4][32];
+      // transform of one loaded chunk: softcap and mask (only on tiles that need it)
+      auto prepare = [&](uint32_t (&r)[32], int key0, bool need_mask) {
+        if (kSoftcap) {
 #pragma unroll
-        for (int cgi = 0; cgi < 4; ++cgi) tc_ld32(s_addr + cgi * 32, sv[cgi]);
-        tc_wait_ld();
-
-        const int k0 = j * kBN;
-        const bool need_mask = (k0 + kBN - 1 > m0 + off && p.is_causal) || (k0 + kBN > p.seqlen_kv);
-        float mx = -INFINITY;
-#pragma unroll
-        for (int cgi = 0; cgi < 4; ++cgi) {
+          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(cap * fast_tanh(__uint_as_float(r[e]) * pre));
+        }
+        if (need_mask) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            float x = __uint_as_float(sv[cgi][e]);
-            if (use_cap) x = cap * fast_tanh(x * pre);
-            if (need_mask) {
-              const int key = k0 + cgi * 32 + e;
-              if (key > key_limit || key >= p.seqlen_kv) x = -INFINITY;
-            }
-            sv[cgi][e] = __float_as_uint(x);
-            mx = fmaxf(mx, x);
+            const int key = key0 + e;
+            if (key > key_limit || key >= p.seqlen_kv) r[e] = 0xff800000u;   // -inf
           }
         }
-        const float m_new = fmaxf(m_run, mx);
-        const float m_use = m_new == -INFINITY ? 0.f : m_new;
-        const float alpha = fast_exp2((m_run - m_use) * c);     // m_run = -inf -> 0
-        const float neg_mc = -m_use * c;
-        float lsum = 0.f;
-#pragma unroll
-        for (int cgi = 0; cgi < 4; ++cgi) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[cgi][2 * e]), c, neg_mc));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[cgi][2 * e + 1]), c, neg_mc));
-            lsum += p0 + p1;
-            pk[e] = pack_pair<T>(p0, p1);
-          }
-          tc_st16(s_addr + cgi * 16, pk);                     // P overwrites S (already in registers)
-        }
-        l_run = l_run * alpha + lsum;
-        m_run = m_new;
+      };
 
-        if (j > 0) {
-          // O holds sum over tiles < j, scaled to the old max: wait for PV_{j-1}, then rescale
-          if (!__all_sync(0xffffffffu, mbar_wait(bar(B_ODONE), (j - 1) & 1, s_abort, p.status, 302))) { ok = false; break; }
-          tc_fence_after();
-          if (__any_sync(0xffffffffu, alpha != 1.f)) {
-            const uint32_t o_addr = tmem + lane_addr + kColO;
+      for (int j = 0; j < n_kv; ++j) {
+        // the warp leaves the loop together: the TMEM loads below are warp-collective
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(B_SFULL), j & 1, s_abort, p.status, 301))) { ok = false; break; }
+        tc_fence_after();
+        const int k0 = j * kBN;
+        const bool need_mask = (p.is_causal && k0 + kBN - 1 > m0 + off) || (k0 + kBN > p.seqlen_kv);
+
+        // ---- pass 1: row maximum ----
+        float mx = -INFINITY;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t ra[32], rb[32];
+          tc_ld32(s_addr + half * 64, ra);
+          tc_ld32(s_addr + half * 64 + 32, rb);
+          tc_wait_ld();
+          prepare(ra, k0 + half * 64, need_mask);
+          prepare(rb, k0 + half * 64 + 32, need_mask);
+          float m0v = mx, m1v = -INFINITY;
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            m0v = max3(m0v, __uint_as_float(ra[e]), __uint_as_float(ra[e + 1]));
+            m1v = max3(m1v, __uint_as_float(rb[e]), __uint_as_float(rb[e + 1]));
+          }
+          mx = fmaxf(m0v, m1v);
+        }
+
+        // ---- decide whether the running maximum moves (and O has to be rescaled) ----
+        const float m_new = fmaxf(m_run, mx);
+        const bool grow = (m_new - m_run) * c > kRescaleThreshold || (m_run == -INFINITY && m_new != -INFINITY);
+        if (__any_sync(0xffffffffu, grow)) {
+          // 1 for a row that still has seen no key (avoids inf - inf), 0 for a row seeing its first
+          const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2((m_run - m_new) * c);
+          l_run *= alpha;
+          if (j > 0) {
+            // S_j is complete, so PV_{j-1} (issued before QK_j) is too: O may be read and written
 #pragma unroll
             for (int cgi = 0; cgi < 4; ++cgi) {
               uint32_t ov[32];
@@ -391,10 +387,34 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
               tc_st32(o_addr + cgi * 32, ov);
             }
           }
+          m_run = m_new;
         }
+        const float neg_mc = (m_run == -INFINITY) ? 0.f : -m_run * c;
+
+        // ---- pass 2: p = 2^(s*c - m*c), row sum, P (16-bit) over the first 64 columns of S ----
+        float lsum0 = 0.f, lsum1 = 0.f;
+#pragma unroll
+        for (int cgi = 0; cgi < 4; ++cgi) {
+          uint32_t r[32];
+          tc_ld32(s_addr + cgi * 32, r);
+          tc_wait_ld();
+          prepare(r, k0 + cgi * 32, need_mask);
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * e]), c, neg_mc));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(r[2 * e + 1]), c, neg_mc));
+            lsum0 += p0;
+            lsum1 += p1;
+            pk[e] = pack_pair<T>(p0, p1);
+          }
+          // P chunk cgi lands in columns [16 cgi, 16 cgi + 16): inside S chunks already consumed
+          tc_st16(s_addr + cgi * 16, pk);
+        }
+        l_run += lsum0 + lsum1;
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(bar(B_PREADY + s));
+        mbar_arrive(bar(B_PREADY));
       }
 
       // ---- epilogue: O / l -> global, LSE ----
@@ -403,7 +423,6 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       if (ok) {
         tc_fence_after();
         const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-        const uint32_t o_addr = tmem + lane_addr + kColO;
         T* orow = reinterpret_cast<T*>(p.o) + ((size_t(b) * p.seqlen_q + q_idx) * p.heads + h) * kHD;
 #pragma unroll
         for (int cgi = 0; cgi < 4; ++cgi) {
@@ -486,10 +505,10 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int batch, int seq, 
   return TB200_OK;
 }
 
-template <typename T>
+template <typename T, bool kSoftcap>
 int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p,
                    cudaStream_t stream) {
-  auto kern = gqa_prefill_kernel<T>;
+  auto kern = gqa_prefill_kernel<T, kSoftcap>;
   const int smem = SmemLayout::total + 1024;
   TB200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int n_m = (p.seqlen_q + kBM - 1) / kBM;
@@ -539,6 +558,9 @@ extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, vo
   p.batch = batch; p.heads = heads; p.heads_kv = heads_kv; p.seqlen_q = seqlen_q; p.seqlen_kv = seqlen_kv;
   p.is_causal = is_causal; p.sm_scale = sm_scale; p.softcap = softcap;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return dtype == TB200_BF16 ? launch_prefill<__nv_bfloat16>(mq, mk, mv, p, s)
-                             : launch_prefill<__half>(mq, mk, mv, p, s);
+  if (softcap > 0.f)
+    return dtype == TB200_BF16 ? launch_prefill<__nv_bfloat16, true>(mq, mk, mv, p, s)
+                               : launch_prefill<__half, true>(mq, mk, mv, p, s);
+  return dtype == TB200_BF16 ? launch_prefill<__nv_bfloat16, false>(mq, mk, mv, p, s)
+                             : launch_prefill<__half, false>(mq, mk, mv, p, s);
 }

@@ -102,12 +102,17 @@ __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(y) : "f"(a), "f"(b), "f"(c));
   return y;
 }
 __device__ __forceinline__ float fast_tanh(float x) {
   float y;
-  asm volatile("tanh.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  asm("tanh.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
 
