@@ -11,7 +11,9 @@ from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_
 
 import torch
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_lib", "libtileops_b200.so")
+#: ``TB200_LIBRARY`` points at another build of the same library (comparing kernel variants)
+_LIB_PATH = os.environ.get("TB200_LIBRARY") or os.path.join(
+    os.path.dirname(os.path.abspath(__file__)), "_lib", "libtileops_b200.so")
 
 OK = 0
 F16, BF16, E4M3, F32 = 0, 1, 2, 3

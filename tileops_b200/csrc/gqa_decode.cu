@@ -19,6 +19,8 @@
 //     per-(page, KV head) scales are applied to the fp32 scores (K) and to P (V);
 //   * partial (O, max, sum) of an item go to a workspace in fp32; the CTA that finishes a
 //     (sequence, KV head) last merges them (atomic ticket, nobody waits).
+#include <stdlib.h>
+
 #include "tb200_common.cuh"
 
 namespace tb200 {
@@ -28,7 +30,19 @@ constexpr int kTile = 64;          // tokens per shared-memory tile
 constexpr int kThreads = 128;      // 4 warps x 16 tokens
 constexpr int kWarps = 4;
 constexpr int kMinChunkTiles = 2;  // never cut a sequence into runs shorter than this
-constexpr int kItemsPerCta = 8;    // target number of work items per resident CTA
+#ifndef TB200_DEC_ITEMS_PER_CTA
+#define TB200_DEC_ITEMS_PER_CTA 8
+#endif
+#ifndef TB200_DEC_DEFER
+#define TB200_DEC_DEFER 1
+#endif
+#ifndef TB200_DEC_STAGES16
+#define TB200_DEC_STAGES16 3
+#endif
+#ifndef TB200_DEC_BLOCKS16
+#define TB200_DEC_BLOCKS16 2
+#endif
+constexpr int kItemsPerCta = TB200_DEC_ITEMS_PER_CTA;  // target number of work items per resident CTA
 constexpr int kMaxBatch = 4096;
 
 struct DecodeParams {
@@ -53,6 +67,7 @@ struct DecodeParams {
   int q_is_bf16;
   int target_items;
   int max_items;
+  int force_chunk;  // > 0: run length in tiles (debug switch TB200_DECODE_CHUNK_TILES)
   int* counters;   // [0] next item, [1] CTAs done, [2 + (b*heads_kv + hk)*n_hb + hb] tickets
   float* part_o;   // [max_items][hb][D]
   float* part_ml;  // [max_items][hb][2]
@@ -66,8 +81,8 @@ struct Cfg {
   static constexpr int kChunksPerRow = kRowBytes / 16;
   static constexpr int kTileBytes = kTile * kRowStride;
   static constexpr int kStageBytes = 2 * kTileBytes + (FP8 ? 2 * kTile * 4 : 0);
-  static constexpr int kStages = FP8 ? 4 : 3;
-  static constexpr int kMinBlocks = FP8 ? 3 : 2;
+  static constexpr int kStages = FP8 ? 4 : TB200_DEC_STAGES16;
+  static constexpr int kMinBlocks = FP8 ? 3 : TB200_DEC_BLOCKS16;
   static constexpr int kOStride = D + 4;  // fp32 words per head in the cross-warp merge area
 };
 
@@ -77,7 +92,7 @@ size_t smem_bytes(int batch, int nt) {
   size_t ring = size_t(C::kStages) * C::kStageBytes;
   size_t merge = size_t(kWarps) * (8 * nt) * (C::kOStride + 2) * 4;
   size_t a = ring > merge ? ring : merge;
-  return a + size_t(batch + 1) * 4 + 64;
+  return a + size_t(batch + 1) * 4 + 128;
 }
 
 __device__ __forceinline__ float apply_softcap(float x, float cap, float inv_cap) {
@@ -103,25 +118,91 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
   constexpr size_t kMerge = size_t(kWarps) * (8 * NT) * (C::kOStride + 2) * 4;
   constexpr size_t kArea = kRing > kMerge ? kRing : kMerge;
   int* s_prefix = reinterpret_cast<int*>(smem + kArea);  // [batch + 1] run counts, exclusive scan
-  int* s_misc = s_prefix + p.batch + 1;                   // [0] item, [1] ticket, [2..5] scratch
+  int* s_misc = s_prefix + p.batch + 1;                   // [1] ticket, [2..5] plan scratch, [6],[7] item ids
 
   const int lanes_per_run = p.heads_kv * p.n_hb;
 
   // ---- plan: cut every sequence into runs of tiles (identical in every CTA) -------------
+  // The run length is chosen from a short list by a cost model in units of one tile's time:
+  //   cost(c) = max(W/P, largest run if there are fewer runs than CTAs)
+  //           + (items per CTA) * kItemCost + (split items per CTA) * kSplitCost
+  //           + half a run of tail imbalance when CTAs take more than one item
+  // (W = all tiles, P = CTAs).  Short runs balance ragged batches; long runs avoid the refill of
+  // the load pipeline, the partial results and the merge; an unsplit sequence costs least per
+  // item.  Integer sums and maxima are reduced with order-independent atomics, so every CTA
+  // arrives at the same plan.
   {
-    int local = 0;
+    constexpr int kCand = 16;
+    constexpr float kItemCost = 2.f, kSplitCost = 3.f;
+    int* s_cand = reinterpret_cast<int*>(smem);   // [kCand][3]: items, split items, largest run (ring not in use yet)
+    int* s_tot = s_cand + kCand * 3;              // [2]: all tiles, longest sequence in tiles
+    if (tid < kCand * 3 + 2) s_cand[tid] = 0;
+    __syncthreads();
+    int local = 0, local_max = 0;
     for (int b = tid; b < p.batch; b += kThreads) {
-      int len = p.lens ? p.lens[b] : p.uniform_len;
-      local += (max(len, 0) + kTile - 1) / kTile;
+      const int len = p.lens ? p.lens[b] : p.uniform_len;
+      const int t = (max(len, 0) + kTile - 1) / kTile;
+      local += t;
+      local_max = max(local_max, t);
+    }
+    local = __reduce_add_sync(0xffffffffu, local);
+    local_max = __reduce_max_sync(0xffffffffu, local_max);
+    if (lane == 0) { atomicAdd(&s_tot[0], local); atomicMax(&s_tot[1], local_max); }
+    __syncthreads();
+    const long long total_tiles = s_tot[0];
+    const int max_tiles = max(s_tot[1], 1);
+    // the workspace holds batch*lanes + target_items partials: never cut finer than this
+    const int c_min = (int)max((long long)kMinChunkTiles,
+                               (total_tiles * lanes_per_run + p.target_items - 1) / p.target_items);
+    auto cand = [&](int i) {
+      // 8, 12, 16, 24, 32, 48, ... , 1024, then "do not split"
+      const int c = i == kCand - 1 ? max_tiles : ((i & 1) ? 12 : 8) << (i >> 1);
+      return min(max(c, c_min), max(max_tiles, c_min));
+    };
+    int it_[kCand], sp_[kCand], mx_[kCand];
+#pragma unroll
+    for (int i = 0; i < kCand; ++i) { it_[i] = 0; sp_[i] = 0; mx_[i] = 0; }
+    for (int b = tid; b < p.batch; b += kThreads) {
+      const int len = p.lens ? p.lens[b] : p.uniform_len;
+      const int t = (max(len, 0) + kTile - 1) / kTile;
+#pragma unroll
+      for (int i = 0; i < kCand; ++i) {
+        const int c = cand(i);
+        const int n = max(1, (t + c - 1) / c);
+        it_[i] += n;
+        sp_[i] += n > 1 ? n : 0;
+        mx_[i] = max(mx_[i], (t + n - 1) / n);
+      }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-    if (lane == 0) s_misc[2 + warp] = local;
+    for (int i = 0; i < kCand; ++i) {
+      const int a0 = __reduce_add_sync(0xffffffffu, it_[i]);
+      const int a1 = __reduce_add_sync(0xffffffffu, sp_[i]);
+      const int a2 = __reduce_max_sync(0xffffffffu, mx_[i]);
+      if (lane == 0) {
+        atomicAdd(&s_cand[i * 3], a0);
+        atomicAdd(&s_cand[i * 3 + 1], a1);
+        atomicMax(&s_cand[i * 3 + 2], a2);
+      }
+    }
     __syncthreads();
-    const long long total_tiles = (long long)s_misc[2] + s_misc[3] + s_misc[4] + s_misc[5];
-    long long want = (total_tiles * lanes_per_run + p.target_items - 1) / p.target_items;
-    const int chunk = (int)max((long long)kMinChunkTiles, want);
-    __syncthreads();
+    int chunk = cand(kCand - 1);
+    if (p.force_chunk > 0) {
+      chunk = max(p.force_chunk, c_min);
+    } else {
+      const float P = float(gridDim.x);
+      const float w_per_cta = float(total_tiles) * lanes_per_run / P;
+      float best = 3.0e38f;
+      for (int i = 0; i < kCand; ++i) {
+        const float k = float(s_cand[i * 3]) * lanes_per_run / P;
+        const float ks = float(s_cand[i * 3 + 1]) * lanes_per_run / P;
+        const float big = float(s_cand[i * 3 + 2]);
+        const float cost = fmaxf(w_per_cta, k <= 1.f ? big : 0.f) + k * kItemCost + ks * kSplitCost +
+                           (k > 1.f ? 0.5f * big : 0.f);
+        if (cost <= best) { best = cost; chunk = cand(i); }   // ties go to the longer run
+      }
+    }
+    __syncthreads();   // s_cand lives in the ring
 
     const int per = (p.batch + kThreads - 1) / kThreads;
     const int b0 = tid * per;
@@ -173,11 +254,82 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
   const uint32_t k_lane_off = (warp * 16 + ld_row_a) * C::kRowStride + ld_col_a * 16;
   const uint32_t v_lane_off = C::kTileBytes + (warp * 16 + ld_row_v) * C::kRowStride + ld_col_v * 16;
 
-  while (true) {
-    __syncthreads();  // previous item's use of the ring / merge area and s_misc is over
-    if (tid == 0) s_misc[0] = atomicAdd(&p.counters[0], 1);
+  // ---- split-KV merge, deferred -----------------------------------------------------------
+  // A finished run leaves its partial (O, max, sum) in the workspace.  Whoever finishes a
+  // (sequence, KV head, head block) last merges all of its runs: thread 0 publishes this CTA's
+  // partial (the CTA barrier hands every thread's stores to thread 0, whose release is cumulative
+  // and makes them visible device-wide) and takes a ticket.  The atomic costs a round trip to L2,
+  // so it runs when the NEXT item's first tiles are already in flight.
+  struct Pending {
+    bool valid;
+    int* ticket;
+    int n_runs, first_item, b, head0, n_heads;
+  } pend{false, nullptr, 0, 0, 0, 0, 0};
+  auto resolve_pending = [&]() {
+    if (!pend.valid) return;           // uniform across the CTA
+    pend.valid = false;
+    if (tid == 0) {
+      // release (publishes the partial) + acquire (sees the other runs' partials) in one
+      // device-scope atomic; a sequentially consistent __threadfence() would also wait for this
+      // thread's loads in flight
+      int t;
+      asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(t) : "l"(pend.ticket) : "memory");
+      s_misc[1] = t;
+    }
     __syncthreads();
-    const int item = s_misc[0];
+    if (s_misc[1] != pend.n_runs - 1) return;
+    // One pass over the runs with a running maximum.  Each thread owns kOut outputs and issues
+    // the loads of a run for all of them before using any, so a merge costs about one memory
+    // round trip per run instead of one per run and output.
+    TO* out = reinterpret_cast<TO*>(p.o);
+    constexpr int kOut = (8 * NT * D) / kThreads;
+    float acc[kOut], L[kOut], M[kOut];
+#pragma unroll
+    for (int k = 0; k < kOut; ++k) { acc[k] = 0.f; L[k] = 0.f; M[k] = kNegFloor; }
+    const int n_out = pend.n_heads * D;
+#pragma unroll 2
+    for (int r = 0; r < pend.n_runs; ++r) {
+      const size_t it2 = size_t(pend.first_item) + size_t(r) * lanes_per_run;
+      const float* ml = p.part_ml + it2 * p.hb * 2;
+      const float* po2 = p.part_o + it2 * p.hb * D;
+      float mt[kOut], lt[kOut], ot[kOut];
+#pragma unroll
+      for (int k = 0; k < kOut; ++k) {
+        const int idx = tid + k * kThreads;
+        const bool ok = idx < n_out;
+        const int hn = ok ? idx / D : 0;
+        mt[k] = ok ? __ldcg(ml + hn * 2) : kNegFloor;
+        lt[k] = ok ? __ldcg(ml + hn * 2 + 1) : 0.f;
+        ot[k] = ok ? __ldcg(po2 + idx) : 0.f;     // part_o row is [hn][d] = idx
+      }
+#pragma unroll
+      for (int k = 0; k < kOut; ++k) {
+        const float mn = fmaxf(M[k], mt[k]);
+        const float ea = fast_exp2(M[k] - mn), eb = fast_exp2(mt[k] - mn);
+        acc[k] = acc[k] * ea + ot[k] * eb;
+        L[k] = L[k] * ea + lt[k] * eb;
+        M[k] = mn;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kOut; ++k) {
+      const int idx = tid + k * kThreads;
+      if (idx < n_out) {
+        const int hn = idx / D, d = idx - hn * D;
+        store_out<TO>(out + (size_t(pend.b) * p.heads + pend.head0 + hn) * D + d, L[k] > 0.f ? acc[k] / L[k] : 0.f);
+        if (d == 0 && p.lse)
+          p.lse[size_t(pend.b) * p.heads + pend.head0 + hn] = L[k] > 0.f ? M[k] + log2f(L[k]) : -INFINITY;
+      }
+    }
+    if (tid == 0) *pend.ticket = 0;  // leave the workspace zeroed for the next launch
+  };
+
+  // Item ids are fetched one item ahead (two alternating slots), so the round trip of the
+  // atomic is hidden behind the loads of the current item instead of sitting between two items.
+  if (tid == 0) s_misc[6] = atomicAdd(&p.counters[0], 1);
+  for (int round = 0;; ++round) {
+    __syncthreads();  // previous item's use of the ring / merge area is over; next id is visible
+    const int item = s_misc[6 + (round & 1)];
     if (item >= total_items) break;
 
     // ---- decode the item ------------------------------------------------------------
@@ -315,6 +467,10 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
       if (s < n_tiles) issue_tile(tile0 + s, s);
       cp_async_commit();
     }
+    if (tid == 0) s_misc[6 + ((round + 1) & 1)] = atomicAdd(&p.counters[0], 1);  // id of the next item
+#if TB200_DEC_DEFER
+    resolve_pending();  // ticket / merge of the previous item, under this item's first loads
+#endif
 
     for (int it = 0; it < n_tiles; ++it) {
       cp_async_wait<C::kStages - 2>();
@@ -495,35 +651,21 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
         if (d == 0) { pml[hn * 2] = M; pml[hn * 2 + 1] = L; }
       }
     }
-    if (single) continue;
-
-    // ---- split-KV: whoever finishes this (sequence, KV head, head block) last merges ----
-    __threadfence();
-    __syncthreads();
-    int* ticket = p.counters + 2 + (size_t(b) * p.heads_kv + hk) * p.n_hb + hbi;
-    if (tid == 0) s_misc[1] = atomicAdd(ticket, 1);
-    __syncthreads();
-    if (s_misc[1] != n_runs - 1) continue;
-    __threadfence();
-    const int first_item = s_prefix[b] * lanes_per_run + rem;
-    for (int idx = tid; idx < n_heads * D; idx += kThreads) {
-      const int hn = idx / D, d = idx - hn * D;
-      float M = kNegFloor;
-      for (int r = 0; r < n_runs; ++r)
-        M = fmaxf(M, __ldcg(p.part_ml + (size_t(first_item) + size_t(r) * lanes_per_run) * p.hb * 2 + hn * 2));
-      float acc = 0.f, L = 0.f;
-      for (int r = 0; r < n_runs; ++r) {
-        const size_t it2 = size_t(first_item) + size_t(r) * lanes_per_run;
-        const float* ml = p.part_ml + it2 * p.hb * 2 + hn * 2;
-        const float e = fast_exp2(__ldcg(ml) - M);
-        acc += e * __ldcg(p.part_o + it2 * p.hb * D + hn * D + d);
-        L += e * __ldcg(ml + 1);
-      }
-      store_out<TO>(out + (size_t(b) * p.heads + head0 + hn) * D + d, L > 0.f ? acc / L : 0.f);
-      if (d == 0 && p.lse) p.lse[size_t(b) * p.heads + head0 + hn] = L > 0.f ? M + log2f(L) : -INFINITY;
+    if (!single) {
+      // the ticket for this (sequence, KV head, head block) is taken at the start of the next
+      // item, after that item's first loads are in flight
+      pend.valid = true;
+      pend.ticket = p.counters + 2 + (size_t(b) * p.heads_kv + hk) * p.n_hb + hbi;
+      pend.n_runs = n_runs;
+      pend.first_item = s_prefix[b] * lanes_per_run + rem;
+      pend.b = b; pend.head0 = head0; pend.n_heads = n_heads;
     }
-    if (tid == 0) *ticket = 0;  // leave the workspace zeroed for the next launch
+#if !TB200_DEC_DEFER
+    __syncthreads();
+    resolve_pending();
+#endif
   }
+  resolve_pending();
 
   // ---- the last CTA to leave resets the scheduler counters ------------------------------
   if (tid == 0) {
@@ -550,7 +692,7 @@ Layout make_layout(int batch, int heads, int heads_kv, int dim, bool fp8) {
   L.hb = group < 16 ? group : 16;
   L.nt = L.hb <= 8 ? 1 : 2;
   L.n_hb = (group + L.hb - 1) / L.hb;
-  const int blocks_per_sm = fp8 ? 3 : 2;
+  const int blocks_per_sm = fp8 ? 3 : TB200_DEC_BLOCKS16;
   L.grid = sm_count() * blocks_per_sm;
   L.target_items = sm_count() * 3 * kItemsPerCta;  // independent of the cache dtype
   L.max_items = batch * heads_kv * L.n_hb + L.target_items;
@@ -665,6 +807,10 @@ extern "C" int tb200_gqa_decode(const void* q, const void* k, const void* v, voi
   p.sm_scale = sm_scale; p.softcap = softcap;
   p.q_is_bf16 = q_dtype == TB200_BF16;
   p.target_items = L.target_items; p.max_items = L.max_items;
+  {
+    const char* e = getenv("TB200_DECODE_CHUNK_TILES");
+    p.force_chunk = e ? atoi(e) : 0;
+  }
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   p.counters = reinterpret_cast<int*>(ws);
   p.part_o = reinterpret_cast<float*>(ws + L.counters_bytes);
