@@ -101,7 +101,13 @@ __device__ __forceinline__ float apply_softcap(float x, float cap, float inv_cap
 
 // T  : MMA element type (bf16 or f16).  For FP8 caches T is f16 and q is converted.
 // TO : output element type.
-template <int D, bool FP8, typename T, int NT, typename TO>
+// F8M: FP8 cache consumed by e4m3 tensor-core MMAs (m16n8k32) with no expansion at all.  K and V
+//      bytes go from ldmatrix straight into the MMA; q and P, which are not e4m3 numbers, enter as
+//      the sum of two e4m3 numbers (hi + lo, about 8 significant bits, what bf16 carries), so
+//      S^T = K q_hi^T + K q_lo^T (two MMAs per 32 dims) and O^T += [V^T V^T] [P_hi; P_lo] (hi and
+//      lo stacked on the k axis of one MMA).  Needs one scale per tile and tensor: tiles that lie
+//      inside one page (page_size a multiple of 64); other layouts use the f16 expansion path.
+template <int D, bool FP8, typename T, int NT, typename TO, bool F8M = false>
 __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_kernel(DecodeParams p) {
   using C = Cfg<D, FP8>;
   constexpr int kKSteps = D / 16;  // MMAs per 16 tokens for S^T, and m-tiles of O^T
@@ -356,11 +362,45 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
 
     // ---- q fragments (B operand of S^T = K Q^T) ---------------------------------------
     uint32_t qf[NT][kKSteps][2];
+    float q_unscale[NT][2] = {};   // F8M: 1 / (scale q was multiplied by), for heads 2*t4, 2*t4+1
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int hn = nt * 8 + g8;
       const bool ok = hn < n_heads;
       const size_t qoff = (size_t(b) * p.heads + head0 + (ok ? hn : 0)) * D;
+      if constexpr (F8M) {
+        // B fragment of m16n8k32: b0 = dims 32j+4t..+3, b1 = dims 32j+16+4t..+3 of head g8.
+        // qf[nt][2j][0/1] = hi bytes of (b0, b1), qf[nt][2j+1][0/1] = lo bytes.
+        float f[D / 32][8];
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < D / 32; ++j)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int d = j * 32 + (e >> 2) * 16 + t4 * 4 + (e & 3);
+            float x = 0.f;
+            if (ok) x = p.q_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.q)[qoff + d])
+                                    : __half2float(reinterpret_cast<const __half*>(p.q)[qoff + d]);
+            f[j][e] = x;
+            amax = fmaxf(amax, fabsf(x));
+          }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const float sq = 384.f / fmaxf(amax, 1e-20f);      // head g8: |q * sq| <= 384 < 448
+        const float inv = 1.f / sq;
+        q_unscale[nt][0] = __shfl_sync(0xffffffffu, inv, (2 * t4) * 4);
+        q_unscale[nt][1] = __shfl_sync(0xffffffffu, inv, (2 * t4 + 1) * 4);
+#pragma unroll
+        for (int j = 0; j < D / 32; ++j) {
+          uint32_t h[4], l[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) split_e4m3x2(f[j][2 * e] * sq, f[j][2 * e + 1] * sq, h[e], l[e]);
+          qf[nt][2 * j][0] = h[0] | (h[1] << 16);
+          qf[nt][2 * j][1] = h[2] | (h[3] << 16);
+          qf[nt][2 * j + 1][0] = l[0] | (l[1] << 16);
+          qf[nt][2 * j + 1][1] = l[2] | (l[3] << 16);
+        }
+      } else
 #pragma unroll
       for (int ks = 0; ks < kKSteps; ++ks) {
         if constexpr (!FP8) {
@@ -452,6 +492,7 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
     // ---- running state ----------------------------------------------------------------
     float oacc[NT][kKSteps][4];
     float m_run[NT][2], l_run[NT][2];
+    float v_unit = 1.f;   // F8M: V scale that oacc is currently expressed in
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       m_run[nt][0] = m_run[nt][1] = kNegFloor;
@@ -485,11 +526,12 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
       const int tok_a = (tile0 + it) * kTile + warp * 16 + g8;  // token of c0/c1; c2/c3 is +8
 
       // ---- S^T = K Q^T  (16 tokens x 8*NT heads per warp) ---------------------------
-      float sacc[NT][4];
+      // two accumulators per score tile (even / odd k-steps) halve the dependent MMA chain
+      float sacc[NT][4], sacc2[NT][4];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) sacc[nt][e] = 0.f;
+        for (int e = 0; e < 4; ++e) { sacc[nt][e] = 0.f; sacc2[nt][e] = 0.f; }
 
       if constexpr (!FP8) {
 #pragma unroll
@@ -497,7 +539,19 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
           uint32_t a[4];
           ldmatrix_x4(a, st_base + k_lane_off + ks * 32);
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) mma_16816<T>(sacc[nt], a, qf[nt][ks]);
+          for (int nt = 0; nt < NT; ++nt) mma_16816<T>((ks & 1) ? sacc2[nt] : sacc[nt], a, qf[nt][ks]);
+        }
+      } else if constexpr (F8M) {
+#pragma unroll
+        for (int jj = 0; jj < D / 32; ++jj) {
+          // the four 8x16-byte blocks are exactly the A fragment of m16n8k32 (16 tokens x 32 dims)
+          uint32_t r[4];
+          ldmatrix_x4(r, st_base + k_lane_off + jj * 32);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            mma_16832_e4m3(sacc[nt], r, qf[nt][2 * jj]);       // K q_hi^T
+            mma_16832_e4m3(sacc2[nt], r, qf[nt][2 * jj + 1]);  // K q_lo^T
+          }
         }
       } else {
 #pragma unroll
@@ -511,7 +565,7 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             mma_16816<T>(sacc[nt], a0, qf[nt][2 * jj]);
-            mma_16816<T>(sacc[nt], a1, qf[nt][2 * jj + 1]);
+            mma_16816<T>(sacc2[nt], a1, qf[nt][2 * jj + 1]);
           }
         }
       }
@@ -519,20 +573,35 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
       // ---- scale, softcap, mask, online softmax ----------------------------------------
       float sc_lo = qk_scale, sc_hi = qk_scale;  // per-token score scale (rows g8 and g8+8)
       float vs_lo = 1.f, vs_hi = 1.f;
+      float unit_fix = 1.f;   // F8M: factor that moves O from the previous tile's V scale to this one's
       if constexpr (FP8) {
         const float* s_ks = reinterpret_cast<const float*>(ring + stage * C::kStageBytes + 2 * C::kTileBytes);
         const float* s_vs = s_ks + kTile;
-        sc_lo *= s_ks[warp * 16 + g8] * 256.f;
-        sc_hi *= s_ks[warp * 16 + g8 + 8] * 256.f;
-        vs_lo = s_vs[warp * 16 + g8] * 256.f;
-        vs_hi = s_vs[warp * 16 + g8 + 8] * 256.f;
+        if constexpr (F8M) {
+          sc_lo *= s_ks[warp * 16 + g8];
+          sc_hi *= s_ks[warp * 16 + g8 + 8];
+          // O is kept in units of the current tile's V scale (one scale per tile: the tile lies in
+          // one page); a slice with no live token (scale loaded as 0) leaves the unit alone
+          const float vs = s_vs[warp * 16];
+          if (vs > 0.f) { unit_fix = v_unit / vs; v_unit = vs; }
+          vs_lo = vs_hi = 256.f;    // P enters the MMA as p * 256 <= 256 (e4m3 holds up to 448)
+        } else {
+          sc_lo *= s_ks[warp * 16 + g8] * kE4m3Unit;
+          sc_hi *= s_ks[warp * 16 + g8 + 8] * kE4m3Unit;
+          vs_lo = s_vs[warp * 16 + g8] * kE4m3Unit;
+          vs_hi = s_vs[warp * 16 + g8 + 8] * kE4m3Unit;
+        }
       }
       const bool ok_lo = tok_a < len, ok_hi = tok_a + 8 < len;
       uint32_t pb[NT][2];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        float s0 = sacc[nt][0] * sc_lo, s1 = sacc[nt][1] * sc_lo;
-        float s2 = sacc[nt][2] * sc_hi, s3 = sacc[nt][3] * sc_hi;
+        float s0 = (sacc[nt][0] + sacc2[nt][0]) * sc_lo, s1 = (sacc[nt][1] + sacc2[nt][1]) * sc_lo;
+        float s2 = (sacc[nt][2] + sacc2[nt][2]) * sc_hi, s3 = (sacc[nt][3] + sacc2[nt][3]) * sc_hi;
+        if constexpr (F8M) {
+          s0 *= q_unscale[nt][0]; s1 *= q_unscale[nt][1];
+          s2 *= q_unscale[nt][0]; s3 *= q_unscale[nt][1];
+        }
         if (p.softcap > 0.f) {
           s0 = apply_softcap(s0, p.softcap, inv_cap) * kLog2e;
           s1 = apply_softcap(s1, p.softcap, inv_cap) * kLog2e;
@@ -549,6 +618,7 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
         }
         const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);
         const float al0 = fast_exp2(m_run[nt][0] - mn0), al1 = fast_exp2(m_run[nt][1] - mn1);
+        const float oa0 = F8M ? al0 * unit_fix : al0, oa1 = F8M ? al1 * unit_fix : al1;
         m_run[nt][0] = mn0; m_run[nt][1] = mn1;
         const float p0 = fast_exp2(s0 - mn0), p1 = fast_exp2(s1 - mn1);
         const float p2 = fast_exp2(s2 - mn0), p3 = fast_exp2(s3 - mn1);
@@ -556,12 +626,30 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
         l_run[nt][1] = l_run[nt][1] * al1 + p1 + p3;
 #pragma unroll
         for (int mt = 0; mt < kKSteps; ++mt) {
-          oacc[nt][mt][0] *= al0; oacc[nt][mt][1] *= al1;
-          oacc[nt][mt][2] *= al0; oacc[nt][mt][3] *= al1;
+          oacc[nt][mt][0] *= oa0; oacc[nt][mt][1] *= oa1;
+          oacc[nt][mt][2] *= oa0; oacc[nt][mt][3] *= oa1;
         }
-        // P^T as the B operand: transpose the two 8x8 (token x head) blocks across the warp
-        pb[nt][0] = movmatrix_trans(pack2<T>(p0 * vs_lo, p1 * vs_lo));
-        pb[nt][1] = movmatrix_trans(pack2<T>(p2 * vs_hi, p3 * vs_hi));
+        if constexpr (F8M) {
+          // B fragment of m16n8k32: b0 = P_hi, b1 = P_lo of head g8 for the four tokens
+          // (2t, 2t+1, 8+2t, 9+2t), the order in which the V fragment below lists its tokens.
+          // x: byte pairs (head 2t, 2t+1) of token g8 (low half) and token g8+8 (high half);
+          // after the 8x8 transpose an even-g8 lane holds tokens 2t, 2t+1 and its odd neighbour
+          // tokens 8+2t, 9+2t, both for the head pair g8>>1; one exchange completes each lane.
+          uint32_t h01, l01, h23, l23;
+          split_e4m3x2(p0 * vs_lo, p1 * vs_lo, h01, l01);
+          split_e4m3x2(p2 * vs_hi, p3 * vs_hi, h23, l23);
+          const uint32_t xh = movmatrix_trans(h01 | (h23 << 16));
+          const uint32_t xl = movmatrix_trans(l01 | (l23 << 16));
+          const uint32_t yh = __shfl_xor_sync(0xffffffffu, xh, 4);
+          const uint32_t yl = __shfl_xor_sync(0xffffffffu, xl, 4);
+          const bool odd = g8 & 1;
+          pb[nt][0] = odd ? prmt(yh, xh, 0x7531) : prmt(xh, yh, 0x6420);
+          pb[nt][1] = odd ? prmt(yl, xl, 0x7531) : prmt(xl, yl, 0x6420);
+        } else {
+          // P^T as the B operand: transpose the two 8x8 (token x head) blocks across the warp
+          pb[nt][0] = movmatrix_trans(pack2<T>(p0 * vs_lo, p1 * vs_lo));
+          pb[nt][1] = movmatrix_trans(pack2<T>(p2 * vs_hi, p3 * vs_hi));
+        }
       }
 
       // ---- O^T += V^T P^T ------------------------------------------------------------------
@@ -572,6 +660,24 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
           ldmatrix_x4_trans(a, st_base + v_lane_off + mt * 32);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) mma_16816<T>(oacc[nt][mt], a, pb[nt]);
+        }
+      } else if constexpr (F8M) {
+#pragma unroll
+        for (int ii = 0; ii < D / 32; ++ii) {
+          // r[0], r[1]: tokens 0-7, 8-15 at dims 32ii..+15; r[2], r[3]: the same tokens, next 16 dims.
+          // Each register is 2 tokens x 2 dims: bytes (0,2) dim 2*g8, bytes (1,3) dim 2*g8+1.
+          uint32_t r[4];
+          ldmatrix_x4_trans(r, st_base + v_lane_off + ii * 32);
+          uint32_t a0[4], a1[4];
+          a0[0] = prmt(r[0], r[1], 0x6420); a0[1] = prmt(r[0], r[1], 0x7531);
+          a1[0] = prmt(r[2], r[3], 0x6420); a1[1] = prmt(r[2], r[3], 0x7531);
+          a0[2] = a0[0]; a0[3] = a0[1];     // k slots 16..31 repeat the 16 tokens: they meet P_lo
+          a1[2] = a1[0]; a1[3] = a1[1];
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            mma_16832_e4m3(oacc[nt][2 * ii], a0, pb[nt]);
+            mma_16832_e4m3(oacc[nt][2 * ii + 1], a1, pb[nt]);
+          }
         }
       } else {
 #pragma unroll
@@ -618,8 +724,9 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
         // ldmatrix on byte pairs interleaves them: rows g8, g8+8 are dims 2*g8, 2*g8+1
         const int d_lo = FP8 ? mt * 16 + 2 * g8 : mt * 16 + g8;
         const int d_hi = FP8 ? d_lo + 1 : d_lo + 8;
-        so0[d_lo] = oacc[nt][mt][0]; so1[d_lo] = oacc[nt][mt][1];
-        so0[d_hi] = oacc[nt][mt][2]; so1[d_hi] = oacc[nt][mt][3];
+        const float of = F8M ? v_unit * (1.f / 256.f) : 1.f;
+        so0[d_lo] = oacc[nt][mt][0] * of; so1[d_lo] = oacc[nt][mt][1] * of;
+        so0[d_hi] = oacc[nt][mt][2] * of; so1[d_hi] = oacc[nt][mt][3] * of;
       }
     }
     __syncthreads();
@@ -704,9 +811,9 @@ Layout make_layout(int batch, int heads, int heads_kv, int dim, bool fp8) {
   return L;
 }
 
-template <int D, bool FP8, typename T, int NT, typename TO>
+template <int D, bool FP8, typename T, int NT, typename TO, bool F8M = false>
 int launch(const DecodeParams& p, int grid, cudaStream_t stream) {
-  auto kern = gqa_decode_kernel<D, FP8, T, NT, TO>;
+  auto kern = gqa_decode_kernel<D, FP8, T, NT, TO, F8M>;
   const size_t smem = smem_bytes<D, FP8>(p.batch, NT);
   static thread_local size_t configured[16] = {0};
   int dev = 0;
@@ -722,19 +829,26 @@ int launch(const DecodeParams& p, int grid, cudaStream_t stream) {
   return TB200_OK;
 }
 
-template <int D, bool FP8, typename T, int NT>
+template <int D, bool FP8, typename T, int NT, bool F8M = false>
 int launch_o(const DecodeParams& p, int o_dtype, int grid, cudaStream_t s) {
   switch (o_dtype) {
-    case TB200_F32: return launch<D, FP8, T, NT, float>(p, grid, s);
-    case TB200_BF16: return launch<D, FP8, T, NT, __nv_bfloat16>(p, grid, s);
-    case TB200_F16: return launch<D, FP8, T, NT, __half>(p, grid, s);
+    case TB200_F32: return launch<D, FP8, T, NT, float, F8M>(p, grid, s);
+    case TB200_BF16: return launch<D, FP8, T, NT, __nv_bfloat16, F8M>(p, grid, s);
+    case TB200_F16: return launch<D, FP8, T, NT, __half, F8M>(p, grid, s);
   }
   TB200_FAIL(TB200_ERR_UNSUPPORTED, "o_dtype %d is not F16, BF16 or F32", o_dtype);
 }
 
 template <int D, int NT>
 int launch_t(const DecodeParams& p, int q_dtype, int kv_dtype, int o_dtype, int grid, cudaStream_t s) {
-  if (kv_dtype == TB200_E4M3) return launch_o<D, true, __half, NT>(p, o_dtype, grid, s);
+  if (kv_dtype == TB200_E4M3) {
+    // The f16 expansion path is the default: on B200 the e4m3 mma.sync path measured slower
+    // (3.7 vs 4.4 TB/s on 128 x 4096-token sequences).  TB200_DECODE_FP8_MMA=1 selects it where
+    // its precondition holds (one scale per tile, i.e. page_size a multiple of 64).
+    const char* e = getenv("TB200_DECODE_FP8_MMA");
+    if (p.tile_in_page && e && e[0] == '1') return launch_o<D, true, __half, NT, true>(p, o_dtype, grid, s);
+    return launch_o<D, true, __half, NT>(p, o_dtype, grid, s);
+  }
   if (q_dtype == TB200_BF16) return launch_o<D, false, __nv_bfloat16, NT>(p, o_dtype, grid, s);
   return launch_o<D, false, __half, NT>(p, o_dtype, grid, s);
 }

@@ -87,6 +87,41 @@ __device__ __forceinline__ void mma_16816<__half>(float (&d)[4], const uint32_t 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+
+// D(16x8,f32) += A(16x32, e4m3) * B(32x8, e4m3)
+__device__ __forceinline__ void mma_16832_e4m3(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// Two floats -> two e4m3 bytes (round to nearest, saturating): byte 0 = lo, byte 1 = hi.
+__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// Two e4m3 bytes (byte 0, byte 1 of the low half of x) -> two floats.
+__device__ __forceinline__ float2 e4m3x2_to_f32x2(uint32_t x) {
+  uint32_t h;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h) : "h"(uint16_t(x)));
+  return __half22float2(*reinterpret_cast<__half2*>(&h));
+}
+// A value as the sum of two e4m3 numbers: hi = rn(x), lo = rn(x - hi); returns bytes (hi0, hi1) and
+// (lo0, lo1) for the pair (x0, x1).  With |x| <= 448 the pair carries about 8 significant bits.
+__device__ __forceinline__ void split_e4m3x2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+  hi = f32x2_to_e4m3x2(x0, x1);
+  const float2 h = e4m3x2_to_f32x2(hi);
+  lo = f32x2_to_e4m3x2(x0 - h.x, x1 - h.y);
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t y;
+  asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(y) : "r"(a), "r"(b), "r"(sel));
+  return y;
+}
+
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi);
 template <>
@@ -117,16 +152,43 @@ __device__ __forceinline__ float fast_tanh(float x) {
 }
 
 // Two e4m3 bytes of `x` (selected by the PRMT selector SEL, which must place them in bytes 1
-// and 3 of the result and zero in bytes 0 and 2) -> packed f16x2 holding 2^-8 times their
-// values.  Moving the 7 magnitude bits one place down turns the e4m3 exponent/mantissa into
-// an f16 exponent/mantissa with the bias off by 8 (subnormals included); the sign is carried
-// from bit 14 into bit 15 by adding bit 14 to itself.
+// and 3 of the result and zero in bytes 0 and 2) -> packed f16x2 holding kE4m3Unit^-1 times their
+// values.
+//   TB200_FP8_CVT=0: integer path.  Moving the 7 magnitude bits one place down turns the e4m3
+//     exponent/mantissa into an f16 exponent/mantissa with the bias off by 8 (subnormals
+//     included); the sign is carried from bit 14 into bit 15 by adding bit 14 to itself.  Result
+//     is 2^-8 times the value (kE4m3Unit = 256).
+//   TB200_FP8_CVT=1: the hardware conversion cvt.rn.f16x2.e4m3x2 (exact values, kE4m3Unit = 1).
+#ifndef TB200_FP8_CVT
+#define TB200_FP8_CVT 1
+#endif
+#if TB200_FP8_CVT
+constexpr float kE4m3Unit = 1.f;
+#else
+constexpr float kE4m3Unit = 256.f;
+#endif
 template <uint32_t SEL>
 __device__ __forceinline__ uint32_t e4m3x2_to_f16x2_scaled(uint32_t x) {
+#if TB200_FP8_CVT
+  // SEL names the two source bytes in its nibbles 1 and 3; gather them into the low half
+  uint32_t h;
+  if constexpr (SEL == 0x1404u) {          // bytes 0,1: the low half as it is
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\t}" : "=r"(h) : "r"(x));
+  } else if constexpr (SEL == 0x3424u) {   // bytes 2,3: the high half as it is
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, hi;\n\t}" : "=r"(h) : "r"(x));
+  } else {
+    constexpr uint32_t sel2 = ((SEL >> 4) & 0xF) | (((SEL >> 12) & 0xF) << 4) | 0x4400u;
+    uint32_t y;
+    asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(y) : "r"(x), "r"(0u), "n"(sel2));
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\t}" : "=r"(h) : "r"(y));
+  }
+  return h;
+#else
   uint32_t y;
   asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(y) : "r"(x), "r"(0u), "n"(SEL));
   uint32_t t = y >> 1;
   return t + (t & 0x40004000u);
+#endif
 }
 
 template <typename T>
