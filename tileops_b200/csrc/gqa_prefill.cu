@@ -33,11 +33,19 @@
 // lets its copies drain, frees its TMEM and returns.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "tb200_common.cuh"
 
 namespace tb200 {
 namespace {
 
+#ifndef TB200_PF_POLY
+#define TB200_PF_POLY 0
+#endif
+#ifndef TB200_PF_TRUNC
+#define TB200_PF_TRUNC 0
+#endif
 constexpr int kBM = 128;
 constexpr int kBN = 128;
 constexpr int kHD = 128;
@@ -60,6 +68,20 @@ struct SmemLayout {
 };
 // barrier indices
 enum { B_QFULL = 0, B_KFULL, B_KEMPTY, B_VFULL, B_VEMPTY, B_SFULL, B_PREADY, B_ODONE, B_COUNT };
+
+// Optional timeline for tuning (-DTB200_TRACE): CTA kTraceCta stamps %globaltimer-free clock64()
+// values of its MMA lane (slots 0-3) and of softmax thread 0 (slots 4-8) for the first
+// kTraceIters KV tiles into the workspace behind the status word.
+#ifdef TB200_TRACE
+constexpr int kTraceIters = 64, kTraceSlots = 10, kTraceCta = 600;
+#define TB200_STAMP(slot, j)                                                                          \
+  do {                                                                                                \
+    if (blockIdx.x == kTraceCta && (j) < kTraceIters)                                                 \
+      reinterpret_cast<long long*>(p.status + 64)[(j) * kTraceSlots + (slot)] = clock64();            \
+  } while (0)
+#else
+#define TB200_STAMP(slot, j) do {} while (0)
+#endif
 
 struct PrefillParams {
   void* o;
@@ -171,6 +193,18 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16])
       : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same wait, naming the registers a preceding tcgen05.ld fills: the load is asynchronous, and the
+// in/out operands keep the compiler from moving any use of those registers above the wait.
+__device__ __forceinline__ void tc_wait_ld(uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+        "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+        "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+        "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+      :
+      : "memory");
+}
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // 64-bit shared-memory matrix descriptor, 128B swizzle, version 1 (sm_100).
@@ -286,6 +320,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int j = 0; ok && j < n_kv; ++j) {
           const uint32_t par = j & 1;
           if (!mbar_wait(bar(B_KFULL), par, s_abort, p.status, 202)) break;
+          TB200_STAMP(0, j);
           tc_fence_after();
           // S = Q K^T.  It overwrites P_{j-1}, which PV_{j-1} (issued just before) still reads:
           // the tensor core executes this thread's MMAs in issue order, so no wait is needed.
@@ -299,8 +334,10 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           }
           tc_commit(bar(B_SFULL));
           tc_commit(bar(B_KEMPTY));
+          TB200_STAMP(1, j);
           if (!mbar_wait(bar(B_VFULL), par, s_abort, p.status, 203)) break;
           if (!mbar_wait(bar(B_PREADY), par, s_abort, p.status, 204)) break;
+          TB200_STAMP(2, j);
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < kBN / 16; ++ks) {
@@ -311,6 +348,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           }
           tc_commit(bar(B_VEMPTY));
           tc_commit(bar(B_ODONE));
+          TB200_STAMP(3, j);
         }
       }
     } else {
@@ -325,6 +363,8 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const uint32_t s_addr = tmem + lane_addr + kColS;
       const uint32_t o_addr = tmem + lane_addr + kColO;
       float m_run = -INFINITY, l_run = 0.f;   // m_run: the maximum O and l are currently scaled to
+      constexpr bool kBf16 = TB200_PF_TRUNC && std::is_same<T, __nv_bfloat16>::value;
+      constexpr float kTruncFix = kBf16 ? 0.0028150156f : 0.f;   // log2(1 + 2^-9)
       bool ok = true;
 
       // transform of one loaded chunk: softcap and mask (only on tiles that need it)
@@ -346,28 +386,39 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // the warp leaves the loop together: the TMEM loads below are warp-collective
         if (!__all_sync(0xffffffffu, mbar_wait(bar(B_SFULL), j & 1, s_abort, p.status, 301))) { ok = false; break; }
         tc_fence_after();
+        if (tid == 0) TB200_STAMP(4, j);
         const int k0 = j * kBN;
         const bool need_mask = (p.is_causal && k0 + kBN - 1 > m0 + off) || (k0 + kBN > p.seqlen_kv);
 
-        // ---- pass 1: row maximum ----
-        float mx = -INFINITY;
+        // ---- pass 1: row maximum.  TMEM loads are asynchronous: the next 32 columns are in flight
+        // while the maximum of the current 32 is taken. ----
+        uint32_t r0[32], r1[32];
+        auto chunk_max = [&](uint32_t (&r)[32], int cgi, float mx_in) {
+          prepare(r, k0 + cgi * 32, need_mask);
+          float a = mx_in, bb = -INFINITY;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t ra[32], rb[32];
-          tc_ld32(s_addr + half * 64, ra);
-          tc_ld32(s_addr + half * 64 + 32, rb);
-          tc_wait_ld();
-          prepare(ra, k0 + half * 64, need_mask);
-          prepare(rb, k0 + half * 64 + 32, need_mask);
-          float m0v = mx, m1v = -INFINITY;
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            m0v = max3(m0v, __uint_as_float(ra[e]), __uint_as_float(ra[e + 1]));
-            m1v = max3(m1v, __uint_as_float(rb[e]), __uint_as_float(rb[e + 1]));
+          for (int e = 0; e < 32; e += 4) {
+            a = max3(a, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
+            bb = max3(bb, __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
           }
-          mx = fmaxf(m0v, m1v);
-        }
+          return fmaxf(a, bb);
+        };
+        float mx = -INFINITY;
+        tc_ld32(s_addr, r0);
+        tc_wait_ld(r0);
+        tc_ld32(s_addr + 32, r1);
+        mx = chunk_max(r0, 0, mx);
+        tc_wait_ld(r1);
+        tc_ld32(s_addr + 64, r0);
+        mx = chunk_max(r1, 1, mx);
+        tc_wait_ld(r0);
+        tc_ld32(s_addr + 96, r1);
+        mx = chunk_max(r0, 2, mx);
+        tc_wait_ld(r1);
+        tc_ld32(s_addr, r0);          // first chunk of pass 2, in flight during the decision below
+        mx = chunk_max(r1, 3, mx);
 
+        if (tid == 0) TB200_STAMP(5, j);
         // ---- decide whether the running maximum moves (and O has to be rescaled) ----
         const float m_new = fmaxf(m_run, mx);
         const bool grow = (m_new - m_run) * c > kRescaleThreshold || (m_run == -INFINITY && m_new != -INFINITY);
@@ -381,7 +432,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             for (int cgi = 0; cgi < 4; ++cgi) {
               uint32_t ov[32];
               tc_ld32(o_addr + cgi * 32, ov);
-              tc_wait_ld();
+              tc_wait_ld(ov);
 #pragma unroll
               for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
               tc_st32(o_addr + cgi * 32, ov);
@@ -389,32 +440,58 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           }
           m_run = m_new;
         }
-        const float neg_mc = (m_run == -INFINITY) ? 0.f : -m_run * c;
+        if (tid == 0) TB200_STAMP(6, j);
+        const float neg_mc = ((m_run == -INFINITY) ? 0.f : -m_run * c) + kTruncFix;
 
         // ---- pass 2: p = 2^(s*c - m*c), row sum, P (16-bit) over the first 64 columns of S ----
         float lsum0 = 0.f, lsum1 = 0.f;
-#pragma unroll
-        for (int cgi = 0; cgi < 4; ++cgi) {
-          uint32_t r[32];
-          tc_ld32(s_addr + cgi * 32, r);
-          tc_wait_ld();
+        // Two tuning switches, both off: they measured slower or neutral on B200 (this pass is
+        // bound by instruction latency, not by the MUFU pipe).  TB200_PF_POLY evaluates every second
+        // exponential on the FMA pipe on tiles without masked entries.  TB200_PF_TRUNC packs bf16 P
+        // by taking the high halves of the two floats with one PRMT; kTruncFix in the exponent
+        // scales p by (1 + 2^-9) first, which turns truncation into round-to-nearest on average
+        // (the row sum carries the same factor, so O = (P V) / l is unaffected; the LSE subtracts it).
+        auto chunk_exp = [&](uint32_t (&r)[32], int cgi, auto masked) {
+          constexpr bool kMasked = decltype(masked)::value;
           prepare(r, k0 + cgi * 32, need_mask);
           uint32_t pk[16];
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * e]), c, neg_mc));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(r[2 * e + 1]), c, neg_mc));
+            const float x0 = fmaf(__uint_as_float(r[2 * e]), c, neg_mc);
+            const float x1 = fmaf(__uint_as_float(r[2 * e + 1]), c, neg_mc);
+            const float p0 = fast_exp2(x0);
+            const float p1 = (kMasked || !TB200_PF_POLY) ? fast_exp2(x1) : exp2_poly(x1);
             lsum0 += p0;
             lsum1 += p1;
-            pk[e] = pack_pair<T>(p0, p1);
+            if constexpr (kBf16)
+              pk[e] = prmt(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
+            else
+              pk[e] = pack_pair<T>(p0, p1);
           }
-          // P chunk cgi lands in columns [16 cgi, 16 cgi + 16): inside S chunks already consumed
+          // P chunk cgi lands in columns [16 cgi, 16 cgi + 16): inside S chunks already consumed,
+          // and below the chunk that is being loaded
           tc_st16(s_addr + cgi * 16, pk);
-        }
+        };
+        auto pass2 = [&](auto masked) {
+          tc_wait_ld(r0);
+          tc_ld32(s_addr + 32, r1);
+          chunk_exp(r0, 0, masked);
+          tc_wait_ld(r1);
+          tc_ld32(s_addr + 64, r0);
+          chunk_exp(r1, 1, masked);
+          tc_wait_ld(r0);
+          tc_ld32(s_addr + 96, r1);
+          chunk_exp(r0, 2, masked);
+          tc_wait_ld(r1);
+          chunk_exp(r1, 3, masked);
+        };
+        if (need_mask) pass2(std::true_type{}); else pass2(std::false_type{});
         l_run += lsum0 + lsum1;
+        if (tid == 0) TB200_STAMP(7, j);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(B_PREADY));
+        if (tid == 0) TB200_STAMP(8, j);
       }
 
       // ---- epilogue: O / l -> global, LSE ----
@@ -428,7 +505,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int cgi = 0; cgi < 4; ++cgi) {
           uint32_t ov[32];
           tc_ld32(o_addr + cgi * 32, ov);
-          tc_wait_ld();
+          tc_wait_ld(ov);
           if (q_idx < p.seqlen_q) {
 #pragma unroll
             for (int e = 0; e < 32; e += 8) {
@@ -443,7 +520,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         if (p.lse && q_idx < p.seqlen_q)
           p.lse[(size_t(b) * p.heads + h) * p.seqlen_q + q_idx] =
-              l_run > 0.f ? m_run * c + log2f(l_run) : -INFINITY;
+              l_run > 0.f ? m_run * c + log2f(l_run) - kTruncFix : -INFINITY;
       }
     }
   } else if (warp < 4) {
@@ -527,7 +604,7 @@ using namespace tb200;
 extern "C" size_t tb200_gqa_prefill_workspace_bytes(int batch, int heads, int heads_kv, int seqlen_q,
                                                     int seqlen_kv, int dim) {
   (void)batch; (void)heads; (void)heads_kv; (void)seqlen_q; (void)seqlen_kv; (void)dim;
-  return 256;  // one status word (0 = ok; otherwise the code of the wait that ran out)
+  return 256 + 8192;  // status word (0 = ok; otherwise the code of the wait that ran out) + tuning timeline
 }
 
 extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, void* o, float* lse, int dtype,
@@ -545,7 +622,7 @@ extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, vo
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
        reinterpret_cast<uintptr_t>(o)) & 15)
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k, v and o must be 16-byte aligned");
-  if (!workspace || workspace_bytes < 256) TB200_FAIL(TB200_ERR_WORKSPACE, "workspace must hold 256 bytes");
+  if (!workspace || workspace_bytes < 256 + 8192) TB200_FAIL(TB200_ERR_WORKSPACE, "workspace must hold 8448 bytes");
 
   CUtensorMap mq, mk, mv;
   int st;

@@ -140,6 +140,20 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x on the FMA and integer pipes (no MUFU): floor by a round-down add of 1.5*2^23, a cubic for
+// 2^frac on [0,1), then the integer part is added to the exponent field.  Relative error about
+// 1e-4 (well under bf16 resolution).  x is clamped at -127, so very negative inputs (and -inf)
+// give about 6e-39 instead of 0: use it only where every input is finite.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -127.f);
+  float xr;
+  asm("add.rm.f32 %0, %1, %2;\n" : "=f"(xr) : "f"(x), "f"(12582912.f));
+  const float f = x - (xr - 12582912.f);
+  float p = fmaf(f, 0.07711909f, 0.22756439f);
+  p = fmaf(p, f, 0.69514614f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float y;
   asm("max.f32 %0, %1, %2, %3;\n" : "=f"(y) : "f"(a), "f"(b), "f"(c));
