@@ -9,15 +9,15 @@
 //
 // One CTA = one 128-row Q tile of one (batch, q head); 6 warps:
 //   warps 0-3  softmax / correction / epilogue: thread r owns row r (TMEM lane r), no shuffles
-//   warp  4    TMA producer (one lane): Q once, then K_j and V_j, one buffer each
+//   warp  4    TMA producer (one lane): Q once, then 64-key K_i and V_i tiles into 2-buffer rings
 //   warp  5    MMA issuer (one lane) and TMEM allocator
-// TMEM (256 columns per CTA): S [0,128) | O [128,256).  P_j (bf16) overwrites the first 64 columns
-// of S_j and feeds the second MMA straight from TMEM.  A CTA by itself alternates between the
-// tensor core (PV_j, QK_{j+1} back to back) and the softmax warps; TWO CTAs are resident per SM
-// (100 KB of shared memory, 256 TMEM columns and at most 168 registers per thread each), so one
-// CTA's MMAs run under the other's softmax, and prologue/epilogue of one hide under the main
-// loop of the other.  K_{j+1} is fetched while softmax_j runs, V_{j+1} while QK_{j+1} and
-// softmax_{j+1} run, so single buffers do not expose TMA latency.
+// KV is consumed in tiles of 64 keys.  TMEM (256 columns per CTA): S0 [0,64) | S1 [64,128) |
+// O [128,256); P_i (16-bit) overwrites the first 32 columns of S_i and feeds the second MMA
+// straight from TMEM.  The MMA lane issues QK_0, QK_1, then PV_i, QK_{i+2} for i = 0, 1, ...:
+// while the softmax warps work on S_i, the tensor core runs PV_{i-1} and QK_{i+1}, so inside one
+// CTA the two sides overlap continuously.  TWO CTAs are resident per SM (97 KB of shared memory,
+// 256 TMEM columns, at most 168 registers per thread each); the second one fills what is left and
+// hides prologue and epilogue.  Every K/V buffer is refilled a full tile period before it is needed.
 //
 // Softmax is two passes over the S tile in TMEM (row max, then exp2 / sum / pack) to keep the
 // register footprint small.  O in TMEM is rescaled only when some row of the warp saw its maximum
@@ -47,27 +47,29 @@ namespace {
 #define TB200_PF_TRUNC 0
 #endif
 constexpr int kBM = 128;
-constexpr int kBN = 128;
+constexpr int kBN = 64;                      // keys per S tile
 constexpr int kHD = 128;
-constexpr int kStages = 1;
-constexpr int kPanelBytes = 128 * 128;       // 128 rows x 128 B
-constexpr int kTileBytes = 2 * kPanelBytes;  // 128 x 128 bf16
+constexpr int kStages = 2;                   // K, V and S buffers
+constexpr int kQPanel = kBM * 128;           // 128 rows x 128 B (64 head dims)
+constexpr int kQBytes = 2 * kQPanel;         // 128 x 128 16-bit
+constexpr int kKvPanel = kBN * 128;          // 64 rows x 128 B
+constexpr int kKvBytes = 2 * kKvPanel;       // 64 x 128 16-bit
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColO = 128;
+constexpr uint32_t kColS = 0, kColO = 128;    // S buffer s at columns [64 s, 64 s + 64)
 constexpr float kRescaleThreshold = 8.f;   // log2 of the growth of the row maximum that forces a rescale
 constexpr long long kWaitCycles = 1000000000LL;  // ~0.5 s at 2 GHz
 
 struct SmemLayout {
   // offsets from the 1024-aligned base
   static constexpr int q = 0;
-  static constexpr int k = q + kTileBytes;
-  static constexpr int v = k + kStages * kTileBytes;
-  static constexpr int bars = v + kStages * kTileBytes;
+  static constexpr int k = q + kQBytes;
+  static constexpr int v = k + kStages * kKvBytes;
+  static constexpr int bars = v + kStages * kKvBytes;
   static constexpr int total = bars + 256;
 };
 // barrier indices
-enum { B_QFULL = 0, B_KFULL, B_KEMPTY, B_VFULL, B_VEMPTY, B_SFULL, B_PREADY, B_ODONE, B_COUNT };
+enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PREADY = 11, B_ODONE = 13, B_OFINAL = 14, B_COUNT = 15 };
 
 // Optional timeline for tuning (-DTB200_TRACE): CTA kTraceCta stamps %globaltimer-free clock64()
 // values of its MMA lane (slots 0-3) and of softmax thread 0 (slots 4-8) for the first
@@ -216,9 +218,9 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
 }
 
 // Instruction descriptor of kind::f16: fp32 accumulate, A/B format fmt (0 = f16, 1 = bf16),
-// M = 128, N = 128, A K-major; B K-major (b_mn = 0) or MN-major (b_mn = 1).
-__host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t b_mn) {
-  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// M = 128, N = n, A K-major; B K-major (b_mn = 0) or MN-major (b_mn = 1).
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t b_mn, uint32_t n) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn << 16) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
 template <typename T>
@@ -263,13 +265,16 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   if (tid == 0) {
     mbar_init(bar(B_QFULL), 1);
-    mbar_init(bar(B_KFULL), 1);
-    mbar_init(bar(B_KEMPTY), 1);
-    mbar_init(bar(B_VFULL), 1);
-    mbar_init(bar(B_VEMPTY), 1);
-    mbar_init(bar(B_SFULL), 1);
-    mbar_init(bar(B_PREADY), 128);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar(B_KFULL + s), 1);
+      mbar_init(bar(B_KEMPTY + s), 1);
+      mbar_init(bar(B_VFULL + s), 1);
+      mbar_init(bar(B_VEMPTY + s), 1);
+      mbar_init(bar(B_SFULL + s), 1);
+      mbar_init(bar(B_PREADY + s), 128);
+    }
     mbar_init(bar(B_ODONE), 1);
+    mbar_init(bar(B_OFINAL), 1);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -283,8 +288,8 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const uint32_t tmem = *s_tmem;
 
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-  constexpr uint32_t idesc_qk = make_idesc(fmt, 0);
-  constexpr uint32_t idesc_pv = make_idesc(fmt, 1);
+  constexpr uint32_t idesc_qk = make_idesc(fmt, 0, kBN);
+  constexpr uint32_t idesc_pv = make_idesc(fmt, 1, kHD);
 
   if (n_kv > 0) {
     if (warp == 4) {
@@ -293,62 +298,75 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
-        mbar_expect_tx(bar(B_QFULL), kTileBytes);
+        mbar_expect_tx(bar(B_QFULL), kQBytes);
         tma_load_4d(sbase + SmemLayout::q, &map_q, bar(B_QFULL), 0, h, m0, b);
-        tma_load_4d(sbase + SmemLayout::q + kPanelBytes, &map_q, bar(B_QFULL), 64, h, m0, b);
-        for (int j = 0; j < n_kv; ++j) {
-          const uint32_t par = j & 1;
-          if (!mbar_wait(bar(B_KEMPTY), par ^ 1, s_abort, p.status, 101)) break;
-          mbar_expect_tx(bar(B_KFULL), kTileBytes);
-          const uint32_t kd = sbase + SmemLayout::k;
-          tma_load_4d(kd, &map_k, bar(B_KFULL), 0, hk, j * kBN, b);
-          tma_load_4d(kd + kPanelBytes, &map_k, bar(B_KFULL), 64, hk, j * kBN, b);
-          if (!mbar_wait(bar(B_VEMPTY), par ^ 1, s_abort, p.status, 102)) break;
-          mbar_expect_tx(bar(B_VFULL), kTileBytes);
-          const uint32_t vd = sbase + SmemLayout::v;
-          tma_load_4d(vd, &map_v, bar(B_VFULL), 0, hk, j * kBN, b);
-          tma_load_4d(vd + kPanelBytes, &map_v, bar(B_VFULL), 64, hk, j * kBN, b);
+        tma_load_4d(sbase + SmemLayout::q + kQPanel, &map_q, bar(B_QFULL), 64, h, m0, b);
+        for (int i = 0; i < n_kv; ++i) {
+          const int s = i & 1;
+          const uint32_t par = (i >> 1) & 1;
+          if (!mbar_wait(bar(B_KEMPTY + s), par ^ 1, s_abort, p.status, 101)) break;
+          mbar_expect_tx(bar(B_KFULL + s), kKvBytes);
+          const uint32_t kd = sbase + SmemLayout::k + s * kKvBytes;
+          tma_load_4d(kd, &map_k, bar(B_KFULL + s), 0, hk, i * kBN, b);
+          tma_load_4d(kd + kKvPanel, &map_k, bar(B_KFULL + s), 64, hk, i * kBN, b);
+          if (!mbar_wait(bar(B_VEMPTY + s), par ^ 1, s_abort, p.status, 102)) break;
+          mbar_expect_tx(bar(B_VFULL + s), kKvBytes);
+          const uint32_t vd = sbase + SmemLayout::v + s * kKvBytes;
+          tma_load_4d(vd, &map_v, bar(B_VFULL + s), 0, hk, i * kBN, b);
+          tma_load_4d(vd + kKvPanel, &map_v, bar(B_VFULL + s), 64, hk, i * kBN, b);
         }
       }
     } else if (warp == 5) {
       // ================= MMA issuer =================
       if (lane == 0) {
         bool ok = mbar_wait(bar(B_QFULL), 0, s_abort, p.status, 201);
-        const uint32_t qbase = sbase + SmemLayout::q;
-        const uint32_t kbase = sbase + SmemLayout::k;
-        const uint32_t vbase = sbase + SmemLayout::v;
-        for (int j = 0; ok && j < n_kv; ++j) {
-          const uint32_t par = j & 1;
-          if (!mbar_wait(bar(B_KFULL), par, s_abort, p.status, 202)) break;
-          TB200_STAMP(0, j);
+        // The buffers are fixed, so the matrix descriptors are built once; a k-step only adds
+        // its byte offset (>> 4) to the start-address field.
+        const uint64_t dq = make_desc(sbase + SmemLayout::q, 16, 1024);
+        const uint64_t dk0 = make_desc(sbase + SmemLayout::k, 16, 1024);
+        const uint64_t dv0 = make_desc(sbase + SmemLayout::v, kKvPanel, 1024);
+        constexpr uint64_t kBufStep = kKvBytes >> 4;        // second buffer, in start-address units
+        // S_i = Q K_i^T into S buffer i&1.  It overwrites P_{i-2}, which PV_{i-2} (issued
+        // earlier by this thread) reads: the tensor core runs one thread's MMAs in issue order.
+        auto issue_qk = [&](int i) -> bool {
+          const int s = i & 1;
+          if (!mbar_wait(bar(B_KFULL + s), (i >> 1) & 1, s_abort, p.status, 202)) return false;
+          TB200_STAMP(0, i);
           tc_fence_after();
-          // S = Q K^T.  It overwrites P_{j-1}, which PV_{j-1} (issued just before) still reads:
-          // the tensor core executes this thread's MMAs in issue order, so no wait is needed.
 #pragma unroll
           for (int ks = 0; ks < kHD / 16; ++ks) {
-            // K-major operands: 16 elements per step = 32 B inside the 128 B swizzled row;
-            // after 4 steps move to the second 64-element panel
-            const uint32_t o = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
-            tc_mma_ss(tmem + kColS, make_desc(qbase + o, 16, 1024), make_desc(kbase + o, 16, 1024), idesc_qk,
-                      ks > 0 ? 1u : 0u);
+            // K-major operands: 16 elements per step = 32 B inside the 128 B swizzled row; after 4
+            // steps move to the second 64-element panel (16 KB further for Q, 8 KB for K)
+            const uint32_t oq = ((ks >> 2) * kQPanel + (ks & 3) * 32) >> 4;
+            const uint32_t ok_ = ((ks >> 2) * kKvPanel + (ks & 3) * 32) >> 4;
+            tc_mma_ss(tmem + kColS + s * kBN, dq + oq, dk0 + s * kBufStep + ok_, idesc_qk, ks > 0 ? 1u : 0u);
           }
-          tc_commit(bar(B_SFULL));
-          tc_commit(bar(B_KEMPTY));
-          TB200_STAMP(1, j);
-          if (!mbar_wait(bar(B_VFULL), par, s_abort, p.status, 203)) break;
-          if (!mbar_wait(bar(B_PREADY), par, s_abort, p.status, 204)) break;
-          TB200_STAMP(2, j);
+          tc_commit(bar(B_SFULL + s));
+          tc_commit(bar(B_KEMPTY + s));
+          TB200_STAMP(1, i);
+          return true;
+        };
+        if (ok) ok = issue_qk(0);
+        if (ok && n_kv > 1) ok = issue_qk(1);
+        for (int i = 0; ok && i < n_kv; ++i) {
+          const int s = i & 1;
+          const uint32_t par = (i >> 1) & 1;
+          if (!mbar_wait(bar(B_VFULL + s), par, s_abort, p.status, 203)) break;
+          if (!mbar_wait(bar(B_PREADY + s), par, s_abort, p.status, 204)) break;
+          TB200_STAMP(2, i);
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < kBN / 16; ++ks) {
             // B = V: MN-major, 16 tokens per step = 16 rows of 128 B; the two 64-wide d panels
-            // are kPanelBytes apart (leading offset), 8-row groups 1024 B apart (stride offset)
-            const uint64_t bd = make_desc(vbase + ks * 2048, kPanelBytes, 1024);
-            tc_mma_ts(tmem + kColO, tmem + kColS + ks * 8, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+            // are kKvPanel apart (leading offset), 8-row groups 1024 B apart (stride offset)
+            tc_mma_ts(tmem + kColO, tmem + kColS + s * kBN + ks * 8, dv0 + s * kBufStep + ((ks * 2048) >> 4), idesc_pv,
+                      (i > 0 || ks > 0) ? 1u : 0u);
           }
-          tc_commit(bar(B_VEMPTY));
+          tc_commit(bar(B_VEMPTY + s));
           tc_commit(bar(B_ODONE));
-          TB200_STAMP(3, j);
+          if (i == n_kv - 1) tc_commit(bar(B_OFINAL));   // its own barrier: B_ODONE may be two phases ahead of a late reader
+          TB200_STAMP(3, i);
+          if (i + 2 < n_kv) ok = issue_qk(i + 2);
         }
       }
     } else {
@@ -360,7 +378,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const float pre = kSoftcap ? p.sm_scale / cap : 0.f;
       const int q_idx = m0 + row;
       const int key_limit = p.is_causal ? q_idx + off : 0x7fffffff;  // last visible key of this row
-      const uint32_t s_addr = tmem + lane_addr + kColS;
+      const uint32_t s_addr0 = tmem + lane_addr + kColS;
       const uint32_t o_addr = tmem + lane_addr + kColO;
       float m_run = -INFINITY, l_run = 0.f;   // m_run: the maximum O and l are currently scaled to
       constexpr bool kBf16 = TB200_PF_TRUNC && std::is_same<T, __nv_bfloat16>::value;
@@ -383,8 +401,10 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       };
 
       for (int j = 0; j < n_kv; ++j) {
+        const int sb = j & 1;                               // S / P buffer of this tile
+        const uint32_t s_addr = s_addr0 + sb * kBN;
         // the warp leaves the loop together: the TMEM loads below are warp-collective
-        if (!__all_sync(0xffffffffu, mbar_wait(bar(B_SFULL), j & 1, s_abort, p.status, 301))) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(B_SFULL + sb), (j >> 1) & 1, s_abort, p.status, 301))) { ok = false; break; }
         tc_fence_after();
         if (tid == 0) TB200_STAMP(4, j);
         const int k0 = j * kBN;
@@ -409,14 +429,8 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tc_ld32(s_addr + 32, r1);
         mx = chunk_max(r0, 0, mx);
         tc_wait_ld(r1);
-        tc_ld32(s_addr + 64, r0);
-        mx = chunk_max(r1, 1, mx);
-        tc_wait_ld(r0);
-        tc_ld32(s_addr + 96, r1);
-        mx = chunk_max(r0, 2, mx);
-        tc_wait_ld(r1);
         tc_ld32(s_addr, r0);          // first chunk of pass 2, in flight during the decision below
-        mx = chunk_max(r1, 3, mx);
+        mx = chunk_max(r1, 1, mx);
 
         if (tid == 0) TB200_STAMP(5, j);
         // ---- decide whether the running maximum moves (and O has to be rescaled) ----
@@ -427,7 +441,10 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2((m_run - m_new) * c);
           l_run *= alpha;
           if (j > 0) {
-            // S_j is complete, so PV_{j-1} (issued before QK_j) is too: O may be read and written
+            // PV_{j-1} was issued after QK_j and may still be adding into O: wait for it.  (It
+            // depends only on P_{j-1}, which these warps handed over a tile ago.)
+            if (!__all_sync(0xffffffffu, mbar_wait(bar(B_ODONE), (j - 1) & 1, s_abort, p.status, 302))) { ok = false; break; }
+            tc_fence_after();
 #pragma unroll
             for (int cgi = 0; cgi < 4; ++cgi) {
               uint32_t ov[32];
@@ -477,25 +494,19 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           tc_ld32(s_addr + 32, r1);
           chunk_exp(r0, 0, masked);
           tc_wait_ld(r1);
-          tc_ld32(s_addr + 64, r0);
           chunk_exp(r1, 1, masked);
-          tc_wait_ld(r0);
-          tc_ld32(s_addr + 96, r1);
-          chunk_exp(r0, 2, masked);
-          tc_wait_ld(r1);
-          chunk_exp(r1, 3, masked);
         };
         if (need_mask) pass2(std::true_type{}); else pass2(std::false_type{});
         l_run += lsum0 + lsum1;
         if (tid == 0) TB200_STAMP(7, j);
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(bar(B_PREADY));
+        mbar_arrive(bar(B_PREADY + sb));
         if (tid == 0) TB200_STAMP(8, j);
       }
 
       // ---- epilogue: O / l -> global, LSE ----
-      if (ok) ok = mbar_wait(bar(B_ODONE), (n_kv - 1) & 1, s_abort, p.status, 303);
+      if (ok) ok = mbar_wait(bar(B_OFINAL), 0, s_abort, p.status, 303);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after();
@@ -566,13 +577,13 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [batch, seq, heads, 128] contiguous 16-bit tensor -> 4-D map (d, head, seq, batch), box 64 x 1 x 128 x 1
-int make_map(CUtensorMap* map, const void* base, int dtype, int batch, int seq, int heads) {
+// [batch, seq, heads, 128] contiguous 16-bit tensor -> 4-D map (d, head, seq, batch), box 64 x 1 x box_rows x 1
+int make_map(CUtensorMap* map, const void* base, int dtype, int batch, int seq, int heads, int box_rows) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) TB200_FAIL(TB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[4] = {cuuint64_t(kHD), cuuint64_t(heads), cuuint64_t(seq), cuuint64_t(batch)};
   cuuint64_t strides[3] = {cuuint64_t(kHD) * 2, cuuint64_t(heads) * kHD * 2, cuuint64_t(seq) * heads * kHD * 2};
-  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t box[4] = {64, 1, cuuint32_t(box_rows), 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, dtype == TB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -626,9 +637,9 @@ extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, vo
 
   CUtensorMap mq, mk, mv;
   int st;
-  if ((st = make_map(&mq, q, dtype, batch, seqlen_q, heads)) != TB200_OK) return st;
-  if ((st = make_map(&mk, k, dtype, batch, seqlen_kv, heads_kv)) != TB200_OK) return st;
-  if ((st = make_map(&mv, v, dtype, batch, seqlen_kv, heads_kv)) != TB200_OK) return st;
+  if ((st = make_map(&mq, q, dtype, batch, seqlen_q, heads, kBM)) != TB200_OK) return st;
+  if ((st = make_map(&mk, k, dtype, batch, seqlen_kv, heads_kv, kBN)) != TB200_OK) return st;
+  if ((st = make_map(&mv, v, dtype, batch, seqlen_kv, heads_kv, kBN)) != TB200_OK) return st;
 
   PrefillParams p{};
   p.o = o; p.lse = lse; p.status = static_cast<int*>(workspace);
