@@ -6,19 +6,22 @@
 // reference's per-call host synchronisation on real_seqlen_kv.max().
 //
 // The op is HBM bound: every K and V byte is read exactly once.  Design:
-//   * work item = (sequence, KV head, contiguous run of 64-token tiles); the runs are cut on
-//     the device from real_seqlen_kv so that all items carry about the same number of
-//     tokens, and CTAs pull items from an atomic counter (no host sync, no idle tail);
-//   * K/V rows are gathered through the block table with 16-byte cp.async into a 3/4-stage
+//   * work item = (sequence, KV head, contiguous run of 64-token tiles); every CTA derives the
+//     same plan from real_seqlen_kv on the device: a small cost model scores 16 candidate run
+//     lengths (busiest CTA's tiles + per-item + per-split merge cost) and takes the cheapest;
+//     CTAs pull items from an atomic counter (no host sync, no idle tail);
+//   * K/V rows are gathered through the block table with 16-byte cp.async into a 3-stage
 //     shared-memory ring (rows padded by 16 B so that ldmatrix is bank-conflict free);
 //   * tokens sit on the MMA M dimension and the q-head group on N=8
 //     (S^T = K Q^T, O^T = V^T P^T, mma.sync.m16n8k16), so no tensor-core row is padding;
 //   * each of the 4 warps owns 16 tokens of a tile and keeps its own running max/sum
 //     (register + shuffle reductions); the warps meet once per item;
-//   * FP8-e4m3 caches are expanded to f16 in registers between ldmatrix and mma, the
-//     per-(page, KV head) scales are applied to the fp32 scores (K) and to P (V);
+//   * FP8-e4m3 caches are converted to f16 in registers between ldmatrix and mma
+//     (cvt.rn.f16x2.e4m3x2), the per-(page, KV head) scales are applied to the fp32 scores
+//     (K) and to P (V);
 //   * partial (O, max, sum) of an item go to a workspace in fp32; the CTA that finishes a
-//     (sequence, KV head) last merges them (atomic ticket, nobody waits).
+//     (sequence, KV head) last merges them (acq_rel atomic ticket taken after the next
+//     item's loads are issued; nobody waits).
 #include <stdlib.h>
 
 #include "tb200_common.cuh"
