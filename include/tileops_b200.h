@@ -12,6 +12,7 @@
  * reference operators (paths relative to the tile-ai/TileOPs tree):
  *   tb200_gqa_decode        GQADecodeKernel.forward        src/tileops/kernels/attention/gqa_decode.py:555-615
  *                           GQADecodePagedKernel.forward   src/tileops/kernels/attention/gqa_decode_paged.py:669-746
+ *   tb200_gqa_prefill_paged GQAPrefillPagedWithKVCacheFwdKernel  src/tileops/kernels/attention/gqa_fwd.py:600-1002
  *   tb200_gqa_prefill       GQAPrefillFwdKernel / GQAPrefillFwdWsPersistentCausalKernel
  *                                                          src/tileops/kernels/attention/gqa_fwd.py:519-597,
  *                                                          src/tileops/kernels/attention/gqa_prefill_fwd_ws.py:436-520
@@ -152,7 +153,7 @@ int tb200_gqa_lse_merge(const float* o_parts, const float* lse_parts, void* o, f
  * for a uniform batch:
  *   q [batch, seqlen_q, heads, dim], k/v [batch, seqlen_kv, heads_kv, dim]  dtype (F16 | BF16)
  *   o [batch, seqlen_q, heads, dim] dtype ; lse [batch, heads, seqlen_q] fp32 log2-domain or NULL
- * dim must be 128 (tcgen05 path).  Rows with no visible key give o = 0, lse = -inf.
+ * dim must be 64 or 128 (tcgen05 path).  Rows with no visible key give o = 0, lse = -inf.
  * workspace: tb200_gqa_prefill_workspace_bytes() bytes (may be 0 -> NULL allowed).
  * ------------------------------------------------------------------------- */
 size_t tb200_gqa_prefill_workspace_bytes(int batch, int heads, int heads_kv, int seqlen_q,
@@ -162,6 +163,39 @@ int tb200_gqa_prefill(const void* q, const void* k, const void* v, void* o, floa
                       int dtype, int batch, int seqlen_q, int seqlen_kv, int heads, int heads_kv,
                       int dim, int is_causal, float sm_scale, float softcap,
                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Packed (ragged) GQA prefill of one chunk per request over a paged KV cache, with append.
+ *
+ * Replaces the forward of GQAPrefillPagedWithKVCacheFwdKernel
+ * (src/tileops/kernels/attention/gqa_fwd.py:600-1002; operator
+ * GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp, src/tileops/ops/attention/gqa.py:765-1157)
+ * and, with the cache arguments NULL, of the packed varlen prefill kernel
+ * (src/tileops/kernels/attention/gqa_prefill_varlen_fwd.py; operator
+ * GroupedQueryAttentionPrefillVarlenFwdOp, gqa.py:555-762 with equal q and kv lengths):
+ *   q [total_q, heads, dim], k_new / v_new [total_q, heads_kv, dim]      dtype (F16 | BF16)
+ *   cu_seqlens_q [batch + 1] int32: request b owns rows cu[b] .. cu[b+1]
+ *   k_pages / v_pages [pool_tokens, heads_kv, dim] dtype, cache_seqlens [batch] int32 (tokens
+ *   of request b already cached), block_table [batch, block_table_stride] int32
+ *   o [total_q, heads, dim] dtype ; lse [heads, total_q] fp32 log2-domain or NULL
+ * Request b attends to its cache_seqlens[b] cached tokens (read from the pages) followed by its
+ * own new tokens (read from k_new / v_new): causal means key position <= cache_seqlens[b] + row.
+ * The new K/V rows are also written into the pages at logical positions cache_seqlens[b] + i
+ * (block_table[b, pos / page_size] * page_size + pos % page_size), in place, by the same launch;
+ * cached tokens are never modified.  page_size: a power of two >= 16.  dim: 64 or 128.
+ * block_table ids are trusted (range-check them on the host, as the reference operator does).
+ * k_pages = v_pages = cache_seqlens = block_table = NULL: no cache, nothing appended.
+ * max_seqlen_q bounds the longest request (it sizes the grid).
+ * workspace: tb200_gqa_prefill_workspace_bytes() bytes, zeroed once.
+ * ------------------------------------------------------------------------- */
+int tb200_gqa_prefill_paged(const void* q, const void* k_new, const void* v_new,
+                            void* k_pages, void* v_pages, void* o, float* lse,
+                            const int32_t* cu_seqlens_q, const int32_t* cache_seqlens,
+                            const int32_t* block_table, int64_t block_table_stride,
+                            int dtype, int total_q, int batch, int max_seqlen_q,
+                            int heads, int heads_kv, int dim, int page_size, int64_t pool_tokens,
+                            int is_causal, float sm_scale, float softcap,
+                            void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -261,6 +261,38 @@ def prefill_packed_ref(q, k, v, cu_seqlens_q, cu_seqlens_kv, is_causal=True,
     return torch.cat(outs, dim=0)
 
 
+def prefill_paged_ref(q, k_new, v_new, k_pages, v_pages, cu_seqlens_q, cache_seqlens, block_table,
+                      page_size, is_causal=True, sm_scale=None, softcap=None):
+    """Packed prefill of one chunk per request over a paged cache, with append.
+
+    q [total_q,H,D], k_new/v_new [total_q,Hkv,D], k_pages/v_pages [pool_tokens,Hkv,D],
+    cu_seqlens_q [B+1], cache_seqlens [B], block_table [B,W] -> (o [total_q,H,D], k_pages_after,
+    v_pages_after).  Follows ``_gqa_prefill_paged_ref`` and the append checks of
+    ``tests/ops/attention/test_gqa_prefill_paged.py:76-117,288-300``: request b attends to its
+    cached tokens (gathered through the table) followed by its new tokens, causal meaning
+    ``kv_pos <= cache_len + q_pos`` (the bottom-right alignment of :func:`prefill_ref`); the new
+    rows land at logical positions ``cache_len + i``; cached rows are untouched.
+    """
+    cq = [int(x) for x in cu_seqlens_q.tolist()]
+    kp_after, vp_after = k_pages.clone(), v_pages.clone()
+    outs = []
+    for b in range(len(cq) - 1):
+        old = int(cache_seqlens[b])
+        n = cq[b + 1] - cq[b]
+        bt_row = block_table[b].numpy() if isinstance(block_table, torch.Tensor) else np.asarray(block_table[b])
+        rows_old = torch.from_numpy(physical_rows(bt_row, old, page_size).astype(np.int64))
+        k_all = torch.cat([k_pages[rows_old].to(q.dtype), k_new[cq[b]:cq[b + 1]]], dim=0)
+        v_all = torch.cat([v_pages[rows_old].to(q.dtype), v_new[cq[b]:cq[b + 1]]], dim=0)
+        if n > 0:
+            outs.append(prefill_ref(q[cq[b]:cq[b + 1]].unsqueeze(0), k_all.unsqueeze(0), v_all.unsqueeze(0),
+                                    is_causal, sm_scale, softcap)[0])
+            rows_new = torch.from_numpy(physical_rows(bt_row, old + n, page_size)[old:].astype(np.int64))
+            kp_after[rows_new] = k_new[cq[b]:cq[b + 1]].to(k_pages.dtype)
+            vp_after[rows_new] = v_new[cq[b]:cq[b + 1]].to(v_pages.dtype)
+    o = torch.cat(outs, dim=0) if outs else q.new_zeros(q.shape)
+    return o, kp_after, vp_after
+
+
 # ---------------------------------------------------------------------------
 # split / shard merge (log2-domain LSE)
 # ---------------------------------------------------------------------------

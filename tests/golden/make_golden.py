@@ -11,6 +11,8 @@ What is executed from the reference (imported, never copied):
   * ``workloads.gqa_fp8_utils.quantize_kv_fa3_descale``
   * ``tests.ops.attention.test_gqa_decode_paged.GroupedQueryAttentionDecodePagedTest.ref_program``
   * ``tests.ops.attention.test_gqa._gqa_prefill_ref`` / ``_gqa_prefill_varlen_ref``
+  * ``tests.ops.attention.test_gqa_prefill_paged._gqa_prefill_paged_ref`` /
+    ``_fill_paged_cache_from_logical`` / ``_physical_pos``
   * ``tileops.perf.formulas.gqa_*_roofline``
 ``tileops.ops`` itself needs a newer TileLang than the container has, so a stub
 module carrying the handful of names those files import is placed in
@@ -157,6 +159,41 @@ def main():
     out["fp8_x"] = bits(xk); out["fp8_q"] = bits(xq); out["fp8_scale"] = desc.numpy()
     # dequantise as tests/ops/attention/test_gqa_prefill_paged.py:355-356 (scale per page/head)
     out["fp8_dq_bf16"] = bits((xq.float() * desc[:, None, :, None]).to(torch.bfloat16))
+
+    # ---- packed prefill over a paged cache with append (unaligned cached lengths, 16-token pages)
+    from tests.ops.attention import test_gqa_prefill_paged as tpp
+    q_lens, old_lens, H, Hkv, D, page, W = [17, 33], [37, 100], 4, 2, 32, 16, 10
+    nb = len(q_lens)
+    tq = sum(q_lens)
+    cu = torch.tensor([0, 17, 50], dtype=torch.int32)
+    bt = torch.randperm(nb * W, generator=g).to(torch.int32).reshape(nb, W)
+    qn = torch.randn(tq, H, D, generator=g)
+    kn = torch.randn(tq, Hkv, D, generator=g)
+    vn = torch.randn(tq, Hkv, D, generator=g)
+    k_old = [torch.randn(n, Hkv, D, generator=g) for n in old_lens]
+    v_old = [torch.randn(n, Hkv, D, generator=g) for n in old_lens]
+    kpg = torch.zeros(nb * W * page, Hkv, D)
+    vpg = torch.zeros_like(kpg)
+    tpp._fill_paged_cache_from_logical(kpg, vpg, k_old, v_old, bt, page)
+    out["pp_q"], out["pp_k_new"], out["pp_v_new"] = qn.numpy(), kn.numpy(), vn.numpy()
+    out["pp_k_pages"], out["pp_v_pages"] = kpg.numpy().copy(), vpg.numpy().copy()
+    out["pp_cu"], out["pp_cache"], out["pp_bt"] = cu.numpy(), np.asarray(old_lens, np.int32), bt.numpy()
+    out["pp_page"] = np.int32(page)
+    kw = dict(batch=nb, heads=H, heads_kv=Hkv)
+    out["pp_o_causal"] = tpp._gqa_prefill_paged_ref(qn, kn, vn, k_old, v_old, cu, is_causal=True, **kw).numpy()
+    out["pp_o_full"] = tpp._gqa_prefill_paged_ref(qn, kn, vn, k_old, v_old, cu, is_causal=False, **kw).numpy()
+    out["pp_o_softcap"] = tpp._gqa_prefill_paged_ref(qn, kn, vn, k_old, v_old, cu, is_causal=True,
+                                                     softcap=2.0, **kw).numpy()
+    out["pp_o_causal_f16"] = bits(tpp._gqa_prefill_paged_ref(
+        qn.half(), kn.half(), vn.half(), [t.half() for t in k_old], [t.half() for t in v_old], cu,
+        is_causal=True, **kw))
+    # pages after the append, as the reference's test states it (test_gqa_prefill_paged.py:288-300)
+    for b_, (ql, ol) in enumerate(zip(q_lens, old_lens)):
+        for i in range(ql):
+            pos = tpp._physical_pos(bt, b_, ol + i, page)
+            kpg[pos] = kn[int(cu[b_]) + i]
+            vpg[pos] = vn[int(cu[b_]) + i]
+    out["pp_k_pages_after"], out["pp_v_pages_after"] = kpg.numpy(), vpg.numpy()
 
     np.savez_compressed(os.path.join(HERE, "gqa_golden.npz"), **out)
 

@@ -54,6 +54,21 @@ def test_fwd_op_matches_oracle(B, S, H, Hkv, causal, dtype):
     assert op.eval_roofline()[0] == (4 * B * H * S * S * 128) // (2 if causal else 1)
 
 
+@pytest.mark.parametrize("B,Sq,Skv,H,Hkv,causal,dtype", [
+    (2, 256, 256, 8, 2, True, torch.float16),
+    (1, 200, 333, 4, 4, True, torch.bfloat16),
+    (1, 1024, 1024, 8, 1, False, torch.bfloat16),
+    (1, 77, 77, 2, 1, True, torch.float16),
+])
+def test_head_dim_64(B, Sq, Skv, H, Hkv, causal, dtype):
+    q, k, v = W.make_prefill(45, B, Sq, Skv, H, Hkv, 64, dtype, "cuda")
+    o, lse = F.gqa_prefill(q, k, v, is_causal=causal, return_lse=True)
+    ro, rl = O.prefill_ref(q.cpu(), k.cpu(), v.cpu(), causal, return_lse=True)
+    close(o, ro)
+    torch.testing.assert_close(lse.cpu(), rl, atol=2e-3, rtol=1e-3)
+    assert F.prefill_status("cuda:0") == 0
+
+
 @pytest.mark.parametrize("Sq,Skv,causal", [(128, 256, True), (512, 4096, True), (96, 150, True),
                                            (150, 406, True), (256, 128, False), (64, 1000, False)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])

@@ -87,6 +87,25 @@ def test_prefill_packed_matches_reference_varlen():
     torch.testing.assert_close(o, t("pre_o_varlen"), atol=2e-6, rtol=1e-5)
 
 
+def _paged_prefill_args():
+    return (t("pp_q"), t("pp_k_new"), t("pp_v_new"), t("pp_k_pages"), t("pp_v_pages"), t("pp_cu"),
+            t("pp_cache"), t("pp_bt"), int(G["pp_page"]))
+
+
+def test_paged_prefill_matches_reference_and_appends():
+    args = _paged_prefill_args()
+    o, kp, vp = O.prefill_paged_ref(*args, is_causal=True)
+    torch.testing.assert_close(o, t("pp_o_causal"), atol=2e-6, rtol=1e-5)
+    assert torch.equal(kp, t("pp_k_pages_after")) and torch.equal(vp, t("pp_v_pages_after"))
+    o, _, _ = O.prefill_paged_ref(*args, is_causal=False)
+    torch.testing.assert_close(o, t("pp_o_full"), atol=2e-6, rtol=1e-5)
+    o, _, _ = O.prefill_paged_ref(*args, is_causal=True, softcap=2.0)
+    torch.testing.assert_close(o, t("pp_o_softcap"), atol=2e-6, rtol=1e-5)
+    q, kn, vn, kpg, vpg = (x.half() for x in args[:5])
+    o, _, _ = O.prefill_paged_ref(q, kn, vn, kpg, vpg, *args[5:], is_causal=True)
+    torch.testing.assert_close(o.float(), fp16("pp_o_causal_f16").float(), atol=1e-3, rtol=1e-3)
+
+
 def test_bottom_right_known_answer():
     # tests/ops/attention/test_gqa.py:417-443 in the reference
     q = torch.zeros(1, 128, 4, 64); k = torch.zeros(1, 256, 2, 64); v = torch.zeros(1, 256, 2, 64)

@@ -48,19 +48,30 @@ namespace {
 #endif
 constexpr int kBM = 128;
 constexpr int kBN = 64;                      // keys per S tile
-constexpr int kHD = 128;
 constexpr int kStages = 2;                   // K, V and S buffers
 constexpr int kQPanel = kBM * 128;           // 128 rows x 128 B (64 head dims)
-constexpr int kQBytes = 2 * kQPanel;         // 128 x 128 16-bit
 constexpr int kKvPanel = kBN * 128;          // 64 rows x 128 B
-constexpr int kKvBytes = 2 * kKvPanel;       // 64 x 128 16-bit
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0, kColO = 128;    // S buffer s at columns [64 s, 64 s + 64)
+#ifndef TB200_PF_TIE
+#define TB200_PF_TIE 1
+#endif
+#ifndef TB200_PF_WAIT_HINT_NS
+#define TB200_PF_WAIT_HINT_NS 0   // suspend-time hint of a failed mbarrier probe; 0 = none
+#endif
+#ifndef TB200_PF_F32X2
+#define TB200_PF_F32X2 1
+#endif
 constexpr float kRescaleThreshold = 8.f;   // log2 of the growth of the row maximum that forces a rescale
 constexpr long long kWaitCycles = 1000000000LL;  // ~0.5 s at 2 GHz
 
-struct SmemLayout {
+// Shared-memory plan for head dim HD (64 or 128): HD / 64 panels per operand tile.
+template <int HD>
+struct SmemLayoutT {
+  static constexpr int kPanels = HD / 64;
+  static constexpr int kQBytes = kPanels * kQPanel;    // 128 x HD 16-bit
+  static constexpr int kKvBytes = kPanels * kKvPanel;  // 64 x HD 16-bit
   // offsets from the 1024-aligned base
   static constexpr int q = 0;
   static constexpr int k = q + kQBytes;
@@ -92,6 +103,17 @@ struct PrefillParams {
   int batch, heads, heads_kv, seqlen_q, seqlen_kv;
   int is_causal;
   float sm_scale, softcap;
+  // packed (ragged) queries over a paged cache; unused by the dense kernel
+  const int32_t* cu_q;         // [batch + 1] row offsets of the requests in q / k_new / v_new / o
+  const int32_t* cache_lens;   // [batch] tokens already in the pages (null: none)
+  const int32_t* bt;           // [batch, bt_stride] logical page -> physical page
+  long long bt_stride;
+  const void* k_new;           // [total_q, heads_kv, HD]
+  const void* v_new;
+  void* k_pages;               // [pool_tokens, heads_kv, HD]; null: nothing is appended
+  void* v_pages;
+  int page_size, page_shift, page_box;   // page_box = min(64, page_size): rows per TMA box of the pool maps
+  int total_q;
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------
@@ -108,10 +130,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
+#if TB200_PF_WAIT_HINT_NS
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(uint32_t(TB200_PF_WAIT_HINT_NS))
       : "memory");
   return ok != 0;
 }
@@ -198,6 +224,10 @@ __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sy
 // The same wait, naming the registers a preceding tcgen05.ld fills: the load is asynchronous, and the
 // in/out operands keep the compiler from moving any use of those registers above the wait.
 __device__ __forceinline__ void tc_wait_ld(uint32_t (&r)[32]) {
+#if !TB200_PF_TIE
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  return;
+#endif
   asm volatile(
       "tcgen05.wait::ld.sync.aligned;"
       : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
@@ -206,6 +236,25 @@ __device__ __forceinline__ void tc_wait_ld(uint32_t (&r)[32]) {
         "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
       :
       : "memory");
+}
+// Packed pairs of fp32 (sm_100 has two-wide fp32 FMA and ADD on 64-bit register pairs).
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -227,10 +276,20 @@ template <typename T>
 __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) { return pack2<T>(lo, hi); }
 
 // ---- kernel --------------------------------------------------------------------------------
-template <typename T, bool kSoftcap>
+// kPaged = false: dense [batch, seq, heads, HD] tensors, one KV segment.
+// kPaged = true: requests packed along the row dimension (cu_q), and two KV segments per request:
+// the tokens already in the paged cache (read through the block table with map_kp / map_vp, all
+// visible to every query row) and then the request's own new tokens (read from k_new / v_new with
+// map_k / map_v, causal inside the chunk).  CTAs of the first q head of a KV group also copy their
+// 128 new K/V rows into the pages; attention never reads those copies, so no CTA waits for another.
+template <typename T, bool kSoftcap, int HD, bool kPaged>
 __global__ void __launch_bounds__(kThreads, 2)
 gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, PrefillParams p) {
+                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_kp,
+                   const __grid_constant__ CUtensorMap map_vp, PrefillParams p) {
+  using SmemLayout = SmemLayoutT<HD>;
+  constexpr int kHD = HD;
+  constexpr int kQBytes = SmemLayout::kQBytes, kKvBytes = SmemLayout::kKvBytes;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -249,19 +308,33 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (s_skip != 0) return;
 
   // ---- which tile ---------------------------------------------------------------------
-  const int n_m = (p.seqlen_q + kBM - 1) / kBM;
+  const int n_m = (p.seqlen_q + kBM - 1) / kBM;            // paged: seqlen_q is the longest request
   const int per_m = p.heads * p.batch;
   const int mt = n_m - 1 - int(blockIdx.x) / per_m;        // heaviest (last) row tiles first
   const int rest = int(blockIdx.x) % per_m;
   const int b = rest / p.heads, h = rest % p.heads;
   const int hk = h / (p.heads / p.heads_kv);
   const int m0 = mt * kBM;
-  const int off = p.seqlen_kv - p.seqlen_q;                // bottom-right alignment
-  int n_kv = (p.seqlen_kv + kBN - 1) / kBN;
+  // rows of this tile in the q / o tensors, and where the (new) K/V segment starts
+  int q_row0 = m0, q_batch = b, q_len = p.seqlen_q, kv_len = p.seqlen_kv, old_len = 0;
+  if (kPaged) {
+    const int q0 = p.cu_q[b];
+    q_len = p.cu_q[b + 1] - q0;
+    if (m0 >= q_len) return;                               // the whole CTA: nothing allocated yet
+    kv_len = q_len;
+    old_len = p.cache_lens ? p.cache_lens[b] : 0;
+    q_row0 = q0 + m0;
+    q_batch = 0;
+  }
+  const int kv_row0 = q_row0 - m0;                         // row of the segment's first key (0 when dense)
+  const int off = kv_len - q_len;                          // bottom-right alignment (0 when paged)
+  const int n_old = (old_len + kBN - 1) / kBN;             // tiles of cached tokens (0 when dense)
+  int n_new = (kv_len + kBN - 1) / kBN;
   if (p.is_causal) {
     const int last_key = m0 + kBM - 1 + off;               // last key the tile's last row may see
-    n_kv = last_key < 0 ? 0 : min(n_kv, last_key / kBN + 1);
+    n_new = last_key < 0 ? 0 : min(n_new, last_key / kBN + 1);
   }
+  const int n_kv = n_old + n_new;
 
   if (tid == 0) {
     mbar_init(bar(B_QFULL), 1);
@@ -298,22 +371,43 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+        if (kPaged && n_old > 0) {
+          asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kp) : "memory");
+          asm volatile("prefetch.tensormap [%0];" ::"l"(&map_vp) : "memory");
+        }
         mbar_expect_tx(bar(B_QFULL), kQBytes);
-        tma_load_4d(sbase + SmemLayout::q, &map_q, bar(B_QFULL), 0, h, m0, b);
-        tma_load_4d(sbase + SmemLayout::q + kQPanel, &map_q, bar(B_QFULL), 64, h, m0, b);
+#pragma unroll
+        for (int pn = 0; pn < kHD / 64; ++pn)
+          tma_load_4d(sbase + SmemLayout::q + pn * kQPanel, &map_q, bar(B_QFULL), pn * 64, h, q_row0, q_batch);
+        // one 64-key tile of K or V: HD / 64 panels; a cached tile is gathered page by page
+        // (page_box rows per copy) through the block table
+        auto load_tile = [&](uint32_t dst, uint32_t full_bar, const CUtensorMap* dense_map,
+                             const CUtensorMap* pool_map, int i) {
+          if (kPaged && i < n_old) {
+            for (int r = 0; r < kBN; r += p.page_box) {
+              const int tok = i * kBN + r;
+              const int page = p.bt[(long long)b * p.bt_stride + (tok >> p.page_shift)];
+              const int row = page * p.page_size + (tok & (p.page_size - 1));
+#pragma unroll
+              for (int pn = 0; pn < kHD / 64; ++pn)
+                tma_load_4d(dst + pn * kKvPanel + r * 128, pool_map, full_bar, pn * 64, hk, row, 0);
+            }
+          } else {
+            const int row = kv_row0 + (i - n_old) * kBN;
+#pragma unroll
+            for (int pn = 0; pn < kHD / 64; ++pn)
+              tma_load_4d(dst + pn * kKvPanel, dense_map, full_bar, pn * 64, hk, row, q_batch);
+          }
+        };
         for (int i = 0; i < n_kv; ++i) {
           const int s = i & 1;
           const uint32_t par = (i >> 1) & 1;
           if (!mbar_wait(bar(B_KEMPTY + s), par ^ 1, s_abort, p.status, 101)) break;
           mbar_expect_tx(bar(B_KFULL + s), kKvBytes);
-          const uint32_t kd = sbase + SmemLayout::k + s * kKvBytes;
-          tma_load_4d(kd, &map_k, bar(B_KFULL + s), 0, hk, i * kBN, b);
-          tma_load_4d(kd + kKvPanel, &map_k, bar(B_KFULL + s), 64, hk, i * kBN, b);
+          load_tile(sbase + SmemLayout::k + s * kKvBytes, bar(B_KFULL + s), &map_k, &map_kp, i);
           if (!mbar_wait(bar(B_VEMPTY + s), par ^ 1, s_abort, p.status, 102)) break;
           mbar_expect_tx(bar(B_VFULL + s), kKvBytes);
-          const uint32_t vd = sbase + SmemLayout::v + s * kKvBytes;
-          tma_load_4d(vd, &map_v, bar(B_VFULL + s), 0, hk, i * kBN, b);
-          tma_load_4d(vd + kKvPanel, &map_v, bar(B_VFULL + s), 64, hk, i * kBN, b);
+          load_tile(sbase + SmemLayout::v + s * kKvBytes, bar(B_VFULL + s), &map_v, &map_vp, i);
         }
       }
     } else if (warp == 5) {
@@ -376,8 +470,28 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const float cap = p.softcap;
       const float c = kSoftcap ? kLog2e : p.sm_scale * kLog2e;   // multiplies the raw (or capped) score
       const float pre = kSoftcap ? p.sm_scale / cap : 0.f;
-      const int q_idx = m0 + row;
-      const int key_limit = p.is_causal ? q_idx + off : 0x7fffffff;  // last visible key of this row
+      const int q_idx = m0 + row;                           // row inside its batch element / request
+      const int causal_limit = p.is_causal ? q_idx + off : 0x7fffffff;  // last visible key of this row
+      int key_limit = causal_limit, seg_len = kv_len;       // of the segment the current tile belongs to
+
+      if (kPaged && p.k_pages != nullptr && h % (p.heads / p.heads_kv) == 0) {
+        // Append this tile's new K/V rows of KV head hk to the pages.  16 bytes per thread and step;
+        // consecutive threads cover one row, so loads and stores are coalesced.
+        constexpr int kChunks = kHD * 2 / 16;
+        const int rows = min(kBM, q_len - m0);
+        const size_t row_bytes = size_t(p.heads_kv) * kHD * 2;
+        for (int idx = tid; idx < rows * kChunks; idx += 128) {
+          const int r = idx / kChunks, ch = idx % kChunks;
+          const int pos = old_len + m0 + r;
+          const int page = p.bt[(long long)b * p.bt_stride + (pos >> p.page_shift)];
+          const size_t dst = (size_t(page) * p.page_size + (pos & (p.page_size - 1))) * row_bytes + size_t(hk) * kHD * 2 + ch * 16;
+          const size_t src = size_t(q_row0 + r) * row_bytes + size_t(hk) * kHD * 2 + ch * 16;
+          const uint4 kk = *reinterpret_cast<const uint4*>(static_cast<const char*>(p.k_new) + src);
+          const uint4 vv = *reinterpret_cast<const uint4*>(static_cast<const char*>(p.v_new) + src);
+          *reinterpret_cast<uint4*>(static_cast<char*>(p.k_pages) + dst) = kk;
+          *reinterpret_cast<uint4*>(static_cast<char*>(p.v_pages) + dst) = vv;
+        }
+      }
       const uint32_t s_addr0 = tmem + lane_addr + kColS;
       const uint32_t o_addr = tmem + lane_addr + kColO;
       float m_run = -INFINITY, l_run = 0.f;   // m_run: the maximum O and l are currently scaled to
@@ -395,7 +509,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             const int key = key0 + e;
-            if (key > key_limit || key >= p.seqlen_kv) r[e] = 0xff800000u;   // -inf
+            if (key > key_limit || key >= seg_len) r[e] = 0xff800000u;   // -inf
           }
         }
       };
@@ -407,8 +521,16 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (!__all_sync(0xffffffffu, mbar_wait(bar(B_SFULL + sb), (j >> 1) & 1, s_abort, p.status, 301))) { ok = false; break; }
         tc_fence_after();
         if (tid == 0) TB200_STAMP(4, j);
-        const int k0 = j * kBN;
-        const bool need_mask = (p.is_causal && k0 + kBN - 1 > m0 + off) || (k0 + kBN > p.seqlen_kv);
+        int k0 = j * kBN;                                   // first key of the tile inside its segment
+        bool need_mask;
+        if (kPaged && j < n_old) {
+          key_limit = 0x7fffffff; seg_len = old_len;        // cached tokens: visible to every row
+          need_mask = k0 + kBN > old_len;
+        } else {
+          k0 -= n_old * kBN;
+          key_limit = causal_limit; seg_len = kv_len;
+          need_mask = (p.is_causal && k0 + kBN - 1 > m0 + off) || (k0 + kBN > kv_len);
+        }
 
         // ---- pass 1: row maximum.  TMEM loads are asynchronous: the next 32 columns are in flight
         // while the maximum of the current 32 is taken. ----
@@ -446,7 +568,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (!__all_sync(0xffffffffu, mbar_wait(bar(B_ODONE), (j - 1) & 1, s_abort, p.status, 302))) { ok = false; break; }
             tc_fence_after();
 #pragma unroll
-            for (int cgi = 0; cgi < 4; ++cgi) {
+            for (int cgi = 0; cgi < kHD / 32; ++cgi) {
               uint32_t ov[32];
               tc_ld32(o_addr + cgi * 32, ov);
               tc_wait_ld(ov);
@@ -462,6 +584,10 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
         // ---- pass 2: p = 2^(s*c - m*c), row sum, P (16-bit) over the first 64 columns of S ----
         float lsum0 = 0.f, lsum1 = 0.f;
+#if TB200_PF_F32X2
+        uint64_t lsum_a = 0, lsum_b = 0;                    // two (even key, odd key) pairs of partial sums
+        const uint64_t c2 = f2_pack(c, c), neg_mc2 = f2_pack(neg_mc, neg_mc);
+#endif
         // Two tuning switches, both off: they measured slower or neutral on B200 (this pass is
         // bound by instruction latency, not by the MUFU pipe).  TB200_PF_POLY evaluates every second
         // exponential on the FMA pipe on tiles without masked entries.  TB200_PF_TRUNC packs bf16 P
@@ -474,12 +600,20 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           uint32_t pk[16];
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
+#if TB200_PF_F32X2
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1])), c2, neg_mc2), x0, x1);
+            const float p0 = fast_exp2(x0);
+            const float p1 = fast_exp2(x1);
+            if (e & 1) lsum_b = f2_add(lsum_b, f2_pack(p0, p1)); else lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
+#else
             const float x0 = fmaf(__uint_as_float(r[2 * e]), c, neg_mc);
             const float x1 = fmaf(__uint_as_float(r[2 * e + 1]), c, neg_mc);
             const float p0 = fast_exp2(x0);
             const float p1 = (kMasked || !TB200_PF_POLY) ? fast_exp2(x1) : exp2_poly(x1);
             lsum0 += p0;
             lsum1 += p1;
+#endif
             if constexpr (kBf16)
               pk[e] = prmt(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
             else
@@ -497,8 +631,27 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           chunk_exp(r1, 1, masked);
         };
         if (need_mask) pass2(std::true_type{}); else pass2(std::false_type{});
+#if TB200_PF_F32X2
+        f2_unpack(f2_add(lsum_a, lsum_b), lsum0, lsum1);
+#endif
         l_run += lsum0 + lsum1;
         if (tid == 0) TB200_STAMP(7, j);
+        if (kPaged && k0 + kBN > seg_len) {
+          // Ragged last tile of a segment: the V rows behind it are another request's tokens or
+          // unwritten page memory.  Their P is zero, but 0 x NaN is NaN, so clear them before the
+          // MMA reads the tile (whole 128-byte rows: the swizzle permutes only inside a row).
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(B_VFULL + sb), (j >> 1) & 1, s_abort, p.status, 304))) { ok = false; break; }
+          const int first = seg_len - k0;                   // 1 .. 63 valid rows
+          unsigned char* vt = smem + SmemLayout::v + sb * kKvBytes;
+          constexpr int kRowChunks = 128 / 16;
+          for (int idx = tid; idx < (kBN - first) * kRowChunks * (kHD / 64); idx += 128) {
+            const int pn = idx / ((kBN - first) * kRowChunks);
+            const int rem = idx % ((kBN - first) * kRowChunks);
+            *reinterpret_cast<uint4*>(vt + pn * kKvPanel + (first + rem / kRowChunks) * 128 + (rem % kRowChunks) * 16) =
+                make_uint4(0, 0, 0, 0);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(B_PREADY + sb));
@@ -511,13 +664,14 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       if (ok) {
         tc_fence_after();
         const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-        T* orow = reinterpret_cast<T*>(p.o) + ((size_t(b) * p.seqlen_q + q_idx) * p.heads + h) * kHD;
+        T* orow = reinterpret_cast<T*>(p.o) +
+                  ((kPaged ? size_t(q_row0 + row) : size_t(b) * p.seqlen_q + q_idx) * p.heads + h) * kHD;
 #pragma unroll
-        for (int cgi = 0; cgi < 4; ++cgi) {
+        for (int cgi = 0; cgi < kHD / 32; ++cgi) {
           uint32_t ov[32];
           tc_ld32(o_addr + cgi * 32, ov);
           tc_wait_ld(ov);
-          if (q_idx < p.seqlen_q) {
+          if (q_idx < q_len) {
 #pragma unroll
             for (int e = 0; e < 32; e += 8) {
               uint4 w;
@@ -529,19 +683,21 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
           }
         }
-        if (p.lse && q_idx < p.seqlen_q)
-          p.lse[(size_t(b) * p.heads + h) * p.seqlen_q + q_idx] =
+        if (p.lse && q_idx < q_len)   // [batch, heads, seqlen_q], or [heads, total_q] for packed requests
+          p.lse[kPaged ? size_t(h) * p.total_q + q_row0 + row : (size_t(b) * p.heads + h) * p.seqlen_q + q_idx] =
               l_run > 0.f ? m_run * c + log2f(l_run) - kTruncFix : -INFINITY;
       }
     }
   } else if (warp < 4) {
     // the whole row tile is masked: zeros, LSE = -inf
     const int q_idx = m0 + tid;
-    if (q_idx < p.seqlen_q) {
-      T* orow = reinterpret_cast<T*>(p.o) + ((size_t(b) * p.seqlen_q + q_idx) * p.heads + h) * kHD;
+    if (q_idx < q_len) {
+      T* orow = reinterpret_cast<T*>(p.o) +
+                ((kPaged ? size_t(q_row0 + tid) : size_t(b) * p.seqlen_q + q_idx) * p.heads + h) * kHD;
       const uint4 z = make_uint4(0, 0, 0, 0);
       for (int e = 0; e < kHD; e += 8) *reinterpret_cast<uint4*>(orow + e) = z;
-      if (p.lse) p.lse[(size_t(b) * p.heads + h) * p.seqlen_q + q_idx] = -INFINITY;
+      if (p.lse)
+        p.lse[kPaged ? size_t(h) * p.total_q + q_row0 + tid : (size_t(b) * p.heads + h) * p.seqlen_q + q_idx] = -INFINITY;
     }
   }
 
@@ -577,12 +733,13 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [batch, seq, heads, 128] contiguous 16-bit tensor -> 4-D map (d, head, seq, batch), box 64 x 1 x box_rows x 1
-int make_map(CUtensorMap* map, const void* base, int dtype, int batch, int seq, int heads, int box_rows) {
+// [batch, seq, heads, hd] contiguous 16-bit tensor -> 4-D map (d, head, seq, batch), box 64 x 1 x box_rows x 1
+int make_map(CUtensorMap* map, const void* base, int dtype, long long batch, long long seq, int heads, int hd,
+             int box_rows) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) TB200_FAIL(TB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t dims[4] = {cuuint64_t(kHD), cuuint64_t(heads), cuuint64_t(seq), cuuint64_t(batch)};
-  cuuint64_t strides[3] = {cuuint64_t(kHD) * 2, cuuint64_t(heads) * kHD * 2, cuuint64_t(seq) * heads * kHD * 2};
+  cuuint64_t dims[4] = {cuuint64_t(hd), cuuint64_t(heads), cuuint64_t(seq), cuuint64_t(batch)};
+  cuuint64_t strides[3] = {cuuint64_t(hd) * 2, cuuint64_t(heads) * hd * 2, cuuint64_t(seq) * heads * hd * 2};
   cuuint32_t box[4] = {64, 1, cuuint32_t(box_rows), 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, dtype == TB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
@@ -593,18 +750,30 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int batch, int seq, 
   return TB200_OK;
 }
 
-template <typename T, bool kSoftcap>
-int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p,
-                   cudaStream_t stream) {
-  auto kern = gqa_prefill_kernel<T, kSoftcap>;
-  const int smem = SmemLayout::total + 1024;
+struct PrefillMaps {
+  CUtensorMap q, k, v, kp, vp;
+};
+
+template <typename T, bool kSoftcap, int HD, bool kPaged>
+int launch_prefill(const PrefillMaps& m, const PrefillParams& p, cudaStream_t stream) {
+  auto kern = gqa_prefill_kernel<T, kSoftcap, HD, kPaged>;
+  const int smem = SmemLayoutT<HD>::total + 1024;
   TB200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int n_m = (p.seqlen_q + kBM - 1) / kBM;
   const long long grid = (long long)n_m * p.heads * p.batch;
   if (grid > 0x7fffffffLL) TB200_FAIL(TB200_ERR_UNSUPPORTED, "problem too large for one launch");
-  kern<<<unsigned(grid), kThreads, smem, stream>>>(mq, mk, mv, p);
+  kern<<<unsigned(grid), kThreads, smem, stream>>>(m.q, m.k, m.v, m.kp, m.vp, p);
   TB200_CUDA_CHECK(cudaGetLastError());
   return TB200_OK;
+}
+
+template <int HD, bool kPaged>
+int dispatch_prefill(int dtype, const PrefillMaps& m, const PrefillParams& p, cudaStream_t s) {
+  if (p.softcap > 0.f)
+    return dtype == TB200_BF16 ? launch_prefill<__nv_bfloat16, true, HD, kPaged>(m, p, s)
+                               : launch_prefill<__half, true, HD, kPaged>(m, p, s);
+  return dtype == TB200_BF16 ? launch_prefill<__nv_bfloat16, false, HD, kPaged>(m, p, s)
+                             : launch_prefill<__half, false, HD, kPaged>(m, p, s);
 }
 
 }  // namespace
@@ -626,7 +795,8 @@ extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, vo
   if (batch <= 0 || seqlen_q <= 0 || seqlen_kv <= 0 || heads <= 0 || heads_kv <= 0)
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "batch, seqlen_q, seqlen_kv, heads and heads_kv must be positive");
   if (heads % heads_kv != 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "heads must be divisible by heads_kv");
-  if (dim != kHD) TB200_FAIL(TB200_ERR_UNSUPPORTED, "head dim %d (the tcgen05 prefill kernel serves 128)", dim);
+  if (dim != 128 && dim != 64)
+    TB200_FAIL(TB200_ERR_UNSUPPORTED, "head dim %d (the tcgen05 prefill kernel serves 64 and 128)", dim);
   if (dtype != TB200_BF16 && dtype != TB200_F16) TB200_FAIL(TB200_ERR_UNSUPPORTED, "dtype must be F16 or BF16");
   if (!(sm_scale > 0.f)) TB200_FAIL(TB200_ERR_UNSUPPORTED, "sm_scale must be positive");
   if (softcap < 0.f) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "softcap must be non-negative");
@@ -635,20 +805,76 @@ extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, vo
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k, v and o must be 16-byte aligned");
   if (!workspace || workspace_bytes < 256 + 8192) TB200_FAIL(TB200_ERR_WORKSPACE, "workspace must hold 8448 bytes");
 
-  CUtensorMap mq, mk, mv;
+  PrefillMaps m;
   int st;
-  if ((st = make_map(&mq, q, dtype, batch, seqlen_q, heads, kBM)) != TB200_OK) return st;
-  if ((st = make_map(&mk, k, dtype, batch, seqlen_kv, heads_kv, kBN)) != TB200_OK) return st;
-  if ((st = make_map(&mv, v, dtype, batch, seqlen_kv, heads_kv, kBN)) != TB200_OK) return st;
+  if ((st = make_map(&m.q, q, dtype, batch, seqlen_q, heads, dim, kBM)) != TB200_OK) return st;
+  if ((st = make_map(&m.k, k, dtype, batch, seqlen_kv, heads_kv, dim, kBN)) != TB200_OK) return st;
+  if ((st = make_map(&m.v, v, dtype, batch, seqlen_kv, heads_kv, dim, kBN)) != TB200_OK) return st;
+  m.kp = m.k;
+  m.vp = m.v;
 
   PrefillParams p{};
   p.o = o; p.lse = lse; p.status = static_cast<int*>(workspace);
   p.batch = batch; p.heads = heads; p.heads_kv = heads_kv; p.seqlen_q = seqlen_q; p.seqlen_kv = seqlen_kv;
   p.is_causal = is_causal; p.sm_scale = sm_scale; p.softcap = softcap;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (softcap > 0.f)
-    return dtype == TB200_BF16 ? launch_prefill<__nv_bfloat16, true>(mq, mk, mv, p, s)
-                               : launch_prefill<__half, true>(mq, mk, mv, p, s);
-  return dtype == TB200_BF16 ? launch_prefill<__nv_bfloat16, false>(mq, mk, mv, p, s)
-                             : launch_prefill<__half, false>(mq, mk, mv, p, s);
+  return dim == 128 ? dispatch_prefill<128, false>(dtype, m, p, s) : dispatch_prefill<64, false>(dtype, m, p, s);
+}
+
+extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const void* v_new, void* k_pages,
+                                       void* v_pages, void* o, float* lse, const int32_t* cu_seqlens_q,
+                                       const int32_t* cache_seqlens, const int32_t* block_table,
+                                       int64_t block_table_stride, int dtype, int total_q, int batch,
+                                       int max_seqlen_q, int heads, int heads_kv, int dim, int page_size,
+                                       int64_t pool_tokens, int is_causal, float sm_scale, float softcap,
+                                       void* workspace, size_t workspace_bytes, void* stream) {
+  if (!q || !k_new || !v_new || !o || !cu_seqlens_q)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k_new, v_new, o and cu_seqlens_q must be non-null");
+  if (total_q <= 0 || batch <= 0 || max_seqlen_q <= 0 || heads <= 0 || heads_kv <= 0)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "total_q, batch, max_seqlen_q, heads and heads_kv must be positive");
+  if (heads % heads_kv != 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "heads must be divisible by heads_kv");
+  if (dim != 128 && dim != 64)
+    TB200_FAIL(TB200_ERR_UNSUPPORTED, "head dim %d (the tcgen05 prefill kernel serves 64 and 128)", dim);
+  if (dtype != TB200_BF16 && dtype != TB200_F16) TB200_FAIL(TB200_ERR_UNSUPPORTED, "dtype must be F16 or BF16");
+  if (!(sm_scale > 0.f)) TB200_FAIL(TB200_ERR_UNSUPPORTED, "sm_scale must be positive");
+  if (softcap < 0.f) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "softcap must be non-negative");
+  const bool has_cache = k_pages != nullptr || v_pages != nullptr || cache_seqlens != nullptr;
+  if (has_cache) {
+    if (!k_pages || !v_pages || !cache_seqlens || !block_table)
+      TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "k_pages, v_pages, cache_seqlens and block_table come together");
+    if (page_size < 16 || (page_size & (page_size - 1)) != 0)
+      TB200_FAIL(TB200_ERR_UNSUPPORTED, "page_size %d (a power of two >= 16 is served)", page_size);
+    if (pool_tokens <= 0 || pool_tokens % page_size != 0)
+      TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "pool_tokens must be a positive multiple of page_size");
+    if (block_table_stride <= 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "block_table_stride must be positive");
+  }
+  uintptr_t bits = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_new) |
+                   reinterpret_cast<uintptr_t>(v_new) | reinterpret_cast<uintptr_t>(o) |
+                   reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages);
+  if (bits & 15) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k_new, v_new, k_pages, v_pages and o must be 16-byte aligned");
+  if (!workspace || workspace_bytes < 256 + 8192) TB200_FAIL(TB200_ERR_WORKSPACE, "workspace must hold 8448 bytes");
+
+  PrefillMaps m;
+  int st;
+  if ((st = make_map(&m.q, q, dtype, 1, total_q, heads, dim, kBM)) != TB200_OK) return st;
+  if ((st = make_map(&m.k, k_new, dtype, 1, total_q, heads_kv, dim, kBN)) != TB200_OK) return st;
+  if ((st = make_map(&m.v, v_new, dtype, 1, total_q, heads_kv, dim, kBN)) != TB200_OK) return st;
+  m.kp = m.k;
+  m.vp = m.v;
+  PrefillParams p{};
+  if (has_cache) {
+    p.page_box = page_size < kBN ? page_size : kBN;
+    if ((st = make_map(&m.kp, k_pages, dtype, 1, pool_tokens, heads_kv, dim, p.page_box)) != TB200_OK) return st;
+    if ((st = make_map(&m.vp, v_pages, dtype, 1, pool_tokens, heads_kv, dim, p.page_box)) != TB200_OK) return st;
+    p.page_size = page_size;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page_size) ++p.page_shift;
+  }
+  p.o = o; p.lse = lse; p.status = static_cast<int*>(workspace);
+  p.batch = batch; p.heads = heads; p.heads_kv = heads_kv; p.seqlen_q = max_seqlen_q; p.seqlen_kv = 0;
+  p.is_causal = is_causal; p.sm_scale = sm_scale; p.softcap = softcap;
+  p.cu_q = cu_seqlens_q; p.cache_lens = cache_seqlens; p.bt = block_table; p.bt_stride = block_table_stride;
+  p.k_new = k_new; p.v_new = v_new; p.k_pages = k_pages; p.v_pages = v_pages; p.total_q = total_q;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return dim == 128 ? dispatch_prefill<128, true>(dtype, m, p, s) : dispatch_prefill<64, true>(dtype, m, p, s);
 }

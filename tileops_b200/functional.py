@@ -224,3 +224,67 @@ def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal:
                                        N.current_stream(q.device))
     N.check(st, "tb200_gqa_prefill")
     return (o, lse) if return_lse else o
+
+
+def gqa_prefill_paged(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
+                      k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                      cu_seqlens_q: torch.Tensor, cache_seqlens: Optional[torch.Tensor],
+                      block_table: Optional[torch.Tensor], max_seqlen_q: int, *, page_size: int = 0,
+                      is_causal: bool = True, sm_scale: Optional[float] = None, softcap: float = 0.0,
+                      return_lse: bool = False):
+    """Packed prefill of one chunk per request over a paged cache, appending the chunk in place.
+
+    q ``[total_q,H,D]``, k_new/v_new ``[total_q,Hkv,D]``, k_pages/v_pages ``[pool_tokens,Hkv,D]``
+    (modified in place), cu_seqlens_q ``[B+1]``, cache_seqlens ``[B]``, block_table ``[B,W]`` (int32)
+    -> o ``[total_q,H,D]`` (+ LSE ``[H,total_q]`` fp32, log2 domain).  With the three cache arguments
+    ``None`` it is the packed varlen prefill without a cache.
+    """
+    _require_cuda(q=q, k_new=k_new, v_new=v_new, cu_seqlens_q=cu_seqlens_q)
+    if q.dim() != 3 or k_new.dim() != 3 or v_new.shape != k_new.shape or k_new.shape[0] != q.shape[0]:
+        raise ValueError("q must be [total_q,H,D] and k_new/v_new [total_q,Hkv,D]")
+    total_q, H, D = q.shape
+    Hkv = k_new.shape[1]
+    if k_new.shape[2] != D or H % Hkv != 0:
+        raise ValueError("head dim must match and heads must be divisible by heads_kv")
+    if k_new.dtype != q.dtype or v_new.dtype != q.dtype:
+        raise ValueError("q/k_new/v_new dtypes must match")
+    if cu_seqlens_q.dtype != torch.int32 or cu_seqlens_q.dim() != 1:
+        raise ValueError("cu_seqlens_q must be a 1-D int32 tensor")
+    B = cu_seqlens_q.numel() - 1
+    has_cache = k_pages is not None
+    pool_tokens, bt_stride = 0, 0
+    if has_cache:
+        if v_pages is None or cache_seqlens is None or block_table is None:
+            raise ValueError("k_pages, v_pages, cache_seqlens and block_table come together")
+        _require_cuda(k_pages=k_pages, v_pages=v_pages, cache_seqlens=cache_seqlens, block_table=block_table)
+        if k_pages.dtype != q.dtype or v_pages.dtype != q.dtype:
+            raise ValueError("k_pages/v_pages must have the dtype of q")
+        if not (k_pages.is_contiguous() and v_pages.is_contiguous()):
+            raise ValueError("k_pages and v_pages must be contiguous (they are written in place)")
+        if k_pages.dim() != 3 or tuple(k_pages.shape[1:]) != (Hkv, D) or v_pages.shape != k_pages.shape:
+            raise ValueError("k_pages/v_pages must be [pool_tokens,Hkv,D]")
+        if cache_seqlens.dtype != torch.int32 or block_table.dtype != torch.int32:
+            raise ValueError("cache_seqlens and block_table must be int32")
+        if cache_seqlens.shape != (B,) or block_table.dim() != 2 or block_table.shape[0] != B:
+            raise ValueError("cache_seqlens must be [B] and block_table [B,W]")
+        if block_table.stride(1) != 1:
+            block_table = block_table.contiguous()
+        pool_tokens, bt_stride = k_pages.shape[0], block_table.stride(0)
+    q, k_new, v_new = q.contiguous(), k_new.contiguous(), v_new.contiguous()
+    cu_seqlens_q = cu_seqlens_q.contiguous()
+    o = torch.empty_like(q)
+    lse = torch.empty((H, total_q), dtype=torch.float32, device=q.device) if return_lse else None
+    if total_q == 0:
+        return (o, lse) if return_lse else o
+    need = N.lib().tb200_gqa_prefill_workspace_bytes(B, H, Hkv, int(max_seqlen_q), 0, D)
+    ws = _prefill_status(q.device, need)
+    scale = D ** -0.5 if sm_scale is None else float(sm_scale)
+    with torch.cuda.device(q.device):
+        st = N.lib().tb200_gqa_prefill_paged(
+            q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), N.ptr(k_pages), N.ptr(v_pages), o.data_ptr(),
+            N.ptr(lse), cu_seqlens_q.data_ptr(), N.ptr(cache_seqlens) if has_cache else None,
+            N.ptr(block_table) if has_cache else None, bt_stride, N.dtype_code(q.dtype), total_q, B,
+            int(max_seqlen_q), H, Hkv, D, int(page_size), pool_tokens, int(bool(is_causal)), scale,
+            float(softcap or 0.0), N.ptr(ws), need, N.current_stream(q.device))
+    N.check(st, "tb200_gqa_prefill_paged")
+    return (o, lse) if return_lse else o

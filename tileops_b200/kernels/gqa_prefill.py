@@ -28,15 +28,15 @@ class GQAPrefillSm100Kernel(Kernel):
 
     @classmethod
     def applies(cls, call) -> bool:
-        return dense_prefill_region(call) and call.dim == 128 and call.dtype in ATTENTION_DTYPES
+        return dense_prefill_region(call) and call.dim in (64, 128) and call.dtype in ATTENTION_DTYPES
 
     def __init__(self, batch, heads, heads_kv, max_seqlen_q, max_seqlen_kv, dim, is_causal, dtype,
                  sm_scale=None, softcap=0.0, window_size_left=-1, window_size_right=-1,
                  accum_dtype=torch.float32, config: Optional[dict] = None, tune: bool = False,
                  device_index=None) -> None:
         super().__init__(device_index=device_index)
-        if dim != 128:
-            raise ValueError(f"GQAPrefillSm100Kernel supports head dim 128, got {dim}")
+        if dim not in (64, 128):
+            raise ValueError(f"GQAPrefillSm100Kernel supports head dim 64 and 128, got {dim}")
         if window_size_left != -1 or window_size_right != -1:
             raise ValueError("GQAPrefillSm100Kernel does not serve sliding-window calls")
         self.batch, self.heads, self.heads_kv, self.dim = batch, heads, heads_kv, dim
@@ -49,7 +49,7 @@ class GQAPrefillSm100Kernel(Kernel):
 
     @property
     def default_config(self) -> dict:
-        return {"block_M": 128, "block_N": 128, "threads": 192}
+        return {"block_M": 128, "block_N": 64, "threads": 192}
 
     def forward(self, q, k, v, cu_seqlens_q=None, cu_seqlens_kv=None, q_scale=None, k_scale=None,
                 v_scale=None, return_lse: bool = False):
