@@ -172,9 +172,13 @@ int tb200_gqa_prefill(const void* q, const void* k, const void* v, void* o, floa
  * GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp, src/tileops/ops/attention/gqa.py:765-1157)
  * and, with the cache arguments NULL, of the packed varlen prefill kernel
  * (src/tileops/kernels/attention/gqa_prefill_varlen_fwd.py; operator
- * GroupedQueryAttentionPrefillVarlenFwdOp, gqa.py:555-762 with equal q and kv lengths):
- *   q [total_q, heads, dim], k_new / v_new [total_q, heads_kv, dim]      dtype (F16 | BF16)
- *   cu_seqlens_q [batch + 1] int32: request b owns rows cu[b] .. cu[b+1]
+ * GroupedQueryAttentionPrefillVarlenFwdOp, gqa.py:555-762):
+ *   q [total_q, heads, dim], k_new / v_new [total_kv, heads_kv, dim]     dtype (F16 | BF16)
+ *   cu_seqlens_q [batch + 1] int32: request b owns rows cu[b] .. cu[b+1] of q and o
+ *   cu_seqlens_kv [batch + 1] int32: its rows of k_new / v_new; NULL (and total_kv = total_q)
+ *   means the same rows as q.  Without a cache the causal mask of a request is bottom-right
+ *   aligned: key j is visible to row i iff j <= i + (kv_len - q_len).  With a cache
+ *   cu_seqlens_kv must be NULL.
  *   k_pages / v_pages [pool_tokens, heads_kv, dim] dtype, cache_seqlens [batch] int32 (tokens
  *   of request b already cached), block_table [batch, block_table_stride] int32
  *   o [total_q, heads, dim] dtype ; lse [heads, total_q] fp32 log2-domain or NULL
@@ -190,9 +194,10 @@ int tb200_gqa_prefill(const void* q, const void* k, const void* v, void* o, floa
  * ------------------------------------------------------------------------- */
 int tb200_gqa_prefill_paged(const void* q, const void* k_new, const void* v_new,
                             void* k_pages, void* v_pages, void* o, float* lse,
-                            const int32_t* cu_seqlens_q, const int32_t* cache_seqlens,
+                            const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_kv,
+                            const int32_t* cache_seqlens,
                             const int32_t* block_table, int64_t block_table_stride,
-                            int dtype, int total_q, int batch, int max_seqlen_q,
+                            int dtype, int total_q, int total_kv, int batch, int max_seqlen_q,
                             int heads, int heads_kv, int dim, int page_size, int64_t pool_tokens,
                             int is_causal, float sm_scale, float softcap,
                             void* workspace, size_t workspace_bytes, void* stream);

@@ -220,6 +220,16 @@ def main():
         "varlen_ragged": F.gqa_prefill_varlen_fwd_roofline(
             q_shape=(40, 4, 32), k_shape=(72, 2, 32), batch=2, max_seqlen_q=24, max_seqlen_kv=50,
             q_lens=[24, 16], kv_lens=[50, 22], is_causal=True, dtype=torch.float16),
+        "paged_prefill_llama8b": F.gqa_prefill_paged_with_kv_cache_fwd_roofline(
+            total_q=4096, batch=8, q_lens=[512] * 8, cache_lens=[4096] * 8, heads=32, heads_kv=8, dim=128,
+            page_size=64, max_pages_per_req=72, max_seqlen_q=512, is_causal=True, dtype=torch.float16),
+        "paged_prefill_mixed": F.gqa_prefill_paged_with_kv_cache_fwd_roofline(
+            total_q=4608, batch=8, q_lens=[256, 512, 768, 1024, 384, 640, 896, 128],
+            cache_lens=[4096, 8192, 16384, 32768, 12288, 24576, 30720, 2048], heads=32, heads_kv=8, dim=128,
+            page_size=64, max_pages_per_req=528, max_seqlen_q=1024, is_causal=True, dtype=torch.bfloat16),
+        "paged_prefill_aggregate_only": F.gqa_prefill_paged_with_kv_cache_fwd_roofline(
+            total_q=2048, batch=4, heads=8, heads_kv=2, dim=64, page_size=64, max_pages_per_req=72,
+            max_seqlen_q=512, is_causal=False, dtype=torch.float16),
     }
     with open(os.path.join(HERE, "roofline_golden.json"), "w") as f:
         json.dump({k: list(map(int, v)) for k, v in roof.items()}, f, indent=1)

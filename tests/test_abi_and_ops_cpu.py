@@ -289,6 +289,79 @@ def test_product_formulas_match_reference_values():
         q_lens=[24, 16], kv_lens=[50, 22], is_causal=True, dtype=torch.float16)) == R["varlen_ragged"]
 
 
+def test_paged_prefill_formula_matches_reference_values_and_manifest_workloads():
+    R = json.load(open(os.path.join(ROOT, "tests", "golden", "roofline_golden.json")))
+    F = formulas.gqa_prefill_paged_with_kv_cache_fwd_roofline
+    assert list(F(total_q=4096, batch=8, q_lens=[512] * 8, cache_lens=[4096] * 8, heads=32, heads_kv=8, dim=128,
+                  page_size=64, max_pages_per_req=72, max_seqlen_q=512, is_causal=True,
+                  dtype=torch.float16)) == R["paged_prefill_llama8b"]
+    assert list(F(total_q=4608, batch=8, q_lens=[256, 512, 768, 1024, 384, 640, 896, 128],
+                  cache_lens=[4096, 8192, 16384, 32768, 12288, 24576, 30720, 2048], heads=32, heads_kv=8,
+                  dim=128, page_size=64, max_pages_per_req=528, max_seqlen_q=1024, is_causal=True,
+                  dtype=torch.bfloat16)) == R["paged_prefill_mixed"]
+    assert list(F(total_q=2048, batch=4, heads=8, heads_kv=2, dim=64, page_size=64, max_pages_per_req=72,
+                  max_seqlen_q=512, is_causal=False, dtype=torch.float16)) == R["paged_prefill_aggregate_only"]
+    entry = tileops_b200.manifest.load_manifest()["GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp"]
+    assert entry["roofline"]["func"].endswith("gqa_prefill_paged_with_kv_cache_fwd_roofline")
+    for w in entry["workloads"]:
+        flops, nbytes = F(**w)
+        assert flops > 0 and nbytes > 0 and sum(w["q_lens"]) == w["total_q"]
+
+
+def test_paged_prefill_op_constructor_and_selection_follow_the_reference():
+    from tileops_b200.ops import (GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp as PagedOp,
+                                  GroupedQueryAttentionPrefillVarlenFwdOp as VarlenOp)
+    with pytest.raises(ValueError, match="page_size must be a power of two"):
+        PagedOp(2, 8, 2, 8, 48, 64)
+    with pytest.raises(ValueError, match="max_position is required when fuse_rope=True"):
+        PagedOp(2, 8, 2, 8, 64, 64, fuse_rope=True)
+    with pytest.raises(ValueError, match="rotary_dim requires fuse_rope=True"):
+        PagedOp(2, 8, 2, 8, 64, 64, rotary_dim=32)
+    with pytest.raises(ValueError, match="max_pages_per_req must be positive"):
+        PagedOp(2, 8, 2, 0, 64, 64)
+    op = PagedOp(2, 8, 2, 8, 64, 64, softcap=50.0)
+    assert op.max_cache_len == 512 and op.groups == 4 and op.softcap == 50.0
+    assert list(op.kernel_map) == ["gqa_prefill_paged_with_kv_cache_fwd_kernel"]
+    from tileops_b200.ops.selection import PAGED_PREFILL_KEYS
+    import dataclasses
+
+    def on_sm100(call):   # no GPU in the CPU suite: state the architecture in the call
+        return dataclasses.replace(call, arch=100)
+    assert op.select_kernel_key(PAGED_PREFILL_KEYS, on_sm100(op.attention_call(torch.float16))) == \
+        "gqa_prefill_paged_with_kv_cache_fwd_kernel"
+    # an FP8 cache, fused RoPE, pages below 16 tokens and head dim 256 have no sm_100 implementation
+    for bad in (PagedOp(2, 8, 2, 8, 64, 64, cache_dtype=torch.float8_e4m3fn),
+                PagedOp(2, 8, 2, 8, 64, 64, fuse_rope=True, max_position=512),
+                PagedOp(2, 8, 2, 64, 8, 64), PagedOp(2, 8, 2, 8, 64, 256)):
+        with pytest.raises(ValueError, match="no implementation serves this call"):
+            bad.select_kernel_key(PAGED_PREFILL_KEYS, on_sm100(bad.attention_call(torch.float16)))
+    with pytest.raises(NotImplementedError):
+        op.total_flops
+    q = torch.zeros(4, 8, 64, dtype=torch.float16)
+    with pytest.raises(ValueError, match="q must be on a cuda device"):
+        op(q, q, q, q, q, q, q, q, q, q, 4)
+    v = VarlenOp(2, 8, 2, 64, 128, 256)
+    assert list(v.kernel_map) == ["gqa_prefill_varlen_fwd_kernel"]
+    with pytest.raises(ValueError, match="q must be a CUDA tensor"):
+        v(q, q, q, q, q)
+    with pytest.raises(RuntimeError, match="requires a prior forward"):
+        v.eval_roofline()
+
+
+def test_packed_prefill_op_routes_ragged_requests_to_the_varlen_kernel():
+    from tileops_b200.ops import GroupedQueryAttentionPrefillFwdOp
+    from tileops_b200.ops.selection import PACKED_PREFILL_KEYS
+    import dataclasses
+
+    def call(op, uniform):
+        return dataclasses.replace(op.attention_call(is_fp8=False, is_uniform=uniform), arch=100)
+    op = GroupedQueryAttentionPrefillFwdOp(2, 8, 2, 128, 256, 256, dtype=torch.bfloat16)
+    assert op.select_kernel_key(PACKED_PREFILL_KEYS, call(op, True)) == "gqa_prefill_fwd_kernel"
+    assert op.select_kernel_key(PACKED_PREFILL_KEYS, call(op, False)) == "gqa_prefill_varlen_fwd_kernel"
+    op = GroupedQueryAttentionPrefillFwdOp(2, 8, 2, 128, 256, 256, dtype=torch.bfloat16, backend="varlen")
+    assert op.select_kernel_key(PACKED_PREFILL_KEYS, call(op, True)) == "gqa_prefill_varlen_fwd_kernel"
+
+
 def test_workload_generator_shards_reproduce_the_full_problem():
     from tileops_b200 import workloads as W
     full = W.make_paged_decode(9, 2, 4, 2, 16, 8, lens=[50, 21], dtype=torch.float32, device="cpu")

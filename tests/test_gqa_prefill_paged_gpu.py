@@ -187,3 +187,53 @@ def test_llama8b_chunk_shape_property():
     o_half = F.gqa_prefill_paged(q[idx].cuda(), kn[idx].cuda(), vn[idx].cuda(), kpd, vpd, cu2.cuda(), cache.cuda(),
                                  bt.cuda(), half, page_size=page)
     assert torch.equal(o_half.cpu(), o.cpu()[idx])
+
+
+# ---- through the operator classes (the reference's call shape) ------------------------------------
+
+def test_paged_op_like_the_reference_test():
+    from tileops_b200.ops import GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp
+    q_lens, old_lens, heads, heads_kv, dim, page, W = [17, 33], [37, 100], 8, 2, 64, 64, 8
+    for dtype in (torch.float16, torch.bfloat16):   # one instance serves both element types
+        case = _case(q_lens, old_lens, heads, heads_kv, dim, page, dtype, pages_per_req=W, seed=20)
+        ref_o, ref_kp, ref_vp = O.prefill_paged_ref(*case, page, is_causal=True)
+        q, kn, vn, kp, vp, cu, cache, bt = (x.cuda() for x in case)
+        op = GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp(
+            batch=2, heads=heads, heads_kv=heads_kv, max_pages_per_req=W, page_size=page, dim=dim)
+        one = torch.ones(1, device="cuda")
+        o = op(q, kn, vn, kp, vp, one, one.clone(), cu, cache, bt, max(q_lens))
+        assert isinstance(o, torch.Tensor) and o.shape == q.shape and o.dtype == dtype
+        torch.testing.assert_close(o.cpu().float(), ref_o.float(), **TOL[dtype])
+        assert torch.equal(kp.cpu().view(torch.int16), ref_kp.view(torch.int16))
+        assert torch.equal(vp.cpu().view(torch.int16), ref_vp.view(torch.int16))
+        with pytest.raises(ValueError, match="exceeds paged KV capacity"):
+            op(q, kn, vn, kp, vp, one, one, cu, cache + 450, bt, max(q_lens))
+        with pytest.raises(ValueError, match="block_table references page"):
+            op(q, kn, vn, kp, vp, one, one, cu, cache, bt + 100, max(q_lens))
+        with pytest.raises(ValueError, match="max_seqlen_q"):
+            op(q, kn, vn, kp, vp, one, one, cu, cache, bt, 8)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_varlen_op_with_longer_kv(causal):
+    from tileops_b200.ops import GroupedQueryAttentionPrefillFwdOp, GroupedQueryAttentionPrefillVarlenFwdOp
+    g = torch.Generator().manual_seed(21)
+    q_lens, kv_lens, H, Hkv, D = [24, 130, 1, 257], [50, 130, 300, 400], 8, 2, 128
+    cu_q = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(np.cumsum(kv_lens)), dtype=torch.int32)
+    q = torch.randn(sum(q_lens), H, D, generator=g).bfloat16()
+    k = torch.randn(sum(kv_lens), Hkv, D, generator=g).bfloat16()
+    v = torch.randn(sum(kv_lens), Hkv, D, generator=g).bfloat16()
+    ref = O.prefill_packed_ref(q, k, v, cu_q, cu_k, is_causal=causal)
+    op = GroupedQueryAttentionPrefillVarlenFwdOp(4, H, Hkv, D, max(q_lens), max(kv_lens), is_causal=causal,
+                                                 validate_inputs=True)
+    o = op(q.cuda(), k.cuda(), v.cuda(), cu_q.cuda(), cu_k.cuda())
+    torch.testing.assert_close(o.cpu().float(), ref.float(), **TOL[torch.bfloat16])
+    flops, nbytes = op.eval_roofline()
+    assert flops > 0 and nbytes > 0
+    # the canonical packed op reaches the same kernel when the request is ragged
+    op2 = GroupedQueryAttentionPrefillFwdOp(4, H, Hkv, D, max(q_lens), max(kv_lens), dtype=torch.bfloat16,
+                                            is_causal=causal)
+    ones = torch.ones(4, Hkv, device="cuda")
+    o2 = op2(q.cuda(), k.cuda(), v.cuda(), cu_q.cuda(), cu_k.cuda(), ones, ones.clone(), ones.clone())
+    assert torch.equal(o2, o)

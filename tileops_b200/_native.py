@@ -54,8 +54,8 @@ SIGNATURES = {
         c_float, c_float, c_void_p, c_size_t, c_void_p]),
     "tb200_gqa_prefill_paged": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # q k_new v_new k_pages v_pages o lse
-        c_void_p, c_void_p, c_void_p, c_int64,                  # cu_seqlens_q cache_seqlens block_table stride
-        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int,  # dtype total_q B maxq H Hkv D page pool causal
+        c_void_p, c_void_p, c_void_p, c_void_p, c_int64,        # cu_seqlens_q cu_seqlens_kv cache_seqlens block_table stride
+        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int,  # dtype total_q total_kv B maxq H Hkv D page pool causal
         c_float, c_float, c_void_p, c_size_t, c_void_p]),
 }
 

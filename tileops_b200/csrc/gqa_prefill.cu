@@ -104,7 +104,8 @@ struct PrefillParams {
   int is_causal;
   float sm_scale, softcap;
   // packed (ragged) queries over a paged cache; unused by the dense kernel
-  const int32_t* cu_q;         // [batch + 1] row offsets of the requests in q / k_new / v_new / o
+  const int32_t* cu_q;         // [batch + 1] row offsets of the requests in q / o (and k_new / v_new)
+  const int32_t* cu_kv;        // [batch + 1] row offsets in k_new / v_new when they differ from cu_q, or null
   const int32_t* cache_lens;   // [batch] tokens already in the pages (null: none)
   const int32_t* bt;           // [batch, bt_stride] logical page -> physical page
   long long bt_stride;
@@ -317,16 +318,17 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const int m0 = mt * kBM;
   // rows of this tile in the q / o tensors, and where the (new) K/V segment starts
   int q_row0 = m0, q_batch = b, q_len = p.seqlen_q, kv_len = p.seqlen_kv, old_len = 0;
+  int kv_row0 = 0;                                         // row of the (new) segment's first key
   if (kPaged) {
     const int q0 = p.cu_q[b];
     q_len = p.cu_q[b + 1] - q0;
     if (m0 >= q_len) return;                               // the whole CTA: nothing allocated yet
-    kv_len = q_len;
+    kv_row0 = p.cu_kv ? p.cu_kv[b] : q0;
+    kv_len = p.cu_kv ? p.cu_kv[b + 1] - kv_row0 : q_len;
     old_len = p.cache_lens ? p.cache_lens[b] : 0;
     q_row0 = q0 + m0;
     q_batch = 0;
   }
-  const int kv_row0 = q_row0 - m0;                         // row of the segment's first key (0 when dense)
   const int off = kv_len - q_len;                          // bottom-right alignment (0 when paged)
   const int n_old = (old_len + kBN - 1) / kBN;             // tiles of cached tokens (0 when dense)
   int n_new = (kv_len + kBN - 1) / kBN;
@@ -823,15 +825,16 @@ extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, vo
 
 extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const void* v_new, void* k_pages,
                                        void* v_pages, void* o, float* lse, const int32_t* cu_seqlens_q,
-                                       const int32_t* cache_seqlens, const int32_t* block_table,
-                                       int64_t block_table_stride, int dtype, int total_q, int batch,
-                                       int max_seqlen_q, int heads, int heads_kv, int dim, int page_size,
+                                       const int32_t* cu_seqlens_kv, const int32_t* cache_seqlens,
+                                       const int32_t* block_table, int64_t block_table_stride, int dtype,
+                                       int total_q, int total_kv, int batch, int max_seqlen_q, int heads,
+                                       int heads_kv, int dim, int page_size,
                                        int64_t pool_tokens, int is_causal, float sm_scale, float softcap,
                                        void* workspace, size_t workspace_bytes, void* stream) {
   if (!q || !k_new || !v_new || !o || !cu_seqlens_q)
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k_new, v_new, o and cu_seqlens_q must be non-null");
-  if (total_q <= 0 || batch <= 0 || max_seqlen_q <= 0 || heads <= 0 || heads_kv <= 0)
-    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "total_q, batch, max_seqlen_q, heads and heads_kv must be positive");
+  if (total_q <= 0 || total_kv <= 0 || batch <= 0 || max_seqlen_q <= 0 || heads <= 0 || heads_kv <= 0)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "total_q, total_kv, batch, max_seqlen_q, heads and heads_kv must be positive");
   if (heads % heads_kv != 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "heads must be divisible by heads_kv");
   if (dim != 128 && dim != 64)
     TB200_FAIL(TB200_ERR_UNSUPPORTED, "head dim %d (the tcgen05 prefill kernel serves 64 and 128)", dim);
@@ -839,6 +842,10 @@ extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const v
   if (!(sm_scale > 0.f)) TB200_FAIL(TB200_ERR_UNSUPPORTED, "sm_scale must be positive");
   if (softcap < 0.f) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "softcap must be non-negative");
   const bool has_cache = k_pages != nullptr || v_pages != nullptr || cache_seqlens != nullptr;
+  if (has_cache && (cu_seqlens_kv != nullptr || total_kv != total_q))
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "with a cache, k_new / v_new hold exactly the rows of q (cu_seqlens_kv must be null)");
+  if (!cu_seqlens_kv && total_kv != total_q)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "total_kv differs from total_q but cu_seqlens_kv is null");
   if (has_cache) {
     if (!k_pages || !v_pages || !cache_seqlens || !block_table)
       TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "k_pages, v_pages, cache_seqlens and block_table come together");
@@ -857,8 +864,8 @@ extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const v
   PrefillMaps m;
   int st;
   if ((st = make_map(&m.q, q, dtype, 1, total_q, heads, dim, kBM)) != TB200_OK) return st;
-  if ((st = make_map(&m.k, k_new, dtype, 1, total_q, heads_kv, dim, kBN)) != TB200_OK) return st;
-  if ((st = make_map(&m.v, v_new, dtype, 1, total_q, heads_kv, dim, kBN)) != TB200_OK) return st;
+  if ((st = make_map(&m.k, k_new, dtype, 1, total_kv, heads_kv, dim, kBN)) != TB200_OK) return st;
+  if ((st = make_map(&m.v, v_new, dtype, 1, total_kv, heads_kv, dim, kBN)) != TB200_OK) return st;
   m.kp = m.k;
   m.vp = m.v;
   PrefillParams p{};
@@ -873,7 +880,7 @@ extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const v
   p.o = o; p.lse = lse; p.status = static_cast<int*>(workspace);
   p.batch = batch; p.heads = heads; p.heads_kv = heads_kv; p.seqlen_q = max_seqlen_q; p.seqlen_kv = 0;
   p.is_causal = is_causal; p.sm_scale = sm_scale; p.softcap = softcap;
-  p.cu_q = cu_seqlens_q; p.cache_lens = cache_seqlens; p.bt = block_table; p.bt_stride = block_table_stride;
+  p.cu_q = cu_seqlens_q; p.cu_kv = cu_seqlens_kv; p.cache_lens = cache_seqlens; p.bt = block_table; p.bt_stride = block_table_stride;
   p.k_new = k_new; p.v_new = v_new; p.k_pages = k_pages; p.v_pages = v_pages; p.total_q = total_q;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return dim == 128 ? dispatch_prefill<128, true>(dtype, m, p, s) : dispatch_prefill<64, true>(dtype, m, p, s);

@@ -231,17 +231,27 @@ def gqa_prefill_paged(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
                       cu_seqlens_q: torch.Tensor, cache_seqlens: Optional[torch.Tensor],
                       block_table: Optional[torch.Tensor], max_seqlen_q: int, *, page_size: int = 0,
                       is_causal: bool = True, sm_scale: Optional[float] = None, softcap: float = 0.0,
-                      return_lse: bool = False):
+                      return_lse: bool = False, cu_seqlens_kv: Optional[torch.Tensor] = None):
     """Packed prefill of one chunk per request over a paged cache, appending the chunk in place.
 
     q ``[total_q,H,D]``, k_new/v_new ``[total_q,Hkv,D]``, k_pages/v_pages ``[pool_tokens,Hkv,D]``
     (modified in place), cu_seqlens_q ``[B+1]``, cache_seqlens ``[B]``, block_table ``[B,W]`` (int32)
     -> o ``[total_q,H,D]`` (+ LSE ``[H,total_q]`` fp32, log2 domain).  With the three cache arguments
-    ``None`` it is the packed varlen prefill without a cache.
+    ``None`` it is the packed varlen prefill without a cache; only then may ``cu_seqlens_kv``
+    give k_new/v_new their own row ranges (bottom-right aligned causal mask per request).
     """
     _require_cuda(q=q, k_new=k_new, v_new=v_new, cu_seqlens_q=cu_seqlens_q)
-    if q.dim() != 3 or k_new.dim() != 3 or v_new.shape != k_new.shape or k_new.shape[0] != q.shape[0]:
-        raise ValueError("q must be [total_q,H,D] and k_new/v_new [total_q,Hkv,D]")
+    if q.dim() != 3 or k_new.dim() != 3 or v_new.shape != k_new.shape:
+        raise ValueError("q must be [total_q,H,D] and k_new/v_new [total_kv,Hkv,D]")
+    if cu_seqlens_kv is None and k_new.shape[0] != q.shape[0]:
+        raise ValueError("k_new/v_new must have the rows of q unless cu_seqlens_kv is given")
+    if cu_seqlens_kv is not None:
+        if k_pages is not None:
+            raise ValueError("cu_seqlens_kv cannot be combined with a cache")
+        _require_cuda(cu_seqlens_kv=cu_seqlens_kv)
+        if cu_seqlens_kv.dtype != torch.int32 or cu_seqlens_kv.shape != cu_seqlens_q.shape:
+            raise ValueError("cu_seqlens_kv must be int32 with the shape of cu_seqlens_q")
+        cu_seqlens_kv = cu_seqlens_kv.contiguous()
     total_q, H, D = q.shape
     Hkv = k_new.shape[1]
     if k_new.shape[2] != D or H % Hkv != 0:
@@ -282,8 +292,9 @@ def gqa_prefill_paged(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
     with torch.cuda.device(q.device):
         st = N.lib().tb200_gqa_prefill_paged(
             q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), N.ptr(k_pages), N.ptr(v_pages), o.data_ptr(),
-            N.ptr(lse), cu_seqlens_q.data_ptr(), N.ptr(cache_seqlens) if has_cache else None,
-            N.ptr(block_table) if has_cache else None, bt_stride, N.dtype_code(q.dtype), total_q, B,
+            N.ptr(lse), cu_seqlens_q.data_ptr(), N.ptr(cu_seqlens_kv), N.ptr(cache_seqlens) if has_cache else None,
+            N.ptr(block_table) if has_cache else None, bt_stride, N.dtype_code(q.dtype), total_q,
+            k_new.shape[0], B,
             int(max_seqlen_q), H, Hkv, D, int(page_size), pool_tokens, int(bool(is_causal)), scale,
             float(softcap or 0.0), N.ptr(ws), need, N.current_stream(q.device))
     N.check(st, "tb200_gqa_prefill_paged")

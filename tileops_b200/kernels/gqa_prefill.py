@@ -19,7 +19,7 @@ from .. import functional as F
 from .call_spec import ATTENTION_DTYPES, dense_prefill_region
 from .kernel_base import Kernel
 
-__all__ = ["GQAPrefillSm100Kernel"]
+__all__ = ["GQAPrefillSm100Kernel", "GQAPrefillVarlenSm100Kernel", "GQAPrefillPagedSm100Kernel"]
 
 
 class GQAPrefillSm100Kernel(Kernel):
@@ -65,3 +65,106 @@ class GQAPrefillSm100Kernel(Kernel):
         if return_lse:
             return out[0].view(q.shape), out[1]
         return out.view(q.shape)
+
+
+def varlen_prefill_region(call) -> bool:
+    """Non-FP8, non-windowed packed prefill that is ragged or asked for as 'varlen'."""
+    from .call_spec import uses_sliding_window
+    if call.is_fp8 or uses_sliding_window(call):
+        return False
+    return call.backend == "varlen" or (call.backend == "auto" and not call.is_uniform)
+
+
+class GQAPrefillVarlenSm100Kernel(Kernel):
+    """Ragged packed prefill in the ``gqa_prefill_varlen_fwd_kernel`` slot.
+
+    Replaces the reference's ``GQAPrefillVarlenFwdKernel``
+    (``src/tileops/kernels/attention/gqa_prefill_varlen_fwd.py``): per request, keys
+    ``cu_seqlens_kv[b] .. cu_seqlens_kv[b+1]`` with a bottom-right aligned causal mask.  Runs the
+    tcgen05 prefill kernel in its packed mode (``tb200_gqa_prefill_paged`` without a cache).
+    """
+
+    supported_archs = [100]
+    general = True
+
+    @classmethod
+    def applies(cls, call) -> bool:
+        return varlen_prefill_region(call) and call.dim in (64, 128) and call.dtype in ATTENTION_DTYPES
+
+    def __init__(self, batch, heads, heads_kv, max_seqlen_q, max_seqlen_kv, dim, is_causal, dtype,
+                 sm_scale=None, softcap=0.0, window_size_left=-1, window_size_right=-1,
+                 accum_dtype=torch.float32, config: Optional[dict] = None, tune: bool = False,
+                 device_index=None) -> None:
+        super().__init__(device_index=device_index)
+        if dim not in (64, 128):
+            raise ValueError(f"GQAPrefillVarlenSm100Kernel supports head dim 64 and 128, got {dim}")
+        if window_size_left != -1 or window_size_right != -1:
+            raise ValueError("GQAPrefillVarlenSm100Kernel does not serve sliding-window calls")
+        self.batch, self.heads, self.heads_kv, self.dim = batch, heads, heads_kv, dim
+        self.max_seqlen_q, self.max_seqlen_kv = max_seqlen_q, max_seqlen_kv
+        self.is_causal, self.dtype = is_causal, dtype
+        self.sm_scale = dim ** -0.5 if sm_scale is None else sm_scale
+        self.softcap = 0.0 if softcap is None else softcap
+        self.tune = tune
+        self.init_config(config, tune)
+
+    @property
+    def default_config(self) -> dict:
+        return {"block_M": 128, "block_N": 64, "threads": 192}
+
+    def forward(self, q, k, v, cu_seqlens_q, cu_seqlens_kv, q_scale=None, k_scale=None, v_scale=None,
+                return_lse: bool = False):
+        """q ``[total_q,H,D]``, k/v ``[total_kv,Hkv,D]`` -> o ``[total_q,H,D]`` (+ LSE ``[H,total_q]``)."""
+        self._require_cuda(q=q, k=k, v=v, cu_seqlens_q=cu_seqlens_q, cu_seqlens_kv=cu_seqlens_kv)
+        return F.gqa_prefill_paged(q, k, v, None, None, cu_seqlens_q, None, None, self.max_seqlen_q,
+                                   is_causal=self.is_causal, sm_scale=self.sm_scale, softcap=self.softcap,
+                                   return_lse=return_lse, cu_seqlens_kv=cu_seqlens_kv)
+
+
+class GQAPrefillPagedSm100Kernel(Kernel):
+    """Packed prefill over a paged cache with in-place append, in the
+    ``gqa_prefill_paged_with_kv_cache_fwd_kernel`` slot.
+
+    Replaces the reference's ``GQAPrefillPagedWithKVCacheFwdKernel``
+    (``src/tileops/kernels/attention/gqa_fwd.py:600-1002``); same keyword constructor and
+    positional ``forward`` (``src/tileops/ops/attention/gqa.py:866-893,1100-1140``).  The cache has
+    the element type of q (the FP8-cache and fused-RoPE slots are not served), so ``k_scale`` /
+    ``v_scale`` are accepted and unused, as in the reference's same-type kernel.
+    """
+
+    supported_archs = [100]
+    general = True
+
+    @classmethod
+    def applies(cls, call) -> bool:
+        return (call.dtype in ATTENTION_DTYPES and call.dim in (64, 128) and not call.fuse_rope
+                and call.cache_dtype in (None, call.dtype) and call.page_size >= 16)
+
+    def __init__(self, batch, heads, heads_kv, max_pages_per_req, page_size, dim, is_causal, dtype,
+                 sm_scale=None, softcap=0.0, max_position=None, rotary_dim=None,
+                 config: Optional[dict] = None, tune: bool = False, device_index=None) -> None:
+        super().__init__(device_index=device_index)
+        if dim not in (64, 128):
+            raise ValueError(f"GQAPrefillPagedSm100Kernel supports head dim 64 and 128, got {dim}")
+        if page_size < 16 or page_size & (page_size - 1):
+            raise ValueError(f"GQAPrefillPagedSm100Kernel supports power-of-two pages >= 16, got {page_size}")
+        self.batch, self.heads, self.heads_kv, self.dim = batch, heads, heads_kv, dim
+        self.max_pages_per_req, self.page_size = max_pages_per_req, page_size
+        self.is_causal, self.dtype = is_causal, dtype
+        self.sm_scale = dim ** -0.5 if sm_scale is None else sm_scale
+        self.softcap = 0.0 if softcap is None else softcap
+        self.tune = tune
+        self.init_config(config, tune)
+
+    @property
+    def default_config(self) -> dict:
+        return {"block_M": 128, "block_N": 64, "threads": 192}
+
+    def forward(self, q, k_new, v_new, k_pages, v_pages, k_scale, v_scale, cu_seqlens_q, cache_seqlens,
+                block_table, max_seqlen_q, cos_table=None, sin_table=None):
+        self._require_cuda(q=q, k_new=k_new, v_new=v_new, k_pages=k_pages, v_pages=v_pages)
+        if cos_table is not None or sin_table is not None:
+            raise ValueError("GQAPrefillPagedSm100Kernel does not fuse RoPE")
+        return F.gqa_prefill_paged(q, k_new, v_new, k_pages, v_pages, cu_seqlens_q, cache_seqlens,
+                                   block_table, int(max_seqlen_q), page_size=self.page_size,
+                                   is_causal=self.is_causal, sm_scale=self.sm_scale, softcap=self.softcap)

@@ -4,6 +4,8 @@ from .gqa import (
     GroupedQueryAttentionDecodeWithKVCacheFwdOp,
     GroupedQueryAttentionFwdOp,
     GroupedQueryAttentionPrefillFwdOp,
+    GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp,
+    GroupedQueryAttentionPrefillVarlenFwdOp,
 )
 from .op_base import Op
 
@@ -11,6 +13,8 @@ __all__ = [
     "Op",
     "GroupedQueryAttentionFwdOp",
     "GroupedQueryAttentionPrefillFwdOp",
+    "GroupedQueryAttentionPrefillVarlenFwdOp",
+    "GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp",
     "GroupedQueryAttentionDecodeWithKVCacheFwdOp",
     "GroupedQueryAttentionDecodePagedWithKVCacheFwdOp",
     "GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp",

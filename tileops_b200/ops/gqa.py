@@ -26,7 +26,9 @@ from ..kernels import (
     GQADecodePagedFp8Sm100Kernel,
     GQADecodePagedSm100Kernel,
     GQADecodeSm100Kernel,
+    GQAPrefillPagedSm100Kernel,
     GQAPrefillSm100Kernel,
+    GQAPrefillVarlenSm100Kernel,
 )
 from ..kernels.kernel_base import Kernel
 from .op_base import Op
@@ -36,6 +38,7 @@ from .selection import (
     PACKED_PREFILL_KEYS,
     PAGED_DECODE_FP8_KEYS,
     PAGED_DECODE_KEYS,
+    PAGED_PREFILL_KEYS,
     AttentionCall,
     check_packed_prefill_request,
     fp8_dtype,
@@ -44,6 +47,8 @@ from .selection import (
 __all__ = [
     "GroupedQueryAttentionFwdOp",
     "GroupedQueryAttentionPrefillFwdOp",
+    "GroupedQueryAttentionPrefillVarlenFwdOp",
+    "GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp",
     "GroupedQueryAttentionDecodeWithKVCacheFwdOp",
     "GroupedQueryAttentionDecodePagedWithKVCacheFwdOp",
     "GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp",
@@ -202,7 +207,8 @@ class GroupedQueryAttentionPrefillFwdOp(Op):
 
     @property
     def default_kernel_map(self) -> Dict[str, type]:
-        return {"gqa_prefill_fwd_kernel": GQAPrefillSm100Kernel}
+        return {"gqa_prefill_fwd_kernel": GQAPrefillSm100Kernel,
+                "gqa_prefill_varlen_fwd_kernel": GQAPrefillVarlenSm100Kernel}
 
     def attention_call(self, *, is_fp8: bool, is_uniform: bool) -> AttentionCall:
         return AttentionCall(
@@ -290,6 +296,310 @@ class GroupedQueryAttentionPrefillFwdOp(Op):
             raise RuntimeError(f"{type(self).__name__}.eval_roofline() requires a prior forward() call")
         from ..perf.formulas import gqa_prefill_varlen_fwd_roofline
         return gqa_prefill_varlen_fwd_roofline(**self._roofline_kwargs)
+
+
+class GroupedQueryAttentionPrefillVarlenFwdOp(Op):
+    """Packed variable-length GQA prefill (THD).  Request b owns rows ``cu_seqlens_q[b]:cu_seqlens_q[b+1]``
+    of q and ``cu_seqlens_kv[b]:cu_seqlens_kv[b+1]`` of k/v; the causal mask is bottom-right aligned per
+    request (key j visible to row i iff ``j <= i + (kv_len - q_len)``).  Mirrors
+    ``src/tileops/ops/attention/gqa.py:555-762`` of the reference."""
+
+    def __init__(self, batch: int, heads: int, heads_kv: int, dim: int, max_seqlen_q: int,
+                 max_seqlen_kv: int, is_causal: bool = True, sm_scale: Optional[float] = None,
+                 softcap: Optional[float] = None, validate_inputs: bool = False,
+                 kernel_map: Optional[Dict[str, type]] = None, tune: bool = False) -> None:
+        _validate_gqa_dims(heads, heads_kv, dim)
+        _validate_positive(batch=batch, max_seqlen_q=max_seqlen_q, max_seqlen_kv=max_seqlen_kv)
+        self.batch, self.heads, self.heads_kv, self.dim = batch, heads, heads_kv, dim
+        self.max_seqlen_q, self.max_seqlen_kv = max_seqlen_q, max_seqlen_kv
+        self.is_causal = is_causal
+        self.sm_scale = _attention_scale(dim, sm_scale)
+        self.softcap = _score_softcap(softcap)
+        self.validate_inputs = validate_inputs
+        self._roofline_kwargs = None
+        self.tune = tune
+        self.dispatch_kernel(kernel_map)
+
+    @property
+    def default_kernel_map(self) -> Dict[str, type]:
+        return {"gqa_prefill_varlen_fwd_kernel": GQAPrefillVarlenSm100Kernel}
+
+    def _get_kernel(self, inputs, dtype: torch.dtype) -> Kernel:
+        _validate_attention_dtype(dtype)
+        return self.get_or_build_kernel(
+            "gqa_prefill_varlen_fwd_kernel", inputs, key=dtype,
+            build=lambda: self.kernel_map["gqa_prefill_varlen_fwd_kernel"](
+                batch=self.batch, heads=self.heads, heads_kv=self.heads_kv, max_seqlen_q=self.max_seqlen_q,
+                max_seqlen_kv=self.max_seqlen_kv, dim=self.dim, is_causal=self.is_causal, dtype=dtype,
+                sm_scale=self.sm_scale, softcap=self.softcap, tune=self.tune))
+
+    @staticmethod
+    def _lengths_from_cu_seqlens(cu_seqlens: torch.Tensor) -> list:
+        values = [int(x) for x in cu_seqlens.detach().cpu().tolist()]
+        return [b - a for a, b in zip(values[:-1], values[1:])]
+
+    def _validate_forward_inputs(self, q, k, v, cu_seqlens_q, cu_seqlens_kv) -> None:
+        named = (("q", q), ("k", k), ("v", v), ("cu_seqlens_q", cu_seqlens_q), ("cu_seqlens_kv", cu_seqlens_kv))
+        for name, t in named:
+            if not t.is_cuda:
+                raise ValueError(f"{name} must be a CUDA tensor")
+            if not t.is_contiguous():
+                raise ValueError(f"{name} must be contiguous")
+        if q.ndim != 3 or tuple(q.shape[1:]) != (self.heads, self.dim):
+            raise ValueError(f"q must have shape [T, {self.heads}, {self.dim}], got {tuple(q.shape)}")
+        for name, t in (("k", k), ("v", v)):
+            if t.ndim != 3 or tuple(t.shape[1:]) != (self.heads_kv, self.dim):
+                raise ValueError(f"{name} must have shape [T, {self.heads_kv}, {self.dim}], got {tuple(t.shape)}")
+            if t.dtype != q.dtype:
+                raise ValueError(f"Expected {name}.dtype {q.dtype}, got {t.dtype}")
+        for name, t in (("cu_seqlens_q", cu_seqlens_q), ("cu_seqlens_kv", cu_seqlens_kv)):
+            if tuple(t.shape) != (self.batch + 1,):
+                raise ValueError(f"{name} must have shape ({self.batch + 1},), got {tuple(t.shape)}")
+            if t.dtype != torch.int32:
+                raise ValueError(f"Expected {name}.dtype torch.int32, got {t.dtype}")
+        if v.shape[0] != k.shape[0]:
+            raise ValueError(f"v.shape[0] ({v.shape[0]}) must equal k.shape[0] ({k.shape[0]})")
+        if not self.validate_inputs:
+            return
+        cu_q = [int(x) for x in cu_seqlens_q.detach().cpu().tolist()]
+        cu_kv = [int(x) for x in cu_seqlens_kv.detach().cpu().tolist()]
+        if cu_q[0] != 0:
+            raise ValueError(f"cu_seqlens_q[0] must be 0, got {cu_q[0]}")
+        if cu_kv[0] != 0:
+            raise ValueError(f"cu_seqlens_kv[0] must be 0, got {cu_kv[0]}")
+        if cu_q[-1] != q.shape[0]:
+            raise ValueError(f"cu_seqlens_q[-1] ({cu_q[-1]}) must equal q.shape[0] ({q.shape[0]})")
+        if cu_kv[-1] != k.shape[0]:
+            raise ValueError(f"cu_seqlens_kv[-1] ({cu_kv[-1]}) must equal k.shape[0] ({k.shape[0]})")
+        q_lens = [b - a for a, b in zip(cu_q[:-1], cu_q[1:])]
+        kv_lens = [b - a for a, b in zip(cu_kv[:-1], cu_kv[1:])]
+        if any(n < 0 for n in q_lens):
+            raise ValueError("cu_seqlens_q must be non-decreasing")
+        if any(n < 0 for n in kv_lens):
+            raise ValueError("cu_seqlens_kv must be non-decreasing")
+        for q_len, kv_len in zip(q_lens, kv_lens):
+            if q_len <= 0:
+                raise ValueError("all q sequence lengths must be positive")
+            if kv_len <= 0:
+                raise ValueError("all kv sequence lengths must be positive")
+            if self.is_causal and q_len > kv_len:
+                raise ValueError("causal varlen prefill requires every q_len <= kv_len")
+        if self.max_seqlen_q < max(q_lens):
+            raise ValueError(f"max_seqlen_q ({self.max_seqlen_q}) must be >= actual max Q "
+                             f"sequence length ({max(q_lens)})")
+        if self.max_seqlen_kv < max(kv_lens):
+            raise ValueError(f"max_seqlen_kv ({self.max_seqlen_kv}) must be >= actual max KV "
+                             f"sequence length ({max(kv_lens)})")
+
+    def _infer_output_shapes(self, q_shape, *rest) -> Dict[str, tuple]:
+        return {"o": tuple(q_shape)}
+
+    def forward(self, q, k, v, cu_seqlens_q, cu_seqlens_kv) -> torch.Tensor:
+        self._validate_forward_inputs(q, k, v, cu_seqlens_q, cu_seqlens_kv)
+        self.dtype = q.dtype
+        tensors = (q, k, v, cu_seqlens_q, cu_seqlens_kv)
+        out = self._get_kernel(tensors, q.dtype)(*tensors)
+        self._roofline_kwargs = {
+            "q_shape": tuple(q.shape), "k_shape": tuple(k.shape), "batch": self.batch,
+            "max_seqlen_q": self.max_seqlen_q, "max_seqlen_kv": self.max_seqlen_kv,
+            "cu_seqlens_q": cu_seqlens_q, "cu_seqlens_kv": cu_seqlens_kv,
+            "is_causal": self.is_causal, "dtype": self.dtype}
+        return out
+
+    def eval_roofline(self) -> tuple:
+        if self._roofline_kwargs is None:
+            raise RuntimeError(f"{type(self).__name__}.eval_roofline() requires a prior forward() call")
+        from ..perf.formulas import gqa_prefill_varlen_fwd_roofline
+        kwargs = dict(self._roofline_kwargs)
+        kwargs["q_lens"] = self._lengths_from_cu_seqlens(kwargs.pop("cu_seqlens_q"))
+        kwargs["kv_lens"] = self._lengths_from_cu_seqlens(kwargs.pop("cu_seqlens_kv"))
+        return gqa_prefill_varlen_fwd_roofline(**kwargs)
+
+
+def _paged_cache_dtype(cache_dtype: Optional[torch.dtype]) -> Optional[torch.dtype]:
+    if cache_dtype is None:
+        return None
+    if cache_dtype != fp8_dtype():
+        _validate_attention_dtype(cache_dtype)
+    return cache_dtype
+
+
+class GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp(Op):
+    """Packed GQA prefill with paged KV-cache append (THD).
+
+    The chunk is packed by request; ``cache_seqlens`` holds every request's logical KV length
+    before the append; ``block_table`` maps logical to physical pages of ``k_pages`` / ``v_pages``,
+    which are modified in place.  Mirrors ``src/tileops/ops/attention/gqa.py:765-1157`` of the
+    reference (constructor, validation order and messages, positional ``forward``).  Served here:
+    a cache of q's element type, head dim 64 / 128, power-of-two pages >= 16.  An FP8 cache and
+    ``fuse_rope=True`` are accepted by the constructor as in the reference but no sm_100
+    implementation serves them: ``forward`` raises "no implementation serves this call".
+    """
+
+    def __init__(self, batch: int, heads: int, heads_kv: int, max_pages_per_req: int, page_size: int,
+                 dim: int, is_causal: bool = True, cache_dtype: Optional[torch.dtype] = None,
+                 sm_scale: Optional[float] = None, softcap: Optional[float] = None,
+                 kernel_map: Optional[Dict[str, type]] = None, tune: bool = False,
+                 fuse_rope: bool = False, rope_base: float = 10000.0, max_position: Optional[int] = None,
+                 rotary_dim: Optional[int] = None) -> None:
+        _validate_gqa_dims(heads, heads_kv, dim)
+        if fuse_rope:
+            rotary_dim = dim if rotary_dim is None else rotary_dim
+            if rotary_dim <= 0 or rotary_dim > dim or rotary_dim % 2:
+                raise ValueError(f"rotary_dim must be an even value in (0, {dim}], got {rotary_dim}")
+            if max_position is None:
+                raise ValueError("max_position is required when fuse_rope=True")
+            _validate_positive(max_position=max_position)
+        elif rotary_dim is not None:
+            raise ValueError("rotary_dim requires fuse_rope=True")
+        _validate_positive(batch=batch, max_pages_per_req=max_pages_per_req, page_size=page_size)
+        if page_size & (page_size - 1) != 0:
+            raise ValueError("page_size must be a power of two")
+        cache_dtype = _paged_cache_dtype(cache_dtype)
+        if fuse_rope and cache_dtype is not None and cache_dtype == fp8_dtype():
+            raise ValueError("fuse_rope is not supported with FP8 paged KV cache yet")
+        self.batch, self.heads, self.heads_kv = batch, heads, heads_kv
+        self.groups = heads // heads_kv
+        self.max_pages_per_req, self.page_size = max_pages_per_req, page_size
+        self.max_cache_len = max_pages_per_req * page_size
+        self.dim, self.is_causal = dim, is_causal
+        self.cache_dtype = cache_dtype          # None: the cache has forward's element type
+        self.sm_scale = _attention_scale(dim, sm_scale)
+        self.softcap = _score_softcap(softcap)
+        self.fuse_rope, self.rope_base = fuse_rope, rope_base
+        self.max_position, self.rotary_dim = max_position, rotary_dim
+        self.tune = tune
+        self.dispatch_kernel(kernel_map)
+
+    @property
+    def default_kernel_map(self) -> Dict[str, type]:
+        return {"gqa_prefill_paged_with_kv_cache_fwd_kernel": GQAPrefillPagedSm100Kernel}
+
+    def _resolved_cache_dtype(self, dtype: torch.dtype) -> torch.dtype:
+        return dtype if self.cache_dtype is None else self.cache_dtype
+
+    def attention_call(self, dtype: torch.dtype) -> AttentionCall:
+        return AttentionCall(
+            dtype=dtype, batch=self.batch, heads=self.heads, heads_kv=self.heads_kv, dim=self.dim,
+            max_pages_per_req=self.max_pages_per_req, page_size=self.page_size, is_causal=self.is_causal,
+            sm_scale=self.sm_scale, softcap=self.softcap, cache_dtype=self._resolved_cache_dtype(dtype),
+            fuse_rope=self.fuse_rope, max_position=self.max_position, rotary_dim=self.rotary_dim,
+            tune=self.tune)
+
+    def _get_kernel(self, inputs, key: str, call: AttentionCall) -> Kernel:
+        return self.get_or_build_kernel(key, inputs, key=call.dtype, build=lambda: self.kernel_map[key](
+            batch=call.batch, heads=call.heads, heads_kv=call.heads_kv,
+            max_pages_per_req=call.max_pages_per_req, page_size=call.page_size, dim=call.dim,
+            is_causal=call.is_causal, dtype=call.dtype, sm_scale=call.sm_scale, softcap=call.softcap,
+            max_position=call.max_position, rotary_dim=call.rotary_dim, tune=call.tune))
+
+    def _validate_forward_inputs(self, q, k_new, v_new, k_pages, v_pages, k_scale, v_scale, cu_seqlens_q,
+                                 cache_seqlens, block_table, max_seqlen_q) -> None:
+        named = (("q", q), ("k_new", k_new), ("v_new", v_new), ("k_pages", k_pages), ("v_pages", v_pages),
+                 ("k_scale", k_scale), ("v_scale", v_scale), ("cu_seqlens_q", cu_seqlens_q),
+                 ("cache_seqlens", cache_seqlens), ("block_table", block_table))
+        for name, t in named:
+            if t.device.type != "cuda":
+                raise ValueError(f"{name} must be on a cuda device, got {t.device}")
+            if not t.is_contiguous():
+                raise ValueError(f"{name} must be contiguous")
+        if q.ndim != 3 or tuple(q.shape[1:]) != (self.heads, self.dim):
+            raise ValueError(f"q must have shape [total_q, {self.heads}, {self.dim}], got {q.shape}")
+        if k_new.ndim != 3 or tuple(k_new.shape[1:]) != (self.heads_kv, self.dim):
+            raise ValueError(f"k_new must have shape [total_q, {self.heads_kv}, {self.dim}], got {k_new.shape}")
+        if v_new.shape != k_new.shape:
+            raise ValueError(f"v_new must have the same shape as k_new, got {v_new.shape} and {k_new.shape}")
+        if k_new.shape[0] != q.shape[0]:
+            raise ValueError(f"k_new.shape[0] ({k_new.shape[0]}) must equal q.shape[0] ({q.shape[0]})")
+        if k_pages.ndim != 3 or tuple(k_pages.shape[1:]) != (self.heads_kv, self.dim):
+            raise ValueError(f"k_pages must have shape [physical_tokens, {self.heads_kv}, {self.dim}], "
+                             f"got {k_pages.shape}")
+        if v_pages.shape != k_pages.shape:
+            raise ValueError(f"v_pages must have the same shape as k_pages, got {v_pages.shape} and "
+                             f"{k_pages.shape}")
+        if k_pages.shape[0] % self.page_size != 0:
+            raise ValueError("k_pages physical token dimension must be divisible by page_size")
+        if k_scale.shape != (1,) or v_scale.shape != (1,):
+            raise ValueError(f"k_scale and v_scale must have shape (1,), got {k_scale.shape} and {v_scale.shape}")
+        if cu_seqlens_q.shape != (self.batch + 1,):
+            raise ValueError(f"cu_seqlens_q shape must be ({self.batch + 1},), got {tuple(cu_seqlens_q.shape)}")
+        if cache_seqlens.shape != (self.batch,):
+            raise ValueError(f"cache_seqlens shape must be ({self.batch},), got {tuple(cache_seqlens.shape)}")
+        if block_table.shape != (self.batch, self.max_pages_per_req):
+            raise ValueError(f"block_table shape must be ({self.batch}, {self.max_pages_per_req}), "
+                             f"got {tuple(block_table.shape)}")
+        _validate_attention_dtype(q.dtype)
+        cache_dtype = self._resolved_cache_dtype(q.dtype)
+        f8 = fp8_dtype()
+        if cache_dtype != q.dtype and cache_dtype != f8:
+            raise ValueError("cache_dtype must be either same as the q element type or "
+                             f"torch.float8_e4m3fn, got {cache_dtype}")
+        for name, t in (("k_new", k_new), ("v_new", v_new)):
+            if t.dtype != q.dtype:
+                raise ValueError(f"Expected {name}.dtype {q.dtype}, got {t.dtype}")
+        for name, t in (("k_pages", k_pages), ("v_pages", v_pages)):
+            if t.dtype != cache_dtype:
+                raise ValueError(f"Expected {name}.dtype {cache_dtype}, got {t.dtype}")
+        for name, t in (("k_scale", k_scale), ("v_scale", v_scale)):
+            if t.dtype != torch.float32:
+                raise ValueError(f"{name} must have dtype torch.float32, got {t.dtype}")
+            if cache_dtype == f8 and not torch.all(torch.isfinite(t) & (t > 0)).item():
+                raise ValueError(f"{name} must contain finite positive values")
+        for name, t in (("cu_seqlens_q", cu_seqlens_q), ("cache_seqlens", cache_seqlens),
+                        ("block_table", block_table)):
+            if t.dtype != torch.int32:
+                raise ValueError(f"{name} must have dtype torch.int32, got {t.dtype}")
+        # the range checks below read the tensors on the host, as the reference's do
+        if int(cu_seqlens_q[0].item()) != 0:
+            raise ValueError("cu_seqlens_q[0] must be 0")
+        q_lens = cu_seqlens_q[1:] - cu_seqlens_q[:-1]
+        if torch.any(q_lens < 0).item():
+            raise ValueError("cu_seqlens_q must be non-decreasing")
+        total_q = int(cu_seqlens_q[-1].item())
+        if total_q != q.shape[0]:
+            raise ValueError(f"cu_seqlens_q[-1] ({total_q}) must equal q.shape[0] ({q.shape[0]})")
+        actual_max_q = int(q_lens.max().item())
+        if max_seqlen_q < actual_max_q:
+            raise ValueError(f"max_seqlen_q ({max_seqlen_q}) must be >= actual max Q "
+                             f"sequence length ({actual_max_q})")
+        if int(cache_seqlens.min().item()) < 0:
+            raise ValueError("cache_seqlens must be non-negative")
+        max_total_len = int((cache_seqlens + q_lens).max().item())
+        if max_total_len > self.max_cache_len:
+            raise ValueError("cache_seqlens + q_len exceeds paged KV capacity: "
+                             f"max total length {max_total_len}, capacity {self.max_cache_len}")
+        if self.fuse_rope and max_total_len > self.max_position:
+            raise ValueError("cache_seqlens + q_len exceeds RoPE max_position: "
+                             f"max total length {max_total_len}, max_position {self.max_position}")
+        num_pages = k_pages.shape[0] // self.page_size
+        if int(block_table.min().item()) < 0:
+            raise ValueError("block_table must contain non-negative physical page ids")
+        max_page = int(block_table.max().item())
+        if max_page >= num_pages:
+            raise ValueError(f"block_table references page {max_page}, but only {num_pages} pages exist")
+
+    def _infer_output_shapes(self, q_shape, *rest) -> Dict[str, tuple]:
+        return {"o": tuple(q_shape)}
+
+    def forward(self, q, k_new, v_new, k_pages, v_pages, k_scale, v_scale, cu_seqlens_q, cache_seqlens,
+                block_table, max_seqlen_q) -> torch.Tensor:
+        self._validate_forward_inputs(q, k_new, v_new, k_pages, v_pages, k_scale, v_scale, cu_seqlens_q,
+                                      cache_seqlens, block_table, max_seqlen_q)
+        self.dtype = q.dtype
+        call = self.attention_call(q.dtype)
+        key = self.select_kernel_key(PAGED_PREFILL_KEYS, call)
+        inputs = (q, k_new, v_new, k_pages, v_pages, k_scale, v_scale, cu_seqlens_q, cache_seqlens, block_table)
+        return self._get_kernel(inputs, key, call)(*inputs, max_seqlen_q, None, None)
+
+    @property
+    def total_flops(self) -> int:
+        raise NotImplementedError("total_flops is not defined for paged varlen ops; "
+                                  "compute per-sample from cu_seqlens and cache_seqlens at call time.")
+
+    @property
+    def total_memory(self) -> int:
+        raise NotImplementedError("total_memory is not defined for paged varlen ops; "
+                                  "compute per-sample from cu_seqlens and cache_seqlens at call time.")
 
 
 class GroupedQueryAttentionDecodeWithKVCacheFwdOp(Op):

@@ -4,7 +4,7 @@
 from ..kernels.call_spec import AttentionCall, fp8_dtype, uses_sliding_window
 
 __all__ = ["DECODE_KEYS", "DENSE_PREFILL_KEYS", "PACKED_PREFILL_KEYS", "PAGED_DECODE_KEYS",
-           "PAGED_DECODE_FP8_KEYS", "AttentionCall", "check_packed_prefill_request", "fp8_dtype"]
+           "PAGED_DECODE_FP8_KEYS", "PAGED_PREFILL_KEYS", "AttentionCall", "check_packed_prefill_request", "fp8_dtype"]
 
 PACKED_PREFILL_KEYS = (
     "gqa_prefill_fp8_tensor_core_fwd_kernel",
@@ -18,6 +18,11 @@ DENSE_PREFILL_KEYS = ("gqa_prefill_square_fwd_kernel", "gqa_prefill_causal_fwd_k
 DECODE_KEYS = ("gqa_decode_bs1_kernel", "gqa_decode_kernel")
 PAGED_DECODE_KEYS = ("gqa_decode_paged_bs1_kernel", "gqa_decode_paged_kernel")
 PAGED_DECODE_FP8_KEYS = ("gqa_decode_paged_fp8_kernel",)
+PAGED_PREFILL_KEYS = (
+    "gqa_prefill_paged_with_kv_cache_rope_fwd_kernel",
+    "gqa_prefill_paged_with_fp8_kv_cache_fwd_kernel",
+    "gqa_prefill_paged_with_kv_cache_fwd_kernel",
+)
 
 
 def check_packed_prefill_request(call: AttentionCall) -> None:

@@ -20,6 +20,7 @@ from typing import Any
 __all__ = [
     "gqa_fwd_roofline",
     "gqa_prefill_varlen_fwd_roofline",
+    "gqa_prefill_paged_with_kv_cache_fwd_roofline",
     "gqa_decode_roofline",
     "gqa_decode_paged_roofline",
 ]
@@ -110,6 +111,40 @@ def gqa_prefill_varlen_fwd_roofline(op: Any = None, **kwargs: Any) -> tuple:
     q_elems = total_q * heads * dim
     kv_elems = total_kv * heads_kv * dim
     return int(4 * heads * visible * dim), int((2 * q_elems + 2 * kv_elems) * e + 2 * (batch + 1) * 4)
+
+
+def gqa_prefill_paged_with_kv_cache_fwd_roofline(op: Any = None, **kwargs: Any) -> tuple:
+    """Packed prefill over a paged cache with append: every query row sees its request's cached
+    tokens plus the causal part of the chunk; bytes = q, o, cached K/V read, new K/V read and
+    written once more (the append), plus the int32 metadata.  Missing per-request lengths are
+    filled deterministically from the aggregate fields, as the reference's formula does
+    (``src/tileops/perf/formulas.py:532-587``)."""
+    d = _fields(op, kwargs)
+    batch, heads, heads_kv, dim = (int(d[k]) for k in ("batch", "heads", "heads_kv", "dim"))
+    pages, page = int(d["max_pages_per_req"]), int(d["page_size"])
+    max_q = int(d.get("max_seqlen_q", pages * page))
+    causal = bool(d.get("is_causal", True))
+    q_lens = d.get("q_lens")
+    total_q = int(d["total_q"]) if "total_q" in d else (int(sum(q_lens)) if q_lens is not None else batch * max_q)
+    if q_lens is None:
+        q_lens = _spread(total_q, batch, max_q)
+    cache_lens = d.get("cache_lens")
+    if cache_lens is None:
+        cap = pages * page if d.get("max_position") is None else int(d["max_position"])
+        cache_lens = [max(cap - int(n), 0) for n in q_lens]
+    if len(q_lens) != len(cache_lens):
+        raise ValueError("q_lens and cache_lens differ in length")
+    visible, cached = 0, 0
+    for n, old in zip(q_lens, cache_lens):
+        n, old = int(n), int(old)
+        cached += old
+        visible += n * old + n * (n + 1) // 2 if causal else n * (old + n)
+    e = _itemsize(_dtype_of(d))
+    q_elems = total_q * heads * dim
+    new_kv = 2 * total_q * heads_kv * dim
+    elems = 2 * q_elems + 2 * cached * heads_kv * dim + 2 * new_kv
+    meta = (batch + 1) * 4 + batch * 4 + batch * pages * 4
+    return int(4 * heads * visible * dim), int(elems * e + meta)
 
 
 def gqa_decode_roofline(op: Any = None, **kwargs: Any) -> tuple:
