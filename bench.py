@@ -261,7 +261,7 @@ def main():
     ap.add_argument("--no-others", action="store_true", help="time only the headline workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--case", default=None,
-                    choices=["decode_small", "decode_fp8_small", "prefill_small"],
+                    choices=["decode_small", "decode_fp8_small", "prefill_small", "prefill_paged"],
                     help="run only a reduced case of one kernel (a few hundred MB on the device: the "
                          "size an ncu capture of all sections can handle) and print its timing")
     a = ap.parse_args()
@@ -361,6 +361,9 @@ def run_small_case(case: str, steps: int, warmup: int):
         op = GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp(32, 64, 8, inp.k.shape[0], 128, 64)
         fn = lambda: op(inp.q, inp.k, inp.v, inp.k_scale, inp.v_scale, inp.real_seqlen_kv, inp.block_table)  # noqa: E731
         work, unit = inp.algorithmic_bytes(), "GB/s"
+    elif case == "prefill_paged":
+        fn, work = paged_prefill_step(device, 0)
+        unit = "TFLOP/s"
     else:
         q, k, v = W.make_prefill(2, 1, 4096, 4096, 32, 8, 128, torch.bfloat16, device)
         op = GroupedQueryAttentionFwdOp(1, 32, 8, 4096, 128, is_causal=True)
@@ -399,7 +402,33 @@ def run_others(rank, world, device, steps, warmup, peaks):
         out["cfg2_causal_prefill"] = run_cfg2(rank, world, device, steps, warmup, peaks)
     except Exception as exc:  # noqa: BLE001
         out["cfg2_causal_prefill"] = {"error": repr(exc)}
+    # the step that fills the pages decode reads: one 512-token chunk per request over a 4k prefix
+    try:
+        fn, flops = paged_prefill_step(device, rank)
+        ms = max_over_ranks(time_steps(fn, steps, warmup, world), world, device) / steps
+        tf = flops * world / (ms * 1e-3) / 1e12
+        out["paged_prefill_llama8b_chunk512"] = {
+            "tflops": tf, "frac_of_peak_burst": tf / world / peaks["bf16_tflops"], "ms_per_step": ms,
+            "tokens_per_s": 8 * 512 * world / (ms * 1e-3), "gpu_launches": steps}
+    except Exception as exc:  # noqa: BLE001
+        out["paged_prefill_llama8b_chunk512"] = {"error": repr(exc)}
     return out
+
+
+def paged_prefill_step(device, rank):
+    """Manifest workload "llama-8b-prefill-paged-b8-prefix4k-chunk512-p64" (fp16, no fused RoPE): the
+    kernel class is called directly, because the operator's own argument checks read the length
+    tensors on the host (as the reference's do) and would put a sync into every timed step."""
+    from tileops_b200 import workloads as W
+    from tileops_b200.kernels import GQAPrefillPagedSm100Kernel
+    from tileops_b200.perf.formulas import gqa_prefill_paged_with_kv_cache_fwd_roofline
+    B, H, Hkv, D, page, W_pages, old, n = 8, 32, 8, 128, 64, 72, 4096, 512
+    args = W.make_paged_prefill(6 + 10 * rank, [n] * B, [old] * B, H, Hkv, D, page, W_pages, torch.float16, device)
+    kern = GQAPrefillPagedSm100Kernel(B, H, Hkv, W_pages, page, D, True, torch.float16)
+    flops, _ = gqa_prefill_paged_with_kv_cache_fwd_roofline(
+        total_q=B * n, batch=B, q_lens=[n] * B, cache_lens=[old] * B, heads=H, heads_kv=Hkv, dim=D,
+        page_size=page, max_pages_per_req=W_pages, max_seqlen_q=n, is_causal=True, dtype=torch.float16)
+    return (lambda: kern(*args)), flops
 
 
 def run_cfg5(rank, world, device, steps, warmup, peaks):

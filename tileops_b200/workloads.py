@@ -179,6 +179,31 @@ def make_prefill(cfg, batch, seqlen_q, seqlen_kv, heads, heads_kv, dim, dtype=to
     return q, torch.stack(ks), torch.stack(vs)
 
 
+def make_paged_prefill(cfg, q_lens, cache_lens, heads, heads_kv, dim, page_size, max_pages_per_req,
+                       dtype=torch.float16, device="cuda"):
+    """Inputs of one packed prefill chunk per request over a paged cache, in the argument order of
+    ``GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp.forward``: (q, k_new, v_new, k_pages, v_pages,
+    k_scale, v_scale, cu_seqlens_q, cache_seqlens, block_table, max_seqlen_q).  All ~ N(0,1); the
+    block table is a seeded permutation of the pool's pages (every request owns
+    ``max_pages_per_req`` of them); every pool row is filled, cached or not."""
+    device = torch.device(device)
+    g = _gen(device, BASE_SEED + 100 * cfg)
+    batch, total_q = len(q_lens), int(sum(q_lens))
+    pool = batch * max_pages_per_req * page_size
+    q = torch.randn(total_q, heads, dim, generator=g, device=device).to(dtype)
+    k_new = torch.randn(total_q, heads_kv, dim, generator=g, device=device).to(dtype)
+    v_new = torch.randn(total_q, heads_kv, dim, generator=g, device=device).to(dtype)
+    k_pages = torch.randn(pool, heads_kv, dim, generator=g, device=device).to(dtype)
+    v_pages = torch.randn(pool, heads_kv, dim, generator=g, device=device).to(dtype)
+    bt = torch.randperm(batch * max_pages_per_req, generator=g, device=device).to(torch.int32)
+    cu = torch.zeros(batch + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(q_lens, dtype=torch.int32).cumsum(0)
+    one = torch.ones(1, dtype=torch.float32, device=device)
+    return (q, k_new, v_new, k_pages, v_pages, one, one.clone(), cu.to(device),
+            torch.tensor(cache_lens, dtype=torch.int32, device=device),
+            bt.reshape(batch, max_pages_per_req).contiguous(), int(max(q_lens)))
+
+
 # The BASELINE configurations, by number (1-based as in BASELINE.json's ``configs`` list).
 def baseline_config(cfg: int, device="cuda", **overrides):
     if cfg == 1:
