@@ -154,6 +154,11 @@ int tb200_gqa_lse_merge(const float* o_parts, const float* lse_parts, void* o, f
  *   q [batch, seqlen_q, heads, dim], k/v [batch, seqlen_kv, heads_kv, dim]  dtype (F16 | BF16)
  *   o [batch, seqlen_q, heads, dim] dtype ; lse [batch, heads, seqlen_q] fp32 log2-domain or NULL
  * dim must be 64 or 128 (tcgen05 path).  Rows with no visible key give o = 0, lse = -inf.
+ * window_left / window_right: sliding window of the reference's
+ * GroupedQueryAttentionSlidingWindowFwdOp (src/tileops/ops/attention/gqa.py:1457-1627): with
+ * d = seqlen_kv - seqlen_q, key j is visible to row i iff j >= i + d - window_left (when
+ * window_left >= 0), j <= i + d + window_right (when window_right >= 0) and j <= i + d (when
+ * causal); -1 = unlimited.  Key tiles outside the window of a whole row tile are skipped.
  * workspace: tb200_gqa_prefill_workspace_bytes() bytes (may be 0 -> NULL allowed).
  * ------------------------------------------------------------------------- */
 size_t tb200_gqa_prefill_workspace_bytes(int batch, int heads, int heads_kv, int seqlen_q,
@@ -162,6 +167,7 @@ size_t tb200_gqa_prefill_workspace_bytes(int batch, int heads, int heads_kv, int
 int tb200_gqa_prefill(const void* q, const void* k, const void* v, void* o, float* lse,
                       int dtype, int batch, int seqlen_q, int seqlen_kv, int heads, int heads_kv,
                       int dim, int is_causal, float sm_scale, float softcap,
+                      int window_left, int window_right,
                       void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------
@@ -190,6 +196,8 @@ int tb200_gqa_prefill(const void* q, const void* k, const void* v, void* o, floa
  * block_table ids are trusted (range-check them on the host, as the reference operator does).
  * k_pages = v_pages = cache_seqlens = block_table = NULL: no cache, nothing appended.
  * max_seqlen_q bounds the longest request (it sizes the grid).
+ * window_left / window_right: as for tb200_gqa_prefill, per request (the reference's
+ * GroupedQueryAttentionSlidingWindowVarlenFwdOp, gqa.py:1630-1831); only without a cache.
  * workspace: tb200_gqa_prefill_workspace_bytes() bytes, zeroed once.
  * ------------------------------------------------------------------------- */
 int tb200_gqa_prefill_paged(const void* q, const void* k_new, const void* v_new,
@@ -200,6 +208,7 @@ int tb200_gqa_prefill_paged(const void* q, const void* k_new, const void* v_new,
                             int dtype, int total_q, int total_kv, int batch, int max_seqlen_q,
                             int heads, int heads_kv, int dim, int page_size, int64_t pool_tokens,
                             int is_causal, float sm_scale, float softcap,
+                            int window_left, int window_right,
                             void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus

@@ -210,8 +210,17 @@ def prefill_ref(
     sm_scale: Optional[float] = None,
     softcap: Optional[float] = None,
     return_lse: bool = False,
+    window_left: int = -1,
+    window_right: int = -1,
 ):
     """q [B,Sq,H,D], k/v [B,Skv,Hkv,D] -> o [B,Sq,H,D] (+ LSE [B,H,Sq] fp32, log2).
+
+    ``window_left`` / ``window_right`` (-1 = unlimited) add the sliding-window conditions of
+    the reference's sliding-window reference programs
+    (``tests/ops/attention/test_gqa_sliding_window.py:17-54``,
+    ``test_gqa_sliding_window_varlen.py:22-84``): with ``d = Skv - Sq``, key j is hidden from
+    row i when ``j < i + d - window_left`` or ``j > i + d + window_right``; rows left without
+    a key give zeros.
 
     Follows ``_gqa_prefill_ref`` (``tests/ops/attention/test_gqa.py:109-139``):
     fp32 materialised scores, softcap before the mask, bottom-right aligned causal
@@ -226,10 +235,16 @@ def prefill_ref(
     scale = _scale(D, sm_scale)
     out = torch.empty(B, Sq, H, D, dtype=q.dtype)
     lse = torch.empty(B, H, Sq, dtype=torch.float32)
+    q_pos = torch.arange(Sq)[:, None] + (Skv - Sq)
+    k_pos = torch.arange(Skv)[None, :]
+    mask = torch.ones(Sq, Skv, dtype=torch.bool)
     if is_causal:
-        q_pos = torch.arange(Sq)[:, None] + (Skv - Sq)
-        k_pos = torch.arange(Skv)[None, :]
-        mask = k_pos <= q_pos
+        mask &= k_pos <= q_pos
+    if window_left >= 0:
+        mask &= k_pos >= q_pos - window_left
+    if window_right >= 0:
+        mask &= k_pos <= q_pos + window_right
+    masked = is_causal or window_left >= 0 or window_right >= 0
     for b in range(B):
         for hk in range(Hkv):
             qf = q[b, :, hk * g:(hk + 1) * g, :].float().permute(1, 0, 2)   # [g,Sq,D]
@@ -237,9 +252,9 @@ def prefill_ref(
             vf = v[b, :, hk, :].float()
             scores = torch.matmul(qf, kf.t()) * scale                       # [g,Sq,Skv]
             scores = _softcap(scores, softcap)
-            if is_causal:
+            if masked:
                 scores = scores.masked_fill(~mask[None], float("-inf"))
-            probs = torch.softmax(scores, dim=-1)
+            probs = torch.softmax(scores, dim=-1).nan_to_num()
             o = torch.matmul(probs, vf)                                     # [g,Sq,D]
             out[b, :, hk * g:(hk + 1) * g, :] = o.permute(1, 0, 2).to(q.dtype)
             lse[b, hk * g:(hk + 1) * g, :] = torch.logsumexp(scores, dim=-1) * LOG2E
@@ -249,7 +264,7 @@ def prefill_ref(
 
 
 def prefill_packed_ref(q, k, v, cu_seqlens_q, cu_seqlens_kv, is_causal=True,
-                       sm_scale=None, softcap=None):
+                       sm_scale=None, softcap=None, window_left=-1, window_right=-1):
     """Packed THD form, per request; follows ``_gqa_prefill_varlen_ref``
     (``tests/ops/attention/test_gqa.py:152-191``)."""
     cq = [int(x) for x in cu_seqlens_q.tolist()]
@@ -257,7 +272,8 @@ def prefill_packed_ref(q, k, v, cu_seqlens_q, cu_seqlens_kv, is_causal=True,
     outs = []
     for b in range(len(cq) - 1):
         outs.append(prefill_ref(q[cq[b]:cq[b + 1]].unsqueeze(0), k[ck[b]:ck[b + 1]].unsqueeze(0),
-                                v[ck[b]:ck[b + 1]].unsqueeze(0), is_causal, sm_scale, softcap)[0])
+                                v[ck[b]:ck[b + 1]].unsqueeze(0), is_causal, sm_scale, softcap,
+                                window_left=window_left, window_right=window_right)[0])
     return torch.cat(outs, dim=0)
 
 

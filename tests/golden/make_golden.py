@@ -13,6 +13,7 @@ What is executed from the reference (imported, never copied):
   * ``tests.ops.attention.test_gqa._gqa_prefill_ref`` / ``_gqa_prefill_varlen_ref``
   * ``tests.ops.attention.test_gqa_prefill_paged._gqa_prefill_paged_ref`` /
     ``_fill_paged_cache_from_logical`` / ``_physical_pos``
+  * ``tests.ops.attention.test_gqa_sliding_window(.py|_varlen.py)`` reference programs
   * ``tileops.perf.formulas.gqa_*_roofline``
 ``tileops.ops`` itself needs a newer TileLang than the container has, so a stub
 module carrying the handful of names those files import is placed in
@@ -194,6 +195,30 @@ def main():
             kpg[pos] = kn[int(cu[b_]) + i]
             vpg[pos] = vn[int(cu[b_]) + i]
     out["pp_k_pages_after"], out["pp_v_pages_after"] = kpg.numpy(), vpg.numpy()
+
+    # ---- sliding window: the reference tests' own reference programs, fixed length and packed
+    from tests.ops.attention import test_gqa_sliding_window as tsw
+    from tests.ops.attention import test_gqa_sliding_window_varlen as tswv
+    B, S, H, Hkv, D = 2, 96, 4, 2, 32
+    qs = torch.randn(B, S, H, D, generator=g)
+    ks_ = torch.randn(B, S, Hkv, D, generator=g)
+    vs_ = torch.randn(B, S, Hkv, D, generator=g)
+    out["sw_q"], out["sw_k"], out["sw_v"] = qs.numpy(), ks_.numpy(), vs_.numpy()
+    for name, (causal, wl, wr) in {"c_l17": (True, 17, -1), "n_l8_r5": (False, 8, 5), "n_r11": (False, -1, 11),
+                                   "c_l0": (True, 0, -1)}.items():
+        t = tsw.GroupedQueryAttentionSlidingWindowFwdTest(B, S, H, Hkv, D, causal, wl, wr, torch.float32)
+        out["sw_o_" + name] = t.ref_program(qs, ks_, vs_).numpy()
+    sq, sk = [24, 16], [50, 22]
+    cuq = torch.tensor([0, 24, 40], dtype=torch.int32)
+    cuk = torch.tensor([0, 50, 72], dtype=torch.int32)
+    qv = torch.randn(40, H, D, generator=g)
+    kv_ = torch.randn(72, Hkv, D, generator=g)
+    vv_ = torch.randn(72, Hkv, D, generator=g)
+    out["swv_q"], out["swv_k"], out["swv_v"] = qv.numpy(), kv_.numpy(), vv_.numpy()
+    out["swv_cu_q"], out["swv_cu_k"] = cuq.numpy(), cuk.numpy()
+    for name, (causal, wl, wr) in {"c_l9": (True, 9, -1), "n_l4_r6": (False, 4, 6)}.items():
+        t = tswv.GroupedQueryAttentionSlidingWindowVarlenFwdTest(2, sq, sk, H, Hkv, D, causal, wl, wr, torch.float32)
+        out["swv_o_" + name] = t.ref_program(qv, kv_, vv_, cuq, cuk, 24).numpy()
 
     np.savez_compressed(os.path.join(HERE, "gqa_golden.npz"), **out)
 

@@ -106,6 +106,20 @@ def test_paged_prefill_matches_reference_and_appends():
     torch.testing.assert_close(o.float(), fp16("pp_o_causal_f16").float(), atol=1e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("name,causal,wl,wr", [("c_l17", True, 17, -1), ("n_l8_r5", False, 8, 5),
+                                                ("n_r11", False, -1, 11), ("c_l0", True, 0, -1)])
+def test_sliding_window_matches_reference(name, causal, wl, wr):
+    o = O.prefill_ref(t("sw_q"), t("sw_k"), t("sw_v"), causal, window_left=wl, window_right=wr)
+    torch.testing.assert_close(o, t("sw_o_" + name), atol=2e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("name,causal,wl,wr", [("c_l9", True, 9, -1), ("n_l4_r6", False, 4, 6)])
+def test_sliding_window_packed_matches_reference(name, causal, wl, wr):
+    o = O.prefill_packed_ref(t("swv_q"), t("swv_k"), t("swv_v"), t("swv_cu_q"), t("swv_cu_k"), causal,
+                             window_left=wl, window_right=wr)
+    torch.testing.assert_close(o, t("swv_o_" + name), atol=2e-6, rtol=1e-5)
+
+
 def test_bottom_right_known_answer():
     # tests/ops/attention/test_gqa.py:417-443 in the reference
     q = torch.zeros(1, 128, 4, 64); k = torch.zeros(1, 256, 2, 64); v = torch.zeros(1, 256, 2, 64)

@@ -51,12 +51,12 @@ SIGNATURES = {
     "tb200_gqa_prefill": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,      # q k v o lse
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,  # dtype B Sq Skv H Hkv D causal
-        c_float, c_float, c_void_p, c_size_t, c_void_p]),
+        c_float, c_float, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "tb200_gqa_prefill_paged": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # q k_new v_new k_pages v_pages o lse
         c_void_p, c_void_p, c_void_p, c_void_p, c_int64,        # cu_seqlens_q cu_seqlens_kv cache_seqlens block_table stride
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int,  # dtype total_q total_kv B maxq H Hkv D page pool causal
-        c_float, c_float, c_void_p, c_size_t, c_void_p]),
+        c_float, c_float, c_int, c_int, c_void_p, c_size_t, c_void_p]),
 }
 
 _lib = None

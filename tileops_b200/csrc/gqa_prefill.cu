@@ -102,6 +102,7 @@ struct PrefillParams {
   int* status;
   int batch, heads, heads_kv, seqlen_q, seqlen_kv;
   int is_causal;
+  int win_left, win_right;     // sliding window around the (bottom-right aligned) diagonal; -1 = unlimited
   float sm_scale, softcap;
   // packed (ragged) queries over a paged cache; unused by the dense kernel
   const int32_t* cu_q;         // [batch + 1] row offsets of the requests in q / o (and k_new / v_new)
@@ -331,11 +332,18 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   }
   const int off = kv_len - q_len;                          // bottom-right alignment (0 when paged)
   const int n_old = (old_len + kBN - 1) / kBN;             // tiles of cached tokens (0 when dense)
-  int n_new = (kv_len + kBN - 1) / kBN;
-  if (p.is_causal) {
-    const int last_key = m0 + kBM - 1 + off;               // last key the tile's last row may see
-    n_new = last_key < 0 ? 0 : min(n_new, last_key / kBN + 1);
+  // Row i sees keys j with i + off - win_left <= j <= i + off + up_extra (each bound only if it
+  // applies): causal means up_extra = 0, otherwise the right window.
+  const bool has_upper = p.is_causal || p.win_right >= 0;
+  const int up_extra = p.is_causal ? 0 : p.win_right;
+  int n_end = (kv_len + kBN - 1) / kBN;                    // one past the last tile of the new segment
+  if (has_upper) {
+    const long long last_key = (long long)m0 + kBM - 1 + off + up_extra;   // of the tile's last row
+    n_end = last_key < 0 ? 0 : int(min((long long)n_end, last_key / kBN + 1));
   }
+  int tile0 = 0;                                           // first tile any row of this CTA can see
+  if (p.win_left >= 0) tile0 = max(0, m0 + off - p.win_left) / kBN;
+  const int n_new = max(0, n_end - tile0);
   const int n_kv = n_old + n_new;
 
   if (tid == 0) {
@@ -395,7 +403,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tma_load_4d(dst + pn * kKvPanel + r * 128, pool_map, full_bar, pn * 64, hk, row, 0);
             }
           } else {
-            const int row = kv_row0 + (i - n_old) * kBN;
+            const int row = kv_row0 + (tile0 + i - n_old) * kBN;
 #pragma unroll
             for (int pn = 0; pn < kHD / 64; ++pn)
               tma_load_4d(dst + pn * kKvPanel, dense_map, full_bar, pn * 64, hk, row, q_batch);
@@ -473,7 +481,8 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const float c = kSoftcap ? kLog2e : p.sm_scale * kLog2e;   // multiplies the raw (or capped) score
       const float pre = kSoftcap ? p.sm_scale / cap : 0.f;
       const int q_idx = m0 + row;                           // row inside its batch element / request
-      const int causal_limit = p.is_causal ? q_idx + off : 0x7fffffff;  // last visible key of this row
+      const int causal_limit = has_upper ? q_idx + off + up_extra : 0x7fffffff;  // last visible key of this row
+      const int key_floor = p.win_left >= 0 ? q_idx + off - p.win_left : int(0x80000000);  // first visible key
       int key_limit = causal_limit, seg_len = kv_len;       // of the segment the current tile belongs to
 
       if (kPaged && p.k_pages != nullptr && h % (p.heads / p.heads_kv) == 0) {
@@ -511,7 +520,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             const int key = key0 + e;
-            if (key > key_limit || key >= seg_len) r[e] = 0xff800000u;   // -inf
+            if (key > key_limit || key < key_floor || key >= seg_len) r[e] = 0xff800000u;   // -inf
           }
         }
       };
@@ -529,9 +538,10 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           key_limit = 0x7fffffff; seg_len = old_len;        // cached tokens: visible to every row
           need_mask = k0 + kBN > old_len;
         } else {
-          k0 -= n_old * kBN;
+          k0 += (tile0 - n_old) * kBN;
           key_limit = causal_limit; seg_len = kv_len;
-          need_mask = (p.is_causal && k0 + kBN - 1 > m0 + off) || (k0 + kBN > kv_len);
+          need_mask = (has_upper && k0 + kBN - 1 > m0 + off + up_extra) || (k0 + kBN > kv_len) ||
+                      (p.win_left >= 0 && k0 < m0 + kBM - 1 + off - p.win_left);
         }
 
         // ---- pass 1: row maximum.  TMEM loads are asynchronous: the next 32 columns are in flight
@@ -791,8 +801,10 @@ extern "C" size_t tb200_gqa_prefill_workspace_bytes(int batch, int heads, int he
 
 extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, void* o, float* lse, int dtype,
                                  int batch, int seqlen_q, int seqlen_kv, int heads, int heads_kv, int dim,
-                                 int is_causal, float sm_scale, float softcap, void* workspace,
-                                 size_t workspace_bytes, void* stream) {
+                                 int is_causal, float sm_scale, float softcap, int window_left, int window_right,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  if (window_left < -1 || window_right < -1)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "window sizes must be -1 (unlimited) or >= 0");
   if (!q || !k || !v || !o) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k, v and o must be non-null");
   if (batch <= 0 || seqlen_q <= 0 || seqlen_kv <= 0 || heads <= 0 || heads_kv <= 0)
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "batch, seqlen_q, seqlen_kv, heads and heads_kv must be positive");
@@ -819,6 +831,7 @@ extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, vo
   p.o = o; p.lse = lse; p.status = static_cast<int*>(workspace);
   p.batch = batch; p.heads = heads; p.heads_kv = heads_kv; p.seqlen_q = seqlen_q; p.seqlen_kv = seqlen_kv;
   p.is_causal = is_causal; p.sm_scale = sm_scale; p.softcap = softcap;
+  p.win_left = window_left; p.win_right = window_right;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return dim == 128 ? dispatch_prefill<128, false>(dtype, m, p, s) : dispatch_prefill<64, false>(dtype, m, p, s);
 }
@@ -830,7 +843,10 @@ extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const v
                                        int total_q, int total_kv, int batch, int max_seqlen_q, int heads,
                                        int heads_kv, int dim, int page_size,
                                        int64_t pool_tokens, int is_causal, float sm_scale, float softcap,
-                                       void* workspace, size_t workspace_bytes, void* stream) {
+                                       int window_left, int window_right, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+  if (window_left < -1 || window_right < -1)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "window sizes must be -1 (unlimited) or >= 0");
   if (!q || !k_new || !v_new || !o || !cu_seqlens_q)
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k_new, v_new, o and cu_seqlens_q must be non-null");
   if (total_q <= 0 || total_kv <= 0 || batch <= 0 || max_seqlen_q <= 0 || heads <= 0 || heads_kv <= 0)
@@ -842,6 +858,8 @@ extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const v
   if (!(sm_scale > 0.f)) TB200_FAIL(TB200_ERR_UNSUPPORTED, "sm_scale must be positive");
   if (softcap < 0.f) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "softcap must be non-negative");
   const bool has_cache = k_pages != nullptr || v_pages != nullptr || cache_seqlens != nullptr;
+  if (has_cache && (window_left >= 0 || window_right >= 0))
+    TB200_FAIL(TB200_ERR_UNSUPPORTED, "a sliding window over a paged cache is not served");
   if (has_cache && (cu_seqlens_kv != nullptr || total_kv != total_q))
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "with a cache, k_new / v_new hold exactly the rows of q (cu_seqlens_kv must be null)");
   if (!cu_seqlens_kv && total_kv != total_q)
@@ -880,6 +898,7 @@ extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const v
   p.o = o; p.lse = lse; p.status = static_cast<int*>(workspace);
   p.batch = batch; p.heads = heads; p.heads_kv = heads_kv; p.seqlen_q = max_seqlen_q; p.seqlen_kv = 0;
   p.is_causal = is_causal; p.sm_scale = sm_scale; p.softcap = softcap;
+  p.win_left = window_left; p.win_right = window_right;
   p.cu_q = cu_seqlens_q; p.cu_kv = cu_seqlens_kv; p.cache_lens = cache_seqlens; p.bt = block_table; p.bt_stride = block_table_stride;
   p.k_new = k_new; p.v_new = v_new; p.k_pages = k_pages; p.v_pages = v_pages; p.total_q = total_q;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -5,11 +5,17 @@ from .gqa_decode import (
     GQADecodeSm100Kernel,
     gqa_decode_paged_block_ns,
 )
-from .gqa_prefill import GQAPrefillPagedSm100Kernel, GQAPrefillSm100Kernel, GQAPrefillVarlenSm100Kernel
+from .gqa_prefill import (
+    GQAPrefillPagedSm100Kernel,
+    GQAPrefillSm100Kernel,
+    GQAPrefillVarlenSm100Kernel,
+    GQASlidingWindowSm100Kernel,
+    GQASlidingWindowVarlenSm100Kernel,
+)
 from .kernel_base import Kernel
 
 __all__ = [
     "AttentionCall", "CallSpec", "Kernel", "GQADecodeSm100Kernel", "GQADecodePagedSm100Kernel",
     "GQADecodePagedFp8Sm100Kernel", "GQAPrefillSm100Kernel", "GQAPrefillVarlenSm100Kernel",
-    "GQAPrefillPagedSm100Kernel", "gqa_decode_paged_block_ns",
+    "GQAPrefillPagedSm100Kernel", "GQASlidingWindowSm100Kernel", "GQASlidingWindowVarlenSm100Kernel", "gqa_decode_paged_block_ns",
 ]

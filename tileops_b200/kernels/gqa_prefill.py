@@ -19,7 +19,8 @@ from .. import functional as F
 from .call_spec import ATTENTION_DTYPES, dense_prefill_region
 from .kernel_base import Kernel
 
-__all__ = ["GQAPrefillSm100Kernel", "GQAPrefillVarlenSm100Kernel", "GQAPrefillPagedSm100Kernel"]
+__all__ = ["GQAPrefillSm100Kernel", "GQAPrefillVarlenSm100Kernel", "GQAPrefillPagedSm100Kernel",
+           "GQASlidingWindowSm100Kernel", "GQASlidingWindowVarlenSm100Kernel"]
 
 
 class GQAPrefillSm100Kernel(Kernel):
@@ -37,8 +38,7 @@ class GQAPrefillSm100Kernel(Kernel):
         super().__init__(device_index=device_index)
         if dim not in (64, 128):
             raise ValueError(f"GQAPrefillSm100Kernel supports head dim 64 and 128, got {dim}")
-        if window_size_left != -1 or window_size_right != -1:
-            raise ValueError("GQAPrefillSm100Kernel does not serve sliding-window calls")
+        self.window_size_left, self.window_size_right = window_size_left, window_size_right
         self.batch, self.heads, self.heads_kv, self.dim = batch, heads, heads_kv, dim
         self.max_seqlen_q, self.max_seqlen_kv = max_seqlen_q, max_seqlen_kv
         self.is_causal, self.dtype = is_causal, dtype
@@ -61,7 +61,8 @@ class GQAPrefillSm100Kernel(Kernel):
                 f"packed q/k must hold {B}x{Sq} and {B}x{Skv} tokens, got {q.shape[0]} and {k.shape[0]}")
         out = F.gqa_prefill(q.view(B, Sq, self.heads, self.dim), k.view(B, Skv, self.heads_kv, self.dim),
                             v.view(B, Skv, self.heads_kv, self.dim), is_causal=self.is_causal,
-                            sm_scale=self.sm_scale, softcap=self.softcap, return_lse=return_lse)
+                            sm_scale=self.sm_scale, softcap=self.softcap, return_lse=return_lse,
+                            window_size_left=self.window_size_left, window_size_right=self.window_size_right)
         if return_lse:
             return out[0].view(q.shape), out[1]
         return out.view(q.shape)
@@ -97,9 +98,8 @@ class GQAPrefillVarlenSm100Kernel(Kernel):
                  device_index=None) -> None:
         super().__init__(device_index=device_index)
         if dim not in (64, 128):
-            raise ValueError(f"GQAPrefillVarlenSm100Kernel supports head dim 64 and 128, got {dim}")
-        if window_size_left != -1 or window_size_right != -1:
-            raise ValueError("GQAPrefillVarlenSm100Kernel does not serve sliding-window calls")
+            raise ValueError(f"{type(self).__name__} supports head dim 64 and 128, got {dim}")
+        self.window_size_left, self.window_size_right = window_size_left, window_size_right
         self.batch, self.heads, self.heads_kv, self.dim = batch, heads, heads_kv, dim
         self.max_seqlen_q, self.max_seqlen_kv = max_seqlen_q, max_seqlen_kv
         self.is_causal, self.dtype = is_causal, dtype
@@ -118,7 +118,55 @@ class GQAPrefillVarlenSm100Kernel(Kernel):
         self._require_cuda(q=q, k=k, v=v, cu_seqlens_q=cu_seqlens_q, cu_seqlens_kv=cu_seqlens_kv)
         return F.gqa_prefill_paged(q, k, v, None, None, cu_seqlens_q, None, None, self.max_seqlen_q,
                                    is_causal=self.is_causal, sm_scale=self.sm_scale, softcap=self.softcap,
-                                   return_lse=return_lse, cu_seqlens_kv=cu_seqlens_kv)
+                                   return_lse=return_lse, cu_seqlens_kv=cu_seqlens_kv,
+                                   window_size_left=self.window_size_left,
+                                   window_size_right=self.window_size_right)
+
+
+class GQASlidingWindowVarlenSm100Kernel(GQAPrefillVarlenSm100Kernel):
+    """Packed prefill with a sliding window, in the ``gqa_sliding_window_varlen_fwd_kernel`` slot
+    (the reference's ``GQASlidingWindowVarlenFwdWgmmaPipelinedKernel``, a Hopper WGMMA kernel).
+    Same tcgen05 kernel: key tiles outside the window of a whole 128-row tile are skipped, the
+    window edges are masked in registers."""
+
+    @classmethod
+    def applies(cls, call) -> bool:
+        from .call_spec import uses_sliding_window
+        return (uses_sliding_window(call) and not call.is_fp8 and call.backend in ("auto", "sliding_window")
+                and call.dim in (64, 128) and call.dtype in ATTENTION_DTYPES)
+
+
+class GQASlidingWindowSm100Kernel(Kernel):
+    """Fixed-length (BSHD, Sq == Skv) prefill with a sliding window, in the
+    ``gqa_sliding_window_fwd_kernel`` slot (the reference's
+    ``GQASlidingWindowFwdWgmmaPipelinedKernel``; constructor keywords as in
+    ``src/tileops/ops/attention/gqa.py:1511-1529``)."""
+
+    supported_archs = [100]
+    general = True
+
+    @classmethod
+    def applies(cls, call) -> bool:
+        return call.dim in (64, 128) and call.dtype in ATTENTION_DTYPES
+
+    def __init__(self, batch, heads, heads_kv, seq_len, dim, is_causal, window_size_left, window_size_right,
+                 dtype, config: Optional[dict] = None, tune: bool = False, device_index=None) -> None:
+        super().__init__(device_index=device_index)
+        if dim not in (64, 128):
+            raise ValueError(f"GQASlidingWindowSm100Kernel supports head dim 64 and 128, got {dim}")
+        self.batch, self.heads, self.heads_kv, self.seq_len, self.dim = batch, heads, heads_kv, seq_len, dim
+        self.is_causal, self.dtype = is_causal, dtype
+        self.window_size_left, self.window_size_right = window_size_left, window_size_right
+        self.init_config(config, tune)
+
+    @property
+    def default_config(self) -> dict:
+        return {"block_M": 128, "block_N": 64, "threads": 192}
+
+    def forward(self, q, k, v):
+        self._require_cuda(q=q, k=k, v=v)
+        return F.gqa_prefill(q, k, v, is_causal=self.is_causal, window_size_left=self.window_size_left,
+                             window_size_right=self.window_size_right)
 
 
 class GQAPrefillPagedSm100Kernel(Kernel):

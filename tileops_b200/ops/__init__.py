@@ -6,6 +6,8 @@ from .gqa import (
     GroupedQueryAttentionPrefillFwdOp,
     GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp,
     GroupedQueryAttentionPrefillVarlenFwdOp,
+    GroupedQueryAttentionSlidingWindowFwdOp,
+    GroupedQueryAttentionSlidingWindowVarlenFwdOp,
 )
 from .op_base import Op
 
@@ -15,6 +17,8 @@ __all__ = [
     "GroupedQueryAttentionPrefillFwdOp",
     "GroupedQueryAttentionPrefillVarlenFwdOp",
     "GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp",
+    "GroupedQueryAttentionSlidingWindowFwdOp",
+    "GroupedQueryAttentionSlidingWindowVarlenFwdOp",
     "GroupedQueryAttentionDecodeWithKVCacheFwdOp",
     "GroupedQueryAttentionDecodePagedWithKVCacheFwdOp",
     "GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp",

@@ -29,6 +29,8 @@ from ..kernels import (
     GQAPrefillPagedSm100Kernel,
     GQAPrefillSm100Kernel,
     GQAPrefillVarlenSm100Kernel,
+    GQASlidingWindowSm100Kernel,
+    GQASlidingWindowVarlenSm100Kernel,
 )
 from ..kernels.kernel_base import Kernel
 from .op_base import Op
@@ -49,6 +51,8 @@ __all__ = [
     "GroupedQueryAttentionPrefillFwdOp",
     "GroupedQueryAttentionPrefillVarlenFwdOp",
     "GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp",
+    "GroupedQueryAttentionSlidingWindowFwdOp",
+    "GroupedQueryAttentionSlidingWindowVarlenFwdOp",
     "GroupedQueryAttentionDecodeWithKVCacheFwdOp",
     "GroupedQueryAttentionDecodePagedWithKVCacheFwdOp",
     "GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp",
@@ -208,7 +212,8 @@ class GroupedQueryAttentionPrefillFwdOp(Op):
     @property
     def default_kernel_map(self) -> Dict[str, type]:
         return {"gqa_prefill_fwd_kernel": GQAPrefillSm100Kernel,
-                "gqa_prefill_varlen_fwd_kernel": GQAPrefillVarlenSm100Kernel}
+                "gqa_prefill_varlen_fwd_kernel": GQAPrefillVarlenSm100Kernel,
+                "gqa_sliding_window_varlen_fwd_kernel": GQASlidingWindowVarlenSm100Kernel}
 
     def attention_call(self, *, is_fp8: bool, is_uniform: bool) -> AttentionCall:
         return AttentionCall(
@@ -600,6 +605,175 @@ class GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp(Op):
     def total_memory(self) -> int:
         raise NotImplementedError("total_memory is not defined for paged varlen ops; "
                                   "compute per-sample from cu_seqlens and cache_seqlens at call time.")
+
+
+def _validate_windows(window_size_left: int, window_size_right: int) -> None:
+    if window_size_left != -1 and window_size_left < 0:
+        raise ValueError(f"window_size_left must be -1 (unlimited) or >= 0, got {window_size_left}")
+    if window_size_right != -1 and window_size_right < 0:
+        raise ValueError(f"window_size_right must be -1 (unlimited) or >= 0, got {window_size_right}")
+
+
+class GroupedQueryAttentionSlidingWindowFwdOp(Op):
+    """Fixed-length GQA forward with sliding-window attention (BSHD, Sq == Skv).  Row ``q_pos`` sees
+    key ``k_pos`` iff ``k_pos <= q_pos`` (causal), ``k_pos >= q_pos - window_size_left`` (when >= 0) and
+    ``k_pos <= q_pos + window_size_right`` (when >= 0).  Mirrors
+    ``src/tileops/ops/attention/gqa.py:1457-1627`` of the reference."""
+
+    def __init__(self, batch: int, heads: int, heads_kv: int, seq_len: int, dim: int, is_causal: bool = True,
+                 window_size_left: int = -1, window_size_right: int = -1,
+                 kernel_map: Optional[Dict[str, type]] = None, tune: bool = False) -> None:
+        if heads % heads_kv != 0:
+            raise ValueError("heads must be divisible by heads_kv")
+        _validate_windows(window_size_left, window_size_right)
+        self.batch, self.heads, self.heads_kv, self.seq_len, self.dim = batch, heads, heads_kv, seq_len, dim
+        self.is_causal = is_causal
+        self.window_size_left, self.window_size_right = window_size_left, window_size_right
+        self.dtype = None
+        self.tune = tune
+        self.dispatch_kernel(kernel_map)
+
+    @property
+    def default_kernel_map(self) -> Dict[str, type]:
+        return {"gqa_sliding_window_fwd_kernel": GQASlidingWindowSm100Kernel}
+
+    def _get_kernel(self, inputs, dtype: torch.dtype) -> Kernel:
+        return self.get_or_build_kernel(
+            "gqa_sliding_window_fwd_kernel", inputs, key=dtype,
+            build=lambda: self.kernel_map["gqa_sliding_window_fwd_kernel"](
+                batch=self.batch, heads=self.heads, heads_kv=self.heads_kv, seq_len=self.seq_len, dim=self.dim,
+                is_causal=self.is_causal, window_size_left=self.window_size_left,
+                window_size_right=self.window_size_right, dtype=dtype, tune=self.tune))
+
+    def _infer_output_shapes(self, q_shape, k_shape, v_shape) -> Dict[str, tuple]:
+        return {"o": tuple(q_shape)}
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        for t, name in ((q, "q"), (k, "k"), (v, "v")):
+            if t.device.type != "cuda":
+                raise ValueError(f"{name} must be on a cuda device, got {t.device}")
+            if t.dtype != q.dtype:
+                raise ValueError(f"{name} dtype {t.dtype} does not match q dtype {q.dtype}")
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        want_q = (self.batch, self.seq_len, self.heads, self.dim)
+        want_kv = (self.batch, self.seq_len, self.heads_kv, self.dim)
+        if tuple(q.shape) != want_q:
+            raise ValueError(f"q shape {q.shape} does not match expected {want_q}")
+        if tuple(k.shape) != want_kv:
+            raise ValueError(f"k shape {k.shape} does not match expected {want_kv}")
+        if tuple(v.shape) != want_kv:
+            raise ValueError(f"v shape {v.shape} does not match expected {want_kv}")
+        self.dtype = q.dtype
+        return self._get_kernel((q, k, v), q.dtype).forward(q, k, v)
+
+    @property
+    def total_flops(self) -> int:
+        S, wl, wr = self.seq_len, self.window_size_left, self.window_size_right
+        attended = 0
+        for i in range(S):
+            hi = i if self.is_causal else (min(S - 1, i + wr) if wr >= 0 else S - 1)
+            lo = max(0, i - wl) if wl >= 0 else 0
+            attended += hi - lo + 1
+        return 4 * self.batch * self.heads * attended * self.dim
+
+    @property
+    def total_memory(self) -> int:
+        if self.dtype is None:
+            raise RuntimeError(f"{type(self).__name__}.total_memory requires a prior forward() "
+                               "call to bind the element type")
+        return 2 * self.batch * self.seq_len * (self.heads + self.heads_kv) * self.dim * self.dtype.itemsize
+
+    def eval_roofline(self) -> tuple:
+        return self.total_flops, self.total_memory
+
+
+class GroupedQueryAttentionSlidingWindowVarlenFwdOp(Op):
+    """Packed GQA forward with sliding-window attention; per request, with
+    ``offset = seqlen_k - seqlen_q`` (bottom-right), row ``q_pos`` sees ``k_pos`` iff
+    ``k_pos <= q_pos + offset`` (causal), ``k_pos >= q_pos + offset - window_size_left`` (when >= 0) and
+    ``k_pos <= q_pos + offset + window_size_right`` (when >= 0).  Mirrors
+    ``src/tileops/ops/attention/gqa.py:1630-1831`` of the reference."""
+
+    def __init__(self, batch: int, heads: int, heads_kv: int, dim: int, is_causal: bool = True,
+                 window_size_left: int = -1, window_size_right: int = -1,
+                 accum_dtype: torch.dtype = torch.float32,
+                 kernel_map: Optional[Dict[str, type]] = None, tune: bool = False) -> None:
+        if heads % heads_kv != 0:
+            raise ValueError("heads must be divisible by heads_kv")
+        _validate_windows(window_size_left, window_size_right)
+        self.batch, self.heads, self.heads_kv, self.dim = batch, heads, heads_kv, dim
+        self.is_causal = is_causal
+        self.window_size_left, self.window_size_right = window_size_left, window_size_right
+        self.accum_dtype = accum_dtype
+        self.tune = tune
+        self.dispatch_kernel(kernel_map)
+
+    @property
+    def default_kernel_map(self) -> Dict[str, type]:
+        return {"gqa_sliding_window_varlen_fwd_kernel": GQASlidingWindowVarlenSm100Kernel}
+
+    def _get_kernel(self, inputs, dtype: torch.dtype, max_seqlen_q: int) -> Kernel:
+        return self.get_or_build_kernel(
+            "gqa_sliding_window_varlen_fwd_kernel", inputs, key=(dtype, max_seqlen_q),
+            build=lambda: self.kernel_map["gqa_sliding_window_varlen_fwd_kernel"](
+                batch=self.batch, heads=self.heads, heads_kv=self.heads_kv, max_seqlen_q=max_seqlen_q,
+                max_seqlen_kv=max_seqlen_q, dim=self.dim, is_causal=self.is_causal, dtype=dtype,
+                window_size_left=self.window_size_left, window_size_right=self.window_size_right,
+                accum_dtype=self.accum_dtype, tune=self.tune))
+
+    def _infer_output_shapes(self, q_shape, *rest) -> Dict[str, tuple]:
+        return {"o": tuple(q_shape)}
+
+    def forward(self, q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int) -> torch.Tensor:
+        for t, name in ((q, "q"), (k, "k"), (v, "v")):
+            if t.device.type != "cuda":
+                raise ValueError(f"{name} must be on a cuda device, got {t.device}")
+            if t.dtype != q.dtype:
+                raise ValueError(f"{name} dtype {t.dtype} does not match q dtype {q.dtype}")
+            if not t.is_contiguous():
+                raise ValueError(f"{name} must be contiguous")
+        if q.ndim != 3 or q.shape[1] != self.heads or q.shape[2] != self.dim:
+            raise ValueError(f"q shape {q.shape} incompatible with heads={self.heads}, dim={self.dim}")
+        for t, name in ((k, "k"), (v, "v")):
+            if t.ndim != 3 or t.shape[1] != self.heads_kv or t.shape[2] != self.dim:
+                raise ValueError(f"{name} shape {t.shape} incompatible with heads_kv={self.heads_kv}, dim={self.dim}")
+        for cu, name in ((cu_seqlens_q, "cu_seqlens_q"), (cu_seqlens_k, "cu_seqlens_k")):
+            if cu.shape[0] != self.batch + 1:
+                raise ValueError(f"{name}.shape[0] ({cu.shape[0]}) must equal batch+1 ({self.batch + 1})")
+        for cu, name in ((cu_seqlens_q, "cu_seqlens_q"), (cu_seqlens_k, "cu_seqlens_k")):
+            if cu.device.type != "cuda":
+                raise ValueError(f"{name} must be on a cuda device, got {cu.device}")
+            if cu.dtype != torch.int32:
+                raise ValueError(f"{name} must have dtype int32, got {cu.dtype}")
+            if not cu.is_contiguous():
+                raise ValueError(f"{name} must be contiguous")
+        for cu, name in ((cu_seqlens_q, "cu_seqlens_q"), (cu_seqlens_k, "cu_seqlens_k")):
+            if cu[0].item() != 0:
+                raise ValueError(f"{name}[0] must be 0, got {cu[0].item()}")
+        for cu, name in ((cu_seqlens_q, "cu_seqlens_q"), (cu_seqlens_k, "cu_seqlens_k")):
+            if not torch.all(cu[1:] >= cu[:-1]):
+                raise ValueError(f"{name} must be non-decreasing")
+        if cu_seqlens_q[-1].item() > q.shape[0]:
+            raise ValueError(f"cu_seqlens_q[-1] ({cu_seqlens_q[-1].item()}) exceeds q.shape[0] ({q.shape[0]})")
+        if cu_seqlens_k[-1].item() > k.shape[0]:
+            raise ValueError(f"cu_seqlens_k[-1] ({cu_seqlens_k[-1].item()}) exceeds k.shape[0] ({k.shape[0]})")
+        actual_max_q = int((cu_seqlens_q[1:] - cu_seqlens_q[:-1]).max().item())
+        if max_seqlen_q < actual_max_q:
+            raise ValueError(f"max_seqlen_q ({max_seqlen_q}) must be >= actual max Q "
+                             f"sequence length ({actual_max_q})")
+        self.dtype = q.dtype
+        return self._get_kernel((q, k, v, cu_seqlens_q, cu_seqlens_k), q.dtype, max_seqlen_q).forward(
+            q, k, v, cu_seqlens_q, cu_seqlens_k)
+
+    @property
+    def total_flops(self) -> int:
+        raise NotImplementedError("total_flops is not defined for varlen ops; "
+                                  "compute per-sample from cu_seqlens at call time.")
+
+    @property
+    def total_memory(self) -> int:
+        raise NotImplementedError("total_memory is not defined for varlen ops; "
+                                  "compute per-sample from cu_seqlens at call time.")
 
 
 class GroupedQueryAttentionDecodeWithKVCacheFwdOp(Op):
