@@ -252,6 +252,29 @@ def test_backend_target_builder_receives_specs_and_params(clean_registry):
     assert op2._settled_target is None                      # a failed first call settles nothing
 
 
+def test_b200_plugin_registers_a_detector_and_a_builder_per_op(clean_registry):
+    from tileops_b200 import plugin
+    plugin.register(backend)
+    assert plugin.TARGET in registry.known_targets()
+    assert registry.DETECTORS[plugin.TARGET] is plugin.detect
+    assert plugin.detect(torch.device("cpu")) is False
+    m = tileops_b200.manifest.load_manifest()
+    for op_name, builder in plugin.BUILDERS.items():
+        assert op_name in m and registry.BUILDERS[(op_name, plugin.TARGET)] is builder
+    with pytest.raises(backend.BackendError):
+        plugin.register(backend)                            # one detector per target
+    # builders are described with specs and manifest params only; nothing touches a device
+    spec = backend.TensorSpec
+    q = spec(torch.device("cuda", 0), torch.bfloat16, (4, 32, 128))
+    kv = spec(torch.device("cuda", 0), torch.bfloat16, (4096, 8, 128))
+    meta = spec(torch.device("cuda", 0), torch.int32, (4,))
+    assert callable(plugin.build_paged_decode(q, kv, kv, meta, meta, page_size=64, sm_scale=None, softcap=None))
+    with pytest.raises(ValueError, match="cache of q's element type"):
+        plugin.build_paged_prefill(q, q, q, spec(kv.device, torch.float8_e4m3fn, kv.shape), kv, page_size=64)
+    text = open(os.path.join(ROOT, "pyproject.toml")).read()
+    assert '[project.entry-points."tileops.backends"]' in text and 'b200 = "tileops_b200.plugin"' in text
+
+
 def test_manifest_and_profile():
     m = tileops_b200.manifest.load_manifest()
     for name in ("GroupedQueryAttentionFwdOp", "GroupedQueryAttentionPrefillFwdOp",
