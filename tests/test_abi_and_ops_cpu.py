@@ -275,6 +275,29 @@ def test_b200_plugin_registers_a_detector_and_a_builder_per_op(clean_registry):
     assert '[project.entry-points."tileops.backends"]' in text and 'b200 = "tileops_b200.plugin"' in text
 
 
+def test_mha_decode_rows_map_onto_a_gqa_group():
+    from tileops_b200.kernels.mha_decode import _as_groups, _from_groups
+    from tileops_b200.ops import MultiHeadAttentionDecodePagedWithKVCacheFwdOp, MultiHeadAttentionDecodeWithKVCacheFwdOp
+    from oracle import gqa_oracle as O
+    g = torch.Generator().manual_seed(3)
+    B, Sq, H, D, S = 2, 3, 4, 16, 40
+    q = torch.randn(B, Sq, H, D, generator=g)
+    k = torch.randn(B, S, H, D, generator=g)
+    v = torch.randn(B, S, H, D, generator=g)
+    # the q rows of one head, laid out as the q-head group of that KV head, give plain per-head attention
+    o = _from_groups(O.decode_ref(_as_groups(q), k, v), B, Sq, H, D)
+    want = torch.softmax(torch.einsum("bqhd,bkhd->bhqk", q, k) * D ** -0.5, dim=-1)
+    want = torch.einsum("bhqk,bkhd->bqhd", want, v)
+    torch.testing.assert_close(o, want, atol=1e-5, rtol=1e-5)
+    assert _as_groups(q[:, :1]).shape == (B, H, D)
+    op = MultiHeadAttentionDecodeWithKVCacheFwdOp(B, H, Sq, 64, D)
+    assert list(op.kernel_map) == ["mha_decode_kernel"]
+    with pytest.raises(ValueError, match="more than seqlen_kv"):
+        op(q, torch.zeros(B, 65, H, D), torch.zeros(B, 65, H, D))
+    assert list(MultiHeadAttentionDecodePagedWithKVCacheFwdOp(B, H, 1, 128, 64, 64).kernel_map) == [
+        "mha_decode_paged_kernel"]
+
+
 def test_manifest_and_profile():
     m = tileops_b200.manifest.load_manifest()
     for name in ("GroupedQueryAttentionFwdOp", "GroupedQueryAttentionPrefillFwdOp",

@@ -45,6 +45,21 @@ constexpr int kMinChunkTiles = 2;  // never cut a sequence into runs shorter tha
 #ifndef TB200_DEC_BLOCKS16
 #define TB200_DEC_BLOCKS16 2
 #endif
+// FP8 caches: 4 CTAs per SM with a 3-stage ring (at most 128 registers) measured 2-6 % faster on
+// ragged and long-context batches than 3 CTAs with 4 stages, and the same on uniform 4k contexts.
+// Cross-item prefetch (off: measured 1-6 % SLOWER on B200): while the last tiles of an item are
+// computed (no loads of this item are left to issue), the first tiles of the CTA's NEXT item are
+// requested into L2, so that the next item's pipeline fill hits L2.  The extra code and live
+// registers in the tile loop cost more than the shorter fill saves.
+#ifndef TB200_DEC_PREFETCH_NEXT
+#define TB200_DEC_PREFETCH_NEXT 0
+#endif
+#ifndef TB200_DEC_STAGES8
+#define TB200_DEC_STAGES8 3
+#endif
+#ifndef TB200_DEC_BLOCKS8
+#define TB200_DEC_BLOCKS8 4
+#endif
 constexpr int kItemsPerCta = TB200_DEC_ITEMS_PER_CTA;  // target number of work items per resident CTA
 constexpr int kMaxBatch = 4096;
 
@@ -84,10 +99,15 @@ struct Cfg {
   static constexpr int kChunksPerRow = kRowBytes / 16;
   static constexpr int kTileBytes = kTile * kRowStride;
   static constexpr int kStageBytes = 2 * kTileBytes + (FP8 ? 2 * kTile * 4 : 0);
-  static constexpr int kStages = FP8 ? 4 : TB200_DEC_STAGES16;
-  static constexpr int kMinBlocks = FP8 ? 3 : TB200_DEC_BLOCKS16;
+  static constexpr int kStages = FP8 ? TB200_DEC_STAGES8 : TB200_DEC_STAGES16;
   static constexpr int kOStride = D + 4;  // fp32 words per head in the cross-warp merge area
 };
+
+// Resident CTAs per SM the kernel is compiled for (it bounds the registers per thread): the FP8
+// kernel for up to 8 q heads per KV head fits 128 registers, the 16-head one does not.
+__host__ __device__ constexpr int min_blocks(bool fp8, int nt) {
+  return fp8 ? (nt == 1 ? TB200_DEC_BLOCKS8 : 3) : TB200_DEC_BLOCKS16;
+}
 
 template <int D, bool FP8>
 size_t smem_bytes(int batch, int nt) {
@@ -111,7 +131,7 @@ __device__ __forceinline__ float apply_softcap(float x, float cap, float inv_cap
 //      lo stacked on the k axis of one MMA).  Needs one scale per tile and tensor: tiles that lie
 //      inside one page (page_size a multiple of 64); other layouts use the f16 expansion path.
 template <int D, bool FP8, typename T, int NT, typename TO, bool F8M = false>
-__global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT)) gqa_decode_kernel(DecodeParams p) {
   using C = Cfg<D, FP8>;
   constexpr int kKSteps = D / 16;  // MMAs per 16 tokens for S^T, and m-tiles of O^T
   extern __shared__ __align__(128) unsigned char smem[];
@@ -492,6 +512,34 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
       }
     };
 
+#if TB200_DEC_PREFETCH_NEXT
+    // (sequence, KV head, first tile, end tile, length) of the CTA's next item, or false.  The id was
+    // requested before this item's tile loop; it is visible after the loop's first barrier.
+    auto next_item_desc = [&](int& nb, int& nhk, int& nt0, int& nt1, int& nlen) -> bool {
+      const int nitem = s_misc[6 + ((round + 1) & 1)];
+      if (nitem >= total_items) return false;
+      const int nrun = nitem / lanes_per_run;
+      nhk = (nitem - nrun * lanes_per_run) / p.n_hb;
+      int lo2 = 0, hi2 = p.batch - 1;
+      while (lo2 < hi2) {
+        const int mid = (lo2 + hi2 + 1) >> 1;
+        if (s_prefix[mid] <= nrun) lo2 = mid; else hi2 = mid - 1;
+      }
+      nb = lo2;
+      nlen = max(p.lens ? p.lens[nb] : p.uniform_len, 0);
+      const int ntiles = (nlen + kTile - 1) / kTile;
+      const int nruns = s_prefix[nb + 1] - s_prefix[nb];
+      const int nrt = (ntiles + nruns - 1) / nruns;
+      nt0 = min((nrun - s_prefix[nb]) * nrt, ntiles);
+      nt1 = min(nt0 + nrt, ntiles);
+      return nt1 > nt0;
+    };
+    // Only where a tile lies inside one page (or there is no table), and only for items long enough
+    // that the table entries fetched at the first iteration have landed by the time they are used.
+    const bool prefetch_ok = (!bt_row || p.tile_in_page) && n_tiles >= 2 * (C::kStages - 1);
+    const int prefetch_at = n_tiles - (C::kStages - 1);      // first iteration with no load left to issue
+#endif
+
     // ---- running state ----------------------------------------------------------------
     float oacc[NT][kKSteps][4];
     float m_run[NT][2], l_run[NT][2];
@@ -522,8 +570,44 @@ __global__ void __launch_bounds__(kThreads, Cfg<D, FP8>::kMinBlocks) gqa_decode_
       {
         const int nx = it + C::kStages - 1;
         if (nx < n_tiles) issue_tile(tile0 + nx, nx % C::kStages);
+#if TB200_DEC_PREFETCH_NEXT
+        if (prefetch_ok && it == 0 && p.bt && tid < C::kStages - 1) {
+          // block-table entries of the next item's first tiles: asynchronous 4-byte copies that ride
+          // in this iteration's group, so no thread waits for them
+          int nb, nhk, nt0, nt1, nlen;
+          if (next_item_desc(nb, nhk, nt0, nt1, nlen) && nt0 + tid < nt1)
+            cp_async_4(smem_u32(&s_misc[8 + tid]),
+                       p.bt + size_t(nb) * p.bt_stride + ((nt0 + tid) * kTile) / p.page_size, 4);
+        }
+#endif
         cp_async_commit();
       }
+#if TB200_DEC_PREFETCH_NEXT
+      if (prefetch_ok && it == prefetch_at) {
+        int nb, nhk, nt0, nt1, nlen;
+        if (next_item_desc(nb, nhk, nt0, nt1, nlen)) {
+          constexpr int kLines = C::kRowBytes >= 128 ? C::kRowBytes / 128 : 1;   // 128-byte lines per token row
+          const size_t head_off = (size_t(nhk) * p.head_stride + (p.bt ? 0 : size_t(nb) * p.batch_stride)) * C::kEsize;
+          const unsigned char* nk = reinterpret_cast<const unsigned char*>(p.k) + head_off;
+          const unsigned char* nv = reinterpret_cast<const unsigned char*>(p.v) + head_off;
+#pragma unroll 1
+          for (int st2 = 0; st2 < C::kStages - 1; ++st2) {
+            const int tile = nt0 + st2;
+            if (tile >= nt1) break;
+            const int tok0 = tile * kTile;
+            const int64_t phys0 = p.bt ? int64_t(s_misc[8 + st2]) * p.page_size + (tok0 % p.page_size) : tok0;
+            for (int idx = tid; idx < kTile * kLines; idx += kThreads) {
+              const int row = idx / kLines, line = idx % kLines;
+              if (tok0 + row < nlen) {
+                const size_t off = size_t(phys0 + row) * tok_bytes + line * 128;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(nk + off));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(nv + off));
+              }
+            }
+          }
+        }
+      }
+#endif
       const int stage = it % C::kStages;
       const uint32_t st_base = ring_u32 + stage * C::kStageBytes;
       const int tok_a = (tile0 + it) * kTile + warp * 16 + g8;  // token of c0/c1; c2/c3 is +8
@@ -802,7 +886,7 @@ Layout make_layout(int batch, int heads, int heads_kv, int dim, bool fp8) {
   L.hb = group < 16 ? group : 16;
   L.nt = L.hb <= 8 ? 1 : 2;
   L.n_hb = (group + L.hb - 1) / L.hb;
-  const int blocks_per_sm = fp8 ? 3 : TB200_DEC_BLOCKS16;
+  const int blocks_per_sm = min_blocks(fp8, L.nt);
   L.grid = sm_count() * blocks_per_sm;
   L.target_items = sm_count() * 3 * kItemsPerCta;  // independent of the cache dtype
   L.max_items = batch * heads_kv * L.n_hb + L.target_items;

@@ -13,9 +13,10 @@ from .gqa_prefill import (
     GQASlidingWindowVarlenSm100Kernel,
 )
 from .kernel_base import Kernel
+from .mha_decode import MHADecodePagedSm100Kernel, MHADecodeSm100Kernel
 
 __all__ = [
     "AttentionCall", "CallSpec", "Kernel", "GQADecodeSm100Kernel", "GQADecodePagedSm100Kernel",
     "GQADecodePagedFp8Sm100Kernel", "GQAPrefillSm100Kernel", "GQAPrefillVarlenSm100Kernel",
-    "GQAPrefillPagedSm100Kernel", "GQASlidingWindowSm100Kernel", "GQASlidingWindowVarlenSm100Kernel", "gqa_decode_paged_block_ns",
+    "GQAPrefillPagedSm100Kernel", "GQASlidingWindowSm100Kernel", "GQASlidingWindowVarlenSm100Kernel", "gqa_decode_paged_block_ns", "MHADecodeSm100Kernel", "MHADecodePagedSm100Kernel",
 ]

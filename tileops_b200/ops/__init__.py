@@ -9,6 +9,7 @@ from .gqa import (
     GroupedQueryAttentionSlidingWindowFwdOp,
     GroupedQueryAttentionSlidingWindowVarlenFwdOp,
 )
+from .mha import MultiHeadAttentionDecodePagedWithKVCacheFwdOp, MultiHeadAttentionDecodeWithKVCacheFwdOp
 from .op_base import Op
 
 __all__ = [
@@ -22,4 +23,6 @@ __all__ = [
     "GroupedQueryAttentionDecodeWithKVCacheFwdOp",
     "GroupedQueryAttentionDecodePagedWithKVCacheFwdOp",
     "GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp",
+    "MultiHeadAttentionDecodeWithKVCacheFwdOp",
+    "MultiHeadAttentionDecodePagedWithKVCacheFwdOp",
 ]
