@@ -12,6 +12,7 @@
  * reference operators (paths relative to the tile-ai/TileOPs tree):
  *   tb200_gqa_decode        GQADecodeKernel.forward        src/tileops/kernels/attention/gqa_decode.py:555-615
  *                           GQADecodePagedKernel.forward   src/tileops/kernels/attention/gqa_decode_paged.py:669-746
+ *   tb200_rope_neox_packed  rotation step of GQAPrefillPagedWithKVCacheRopeFwdKernel  src/tileops/kernels/attention/gqa_fwd.py:1463-2122
  *   tb200_gqa_prefill_paged GQAPrefillPagedWithKVCacheFwdKernel  src/tileops/kernels/attention/gqa_fwd.py:600-1002
  *   tb200_gqa_prefill       GQAPrefillFwdKernel / GQAPrefillFwdWsPersistentCausalKernel
  *                                                          src/tileops/kernels/attention/gqa_fwd.py:519-597,
@@ -210,6 +211,25 @@ int tb200_gqa_prefill_paged(const void* q, const void* k_new, const void* v_new,
                             int is_causal, float sm_scale, float softcap,
                             int window_left, int window_right,
                             void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * GPT-NeoX rotary embedding of a packed tensor at the positions of a prefill chunk.
+ *
+ * The rotation the reference's fused-RoPE paged prefill applies to q and k_new
+ * (GQAPrefillPagedWithKVCacheRopeFwdKernel, src/tileops/kernels/attention/gqa_fwd.py:1463-2122;
+ * arithmetic of RopeNeoxPositionIdsFwdOp, src/tileops/ops/rope.py:544-640), as a pass of its own:
+ *   x, y [total_tokens, heads, dim] dtype (F16 | BF16), y may not alias x
+ *   cos_table, sin_table [max_position, rotary_dim / 2] dtype
+ *   token t of request b (cu_seqlens_q[b] <= t < cu_seqlens_q[b+1]) has position
+ *   cache_seqlens[b] + t - cu_seqlens_q[b]  (cache_seqlens NULL: 0)
+ * The first rotary_dim dims are rotated about their midpoint in fp32, the rest are copied.
+ * status: optional device int (zeroed by the caller); set to 401 if a position falls outside
+ * [0, max_position) (that token is rotated with position 0).
+ * ------------------------------------------------------------------------- */
+int tb200_rope_neox_packed(const void* x, void* y, const void* cos_table, const void* sin_table,
+                           const int32_t* cu_seqlens_q, const int32_t* cache_seqlens, int dtype,
+                           int total_tokens, int batch, int heads, int dim, int rotary_dim,
+                           int max_position, int* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -277,6 +277,31 @@ def prefill_packed_ref(q, k, v, cu_seqlens_q, cu_seqlens_kv, is_causal=True,
     return torch.cat(outs, dim=0)
 
 
+def rope_tables_ref(rotary_dim: int, max_position: int, base: float = 10000.0, dtype=torch.float32):
+    """cos / sin tables [max_position, rotary_dim/2], computed in fp32 and cast to ``dtype``; follows
+    ``base_freqs`` (``src/tileops/ops/rope.py:97-120``)."""
+    half = rotary_dim // 2
+    freqs = 1.0 / (base ** (torch.arange(0, half, dtype=torch.float32) / half))
+    angles = torch.outer(torch.arange(max_position, dtype=torch.float32), freqs)
+    return torch.cos(angles).to(dtype), torch.sin(angles).to(dtype)
+
+
+def rope_neox_packed_ref(x, cos, sin, cu_seqlens_q, cache_seqlens, rotary_dim=None):
+    """GPT-NeoX rotation of packed x [T,H,D] at positions ``cache_len[b] + i``; follows
+    ``ref_rope_neox_position_ids`` (``tests/ops/test_rope.py:84-102``): fp32 arithmetic on tables held
+    in x's dtype, the first ``rotary_dim`` dims rotated about their midpoint, the rest copied."""
+    cq = [int(v) for v in cu_seqlens_q.tolist()]
+    pos = torch.cat([torch.arange(cq[b + 1] - cq[b]) + (int(cache_seqlens[b]) if cache_seqlens is not None else 0)
+                     for b in range(len(cq) - 1)]).long()
+    rd = x.shape[-1] if rotary_dim is None else rotary_dim
+    cos_full = torch.cat([cos, cos], dim=-1)[pos].unsqueeze(1).float()
+    sin_full = torch.cat([sin, sin], dim=-1)[pos].unsqueeze(1).float()
+    xr = x[..., :rd]
+    rot = torch.cat([-xr[..., rd // 2:], xr[..., :rd // 2]], dim=-1)
+    y = (xr.float() * cos_full + rot.float() * sin_full).to(x.dtype)
+    return y if rd == x.shape[-1] else torch.cat([y, x[..., rd:]], dim=-1)
+
+
 def prefill_paged_ref(q, k_new, v_new, k_pages, v_pages, cu_seqlens_q, cache_seqlens, block_table,
                       page_size, is_causal=True, sm_scale=None, softcap=None):
     """Packed prefill of one chunk per request over a paged cache, with append.

@@ -14,6 +14,7 @@ What is executed from the reference (imported, never copied):
   * ``tests.ops.attention.test_gqa_prefill_paged._gqa_prefill_paged_ref`` /
     ``_fill_paged_cache_from_logical`` / ``_physical_pos``
   * ``tests.ops.attention.test_gqa_sliding_window(.py|_varlen.py)`` reference programs
+  * ``tests.ops.test_rope.ref_rope_neox_position_ids`` / ``_compute_freqs_cis_base``
   * ``tileops.perf.formulas.gqa_*_roofline``
 ``tileops.ops`` itself needs a newer TileLang than the container has, so a stub
 module carrying the handful of names those files import is placed in
@@ -219,6 +220,18 @@ def main():
     for name, (causal, wl, wr) in {"c_l9": (True, 9, -1), "n_l4_r6": (False, 4, 6)}.items():
         t = tswv.GroupedQueryAttentionSlidingWindowVarlenFwdTest(2, sq, sk, H, Hkv, D, causal, wl, wr, torch.float32)
         out["swv_o_" + name] = t.ref_program(qv, kv_, vv_, cuq, cuk, 24).numpy()
+
+    # ---- NeoX RoPE at explicit positions: the reference test-suite's reference program and the
+    # reference's own table generator (CPU)
+    from tests.ops import test_rope as trp
+    base_freqs = trp._compute_freqs_cis_base   # same formula as tileops.ops.rope.base_freqs (:97-120)
+    xr = torch.randn(50, 3, 32, generator=g).half()
+    pos = torch.cat([torch.arange(37, 37 + 17), torch.arange(100, 100 + 33)]).int()
+    for name, rd in {"full": 32, "partial": 16}.items():
+        cos, sin = base_freqs(rd, 134, dtype=torch.float16, device="cpu")
+        out["rope_cos_" + name], out["rope_sin_" + name] = bits(cos), bits(sin)
+        out["rope_y_" + name] = bits(trp.ref_rope_neox_position_ids(xr, cos, sin, pos.long(), rotary_dim=rd))
+    out["rope_x"] = bits(xr)
 
     np.savez_compressed(os.path.join(HERE, "gqa_golden.npz"), **out)
 

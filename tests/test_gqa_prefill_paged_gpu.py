@@ -237,3 +237,61 @@ def test_varlen_op_with_longer_kv(causal):
     ones = torch.ones(4, Hkv, device="cuda")
     o2 = op2(q.cuda(), k.cuda(), v.cuda(), cu_q.cuda(), cu_k.cuda(), ones, ones.clone(), ones.clone())
     assert torch.equal(o2, o)
+
+
+# ---- RoPE ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rotary_dim", [None, 32])
+def test_rope_neox_packed_is_bit_exact(rotary_dim, dtype):
+    g = torch.Generator().manual_seed(30)
+    q_lens, old_lens, H, D = [48, 33, 1], [67, 100, 0], 8, 64
+    cu = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    cache = torch.tensor(old_lens, dtype=torch.int32)
+    x = torch.randn(sum(q_lens), H, D, generator=g).to(dtype)
+    cos, sin = O.rope_tables_ref(rotary_dim or D, 200, dtype=dtype)
+    y = _F().rope_neox_packed(x.cuda(), cos.cuda(), sin.cuda(), cu.cuda(), cache.cuda(), rotary_dim)
+    ref = O.rope_neox_packed_ref(x, cos, sin, cu, cache, rotary_dim)
+    assert torch.equal(y.cpu().view(torch.int16), ref.view(torch.int16))
+
+
+def test_rope_golden_vectors():
+    G = np.load(os.path.join(HERE, "golden", "gqa_golden.npz"))
+
+    def h(name):
+        return torch.from_numpy(G[name].view(np.int16)).view(torch.float16)
+    cu = torch.tensor([0, 17, 50], dtype=torch.int32).cuda()
+    cache = torch.tensor([37, 100], dtype=torch.int32).cuda()
+    for name, rd in (("full", 32), ("partial", 16)):
+        y = _F().rope_neox_packed(h("rope_x").cuda(), h("rope_cos_" + name).cuda(), h("rope_sin_" + name).cuda(),
+                                  cu, cache, rd)
+        assert torch.equal(y.cpu(), h("rope_y_" + name))
+
+
+@pytest.mark.parametrize("rotary_dim,is_causal,softcap", [(None, True, None), (32, True, None), (32, False, None),
+                                                          (32, True, 2.0)])
+def test_paged_op_with_rope_like_the_reference_test(rotary_dim, is_causal, softcap):
+    # tests/ops/attention/test_gqa_prefill_paged.py:476-590 of the reference: raw q / k_new go in; the result
+    # equals attention over rotated q and keys, and the pages receive the rotated keys
+    from tileops_b200.ops import GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp
+    q_lens, old_lens, heads, heads_kv, dim, page, W = [48, 33], [67, 100], 8, 2, 64, 64, 8
+    dtype = torch.float16
+    max_position = max(o + n for o, n in zip(old_lens, q_lens)) + 1
+    q, kn, vn, kp, vp, cu, cache, bt = _case(q_lens, old_lens, heads, heads_kv, dim, page, dtype, seed=31,
+                                             pages_per_req=W)
+    cos, sin = O.rope_tables_ref(rotary_dim or dim, max_position, dtype=dtype)
+    q_rot = O.rope_neox_packed_ref(q, cos, sin, cu, cache, rotary_dim)
+    k_rot = O.rope_neox_packed_ref(kn, cos, sin, cu, cache, rotary_dim)
+    ref_o, ref_kp, ref_vp = O.prefill_paged_ref(q_rot, k_rot, vn, kp, vp, cu, cache, bt, page, is_causal=is_causal,
+                                                softcap=softcap)
+    op = GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp(
+        batch=2, heads=heads, heads_kv=heads_kv, max_pages_per_req=W, page_size=page, dim=dim, is_causal=is_causal,
+        softcap=softcap, fuse_rope=True, max_position=max_position, rotary_dim=rotary_dim)
+    kpd, vpd = kp.cuda(), vp.cuda()
+    one = torch.ones(1, device="cuda")
+    o = op(q.cuda(), kn.cuda(), vn.cuda(), kpd, vpd, one, one.clone(), cu.cuda(), cache.cuda(), bt.cuda(), max(q_lens))
+    torch.testing.assert_close(o.cpu().float(), ref_o.float(), atol=5e-3, rtol=1e-3)
+    assert torch.equal(kpd.cpu().view(torch.int16), ref_kp.view(torch.int16))
+    assert torch.equal(vpd.cpu().view(torch.int16), ref_vp.view(torch.int16))
+    with pytest.raises(ValueError, match="exceeds RoPE max_position"):
+        op(q.cuda(), kn.cuda(), vn.cuda(), kpd, vpd, one, one, cu.cuda(), cache.cuda() + 2, bt.cuda(), max(q_lens))

@@ -120,6 +120,16 @@ def test_sliding_window_packed_matches_reference(name, causal, wl, wr):
     torch.testing.assert_close(o, t("swv_o_" + name), atol=2e-6, rtol=1e-5)
 
 
+@pytest.mark.parametrize("name,rd", [("full", 32), ("partial", 16)])
+def test_rope_neox_matches_reference_bit_for_bit(name, rd):
+    cos, sin = O.rope_tables_ref(rd, 134, dtype=torch.float16)
+    assert torch.equal(cos, fp16("rope_cos_" + name)) and torch.equal(sin, fp16("rope_sin_" + name))
+    cu = torch.tensor([0, 17, 50], dtype=torch.int32)
+    cache = torch.tensor([37, 100], dtype=torch.int32)
+    y = O.rope_neox_packed_ref(fp16("rope_x"), cos, sin, cu, cache, rotary_dim=rd)
+    assert torch.equal(y, fp16("rope_y_" + name))
+
+
 def test_bottom_right_known_answer():
     # tests/ops/attention/test_gqa.py:417-443 in the reference
     q = torch.zeros(1, 128, 4, 64); k = torch.zeros(1, 256, 2, 64); v = torch.zeros(1, 256, 2, 64)

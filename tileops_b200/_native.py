@@ -57,6 +57,10 @@ SIGNATURES = {
         c_void_p, c_void_p, c_void_p, c_void_p, c_int64,        # cu_seqlens_q cu_seqlens_kv cache_seqlens block_table stride
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int,  # dtype total_q total_kv B maxq H Hkv D page pool causal
         c_float, c_float, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "tb200_rope_neox_packed": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,      # x y cos sin cu_seqlens_q cache_seqlens
+        c_int, c_int, c_int, c_int, c_int, c_int, c_int,              # dtype tokens B H D rotary_dim max_position
+        c_void_p, c_void_p]),                                        # status stream
 }
 
 _lib = None

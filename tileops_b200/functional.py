@@ -302,3 +302,31 @@ def gqa_prefill_paged(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
             N.current_stream(q.device))
     N.check(st, "tb200_gqa_prefill_paged")
     return (o, lse) if return_lse else o
+
+
+def rope_neox_packed(x: torch.Tensor, cos_table: torch.Tensor, sin_table: torch.Tensor,
+                     cu_seqlens_q: torch.Tensor, cache_seqlens: Optional[torch.Tensor],
+                     rotary_dim: Optional[int] = None) -> torch.Tensor:
+    """GPT-NeoX rotary embedding of packed ``x [T,H,D]`` at positions ``cache_seqlens[b] + i`` for the
+    i-th token of request b; tables ``[max_position, rotary_dim/2]`` in x's dtype.  Returns a new tensor."""
+    _require_cuda(x=x, cos_table=cos_table, sin_table=sin_table, cu_seqlens_q=cu_seqlens_q)
+    if x.dim() != 3:
+        raise ValueError("x must be [tokens, heads, dim]")
+    T, H, D = x.shape
+    rotary_dim = D if rotary_dim is None else int(rotary_dim)
+    if cos_table.dtype != x.dtype or sin_table.dtype != x.dtype:
+        raise ValueError("cos/sin tables must have x's dtype")
+    if cos_table.shape != sin_table.shape or cos_table.dim() != 2 or cos_table.shape[1] != rotary_dim // 2:
+        raise ValueError(f"cos/sin tables must be [max_position, {rotary_dim // 2}]")
+    if cu_seqlens_q.dtype != torch.int32 or (cache_seqlens is not None and cache_seqlens.dtype != torch.int32):
+        raise ValueError("cu_seqlens_q and cache_seqlens must be int32")
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    # positions are range-checked by the caller (the operator does, on the host); no status word is passed
+    with torch.cuda.device(x.device):
+        st = N.lib().tb200_rope_neox_packed(
+            x.data_ptr(), y.data_ptr(), cos_table.contiguous().data_ptr(), sin_table.contiguous().data_ptr(),
+            cu_seqlens_q.contiguous().data_ptr(), N.ptr(cache_seqlens), N.dtype_code(x.dtype), T,
+            cu_seqlens_q.numel() - 1, H, D, rotary_dim, cos_table.shape[0], None, N.current_stream(x.device))
+    N.check(st, "tb200_rope_neox_packed")
+    return y

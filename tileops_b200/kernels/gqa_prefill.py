@@ -20,7 +20,7 @@ from .call_spec import ATTENTION_DTYPES, dense_prefill_region
 from .kernel_base import Kernel
 
 __all__ = ["GQAPrefillSm100Kernel", "GQAPrefillVarlenSm100Kernel", "GQAPrefillPagedSm100Kernel",
-           "GQASlidingWindowSm100Kernel", "GQASlidingWindowVarlenSm100Kernel"]
+           "GQASlidingWindowSm100Kernel", "GQASlidingWindowVarlenSm100Kernel", "GQAPrefillPagedRopeSm100Kernel"]
 
 
 class GQAPrefillSm100Kernel(Kernel):
@@ -214,5 +214,41 @@ class GQAPrefillPagedSm100Kernel(Kernel):
         if cos_table is not None or sin_table is not None:
             raise ValueError("GQAPrefillPagedSm100Kernel does not fuse RoPE")
         return F.gqa_prefill_paged(q, k_new, v_new, k_pages, v_pages, cu_seqlens_q, cache_seqlens,
+                                   block_table, int(max_seqlen_q), page_size=self.page_size,
+                                   is_causal=self.is_causal, sm_scale=self.sm_scale, softcap=self.softcap)
+
+
+class GQAPrefillPagedRopeSm100Kernel(GQAPrefillPagedSm100Kernel):
+    """Paged prefill with RoPE, in the ``gqa_prefill_paged_with_kv_cache_rope_fwd_kernel`` slot
+    (the reference's ``GQAPrefillPagedWithKVCacheRopeFwdKernel``,
+    ``src/tileops/kernels/attention/gqa_fwd.py:1463-2122``).  q and k_new are rotated (GPT-NeoX, at
+    positions ``cache_seqlens[b] + i``) by a pass of their own (``tb200_rope_neox_packed``), then the
+    paged prefill runs on the rotated tensors, so the pages receive the rotated keys as in the
+    reference.  The rotation is not fused into the tcgen05 kernel: q and k_new of a chunk are small next
+    to the cached K/V the attention reads."""
+
+    @classmethod
+    def applies(cls, call) -> bool:
+        return (call.dtype in ATTENTION_DTYPES and call.dim in (64, 128) and call.fuse_rope
+                and call.cache_dtype in (None, call.dtype) and call.page_size >= 16)
+
+    def __init__(self, batch, heads, heads_kv, max_pages_per_req, page_size, dim, is_causal, dtype,
+                 sm_scale=None, softcap=0.0, max_position=None, rotary_dim=None,
+                 config: Optional[dict] = None, tune: bool = False, device_index=None) -> None:
+        super().__init__(batch, heads, heads_kv, max_pages_per_req, page_size, dim, is_causal, dtype,
+                         sm_scale=sm_scale, softcap=softcap, config=config, tune=tune, device_index=device_index)
+        if max_position is None:
+            raise ValueError("GQAPrefillPagedRopeSm100Kernel needs max_position")
+        self.max_position = max_position
+        self.rotary_dim = dim if rotary_dim is None else rotary_dim
+
+    def forward(self, q, k_new, v_new, k_pages, v_pages, k_scale, v_scale, cu_seqlens_q, cache_seqlens,
+                block_table, max_seqlen_q, cos_table=None, sin_table=None):
+        self._require_cuda(q=q, k_new=k_new, v_new=v_new, k_pages=k_pages, v_pages=v_pages)
+        if cos_table is None or sin_table is None:
+            raise ValueError("GQAPrefillPagedRopeSm100Kernel needs the cos / sin tables")
+        q_rot = F.rope_neox_packed(q, cos_table, sin_table, cu_seqlens_q, cache_seqlens, self.rotary_dim)
+        k_rot = F.rope_neox_packed(k_new, cos_table, sin_table, cu_seqlens_q, cache_seqlens, self.rotary_dim)
+        return F.gqa_prefill_paged(q_rot, k_rot, v_new, k_pages, v_pages, cu_seqlens_q, cache_seqlens,
                                    block_table, int(max_seqlen_q), page_size=self.page_size,
                                    is_causal=self.is_causal, sm_scale=self.sm_scale, softcap=self.softcap)

@@ -26,6 +26,7 @@ from ..kernels import (
     GQADecodePagedFp8Sm100Kernel,
     GQADecodePagedSm100Kernel,
     GQADecodeSm100Kernel,
+    GQAPrefillPagedRopeSm100Kernel,
     GQAPrefillPagedSm100Kernel,
     GQAPrefillSm100Kernel,
     GQAPrefillVarlenSm100Kernel,
@@ -436,9 +437,10 @@ class GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp(Op):
     before the append; ``block_table`` maps logical to physical pages of ``k_pages`` / ``v_pages``,
     which are modified in place.  Mirrors ``src/tileops/ops/attention/gqa.py:765-1157`` of the
     reference (constructor, validation order and messages, positional ``forward``).  Served here:
-    a cache of q's element type, head dim 64 / 128, power-of-two pages >= 16.  An FP8 cache and
-    ``fuse_rope=True`` are accepted by the constructor as in the reference but no sm_100
-    implementation serves them: ``forward`` raises "no implementation serves this call".
+    a cache of q's element type, head dim 64 / 128, power-of-two pages >= 16, with or without
+    ``fuse_rope=True`` (GPT-NeoX rotation of q and k_new at positions ``cache_seqlens[b] + i``; the
+    pages receive the rotated keys).  An FP8 cache is accepted by the constructor as in the reference
+    but no sm_100 implementation serves it: ``forward`` raises "no implementation serves this call".
     """
 
     def __init__(self, batch: int, heads: int, heads_kv: int, max_pages_per_req: int, page_size: int,
@@ -473,12 +475,14 @@ class GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp(Op):
         self.softcap = _score_softcap(softcap)
         self.fuse_rope, self.rope_base = fuse_rope, rope_base
         self.max_position, self.rotary_dim = max_position, rotary_dim
+        self._rope_tables: dict = {}
         self.tune = tune
         self.dispatch_kernel(kernel_map)
 
     @property
     def default_kernel_map(self) -> Dict[str, type]:
-        return {"gqa_prefill_paged_with_kv_cache_fwd_kernel": GQAPrefillPagedSm100Kernel}
+        return {"gqa_prefill_paged_with_kv_cache_fwd_kernel": GQAPrefillPagedSm100Kernel,
+                "gqa_prefill_paged_with_kv_cache_rope_fwd_kernel": GQAPrefillPagedRopeSm100Kernel}
 
     def _resolved_cache_dtype(self, dtype: torch.dtype) -> torch.dtype:
         return dtype if self.cache_dtype is None else self.cache_dtype
@@ -594,7 +598,20 @@ class GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp(Op):
         call = self.attention_call(q.dtype)
         key = self.select_kernel_key(PAGED_PREFILL_KEYS, call)
         inputs = (q, k_new, v_new, k_pages, v_pages, k_scale, v_scale, cu_seqlens_q, cache_seqlens, block_table)
-        return self._get_kernel(inputs, key, call)(*inputs, max_seqlen_q, None, None)
+        cos_table, sin_table = self._get_rope_cos_sin(q.device, q.dtype) if self.fuse_rope else (None, None)
+        return self._get_kernel(inputs, key, call)(*inputs, max_seqlen_q, cos_table, sin_table)
+
+    def _get_rope_cos_sin(self, device: torch.device, dtype: torch.dtype):
+        """cos / sin tables ``[max_position, rotary_dim / 2]`` in the attention element type, computed in
+        fp32 as the reference's ``base_freqs`` does (``src/tileops/ops/rope.py:97-120``); cached."""
+        cached = self._rope_tables.get((device, dtype))
+        if cached is None:
+            half = self.rotary_dim // 2
+            freqs = 1.0 / (self.rope_base ** (torch.arange(0, half, device=device, dtype=torch.float32) / half))
+            angles = torch.outer(torch.arange(self.max_position, device=device, dtype=torch.float32), freqs)
+            cached = (torch.cos(angles).to(dtype), torch.sin(angles).to(dtype))
+            self._rope_tables[(device, dtype)] = cached
+        return cached
 
     @property
     def total_flops(self) -> int:
