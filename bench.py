@@ -177,9 +177,11 @@ def build_paged(cfg: int, rank: int, device):
     from tileops_b200 import workloads as W
     from tileops_b200.ops import (GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp,
                                   GroupedQueryAttentionDecodePagedWithKVCacheFwdOp)
-    # every rank draws its own batch of the same shape (different seed stream per rank)
+    # every rank has its own batch (own data and block table from its own seed stream) with the SAME
+    # context lengths, so that the work per GPU is identical at every N (weak scaling)
     if cfg == 3:
-        inp = W.make_paged_decode(3 + 10 * rank, 64, 32, 8, 128, 64, len_range=(512, 8192), device=device)
+        inp = W.make_paged_decode(3 + 10 * rank, 64, 32, 8, 128, 64, lens=W.draw_lengths(3, 64, (512, 8192)),
+                                  device=device)
     elif cfg == 4:
         inp = W.make_paged_decode(4 + 10 * rank, 128, 64, 8, 128, 64, lens=[4096] * 128, fp8_cache=True,
                                   device=device)
@@ -439,11 +441,16 @@ def run_cfg5(rank, world, device, steps, warmup, peaks):
     inp = W.make_paged_decode(5, B, H, Hkv, D, page, lens=[ctx] * B, device=device, page_begin=p0, page_end=p1)
     op = KVSequenceShardedPagedDecode(B, H, Hkv, D, page)
     fn = lambda: op(inp.q, inp.k, inp.v, inp.real_seqlen_kv, inp.block_table)  # noqa: E731
+    # one CUDA graph per step (decode launch + NCCL all-gather + merge launch): at 4+ GPUs the GPU work of a
+    # step is shorter than the time Python needs to issue the three calls.  Every rank takes the same branch.
+    graphed = os.environ.get("TB200_BENCH_GRAPH", "1") != "0"
+    if graphed:
+        fn = op.graphed(inp.q, inp.k, inp.v, inp.real_seqlen_kv, inp.block_table)
     ms = max_over_ranks(time_steps(fn, steps, warmup, world), world, device) / steps
     total = 2 * B * ctx * Hkv * D * 2 + 2 * B * H * D * 2 + 4 * B * (ctx // page) + 4 * B
     return {"gbs": total / (ms * 1e-3) / 1e9, "frac_of_peak": total / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "ms_per_step": ms, "tokens_per_s": B / (ms * 1e-3), "scaling": "strong",
-            "exchange_bytes_per_rank": B * H * (D + 1) * 4 * world,
+            "exchange_bytes_per_rank": B * H * (D + 1) * 4 * world, "cuda_graph": graphed,
             "gpu_launches": steps * (2 if world > 1 else 2)}
 
 

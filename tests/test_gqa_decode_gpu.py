@@ -259,3 +259,18 @@ def test_merge_handles_empty_parts():
     want, wl = O.merge_partials_ref(o_parts.cpu(), lse.cpu())
     torch.testing.assert_close(got.cpu(), want, atol=1e-6, rtol=1e-5)
     assert torch.all(got[3] == 0) and torch.all(torch.isinf(gl[3]))
+
+
+def test_sharded_decode_graph_replay_matches_eager():
+    # single rank: the captured step is the decode launch and the merge launch (the all-gather joins at
+    # world size > 1); a replay must see tensors updated in place
+    from tileops_b200.sharded import KVSequenceShardedPagedDecode
+    inp = W.make_paged_decode(61, 4, 32, 8, 128, 64, len_range=(300, 3000), device="cuda")
+    op = KVSequenceShardedPagedDecode(4, 32, 8, 128, 64)
+    args = (inp.q, inp.k, inp.v, inp.real_seqlen_kv, inp.block_table)
+    eager = op(*args).clone()
+    replay = op.graphed(*args)
+    assert torch.equal(replay(), eager)
+    inp.q.mul_(0.5)
+    want = op(*args).clone()
+    assert torch.equal(replay(), want) and not torch.equal(want, eager)

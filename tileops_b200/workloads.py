@@ -72,6 +72,14 @@ def quantize_kv_per_page(x: torch.Tensor, page_size: int):
     return xq.reshape(N, Hkv, D).contiguous(), scale.float().contiguous()
 
 
+def draw_lengths(cfg, batch, len_range, generator=None):
+    """``batch`` context lengths drawn uniformly from ``len_range`` (inclusive) with the seed stream of
+    workload ``cfg``: what :func:`make_paged_decode` draws when it is given no lengths."""
+    g = generator if generator is not None else torch.Generator().manual_seed(BASE_SEED + cfg)
+    lo, hi = len_range
+    return torch.randint(lo, hi + 1, (batch,), generator=g).tolist()
+
+
 def make_paged_decode(
     cfg: int,
     batch: int,
@@ -100,8 +108,7 @@ def make_paged_decode(
     device = torch.device(device)
     gcpu = torch.Generator().manual_seed(BASE_SEED + cfg)
     if lens is None:
-        lo, hi = len_range
-        lens = torch.randint(lo, hi + 1, (batch,), generator=gcpu).tolist()
+        lens = draw_lengths(cfg, batch, len_range, gcpu)
     lens = [int(x) for x in lens]
     full_pages = [-(-n // page_size) for n in lens]
     # logical page range kept by this shard, per sequence
