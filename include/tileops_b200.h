@@ -231,6 +231,36 @@ int tb200_rope_neox_packed(const void* x, void* y, const void* cos_table, const 
                            int total_tokens, int batch, int heads, int dim, int rotary_dim,
                            int max_position, int* status, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * FP8-e4m3 paged cache with one scalar scale per tensor, around a prefill chunk.
+ *
+ * Together with tb200_gqa_prefill_paged (no cache, cu_seqlens_kv given) these two replace the forward of
+ * GQAPrefillPagedWithFP8KVCacheFwdKernel (src/tileops/kernels/attention/gqa_fwd.py:1005-1460):
+ *
+ * tb200_fp8_cache_gather builds the packed 16-bit K/V the attention reads: for request b, rows
+ * cu_seqlens_kv[b] .. +cache_seqlens[b] are its cached tokens dequantised (float(x8) * scale, rounded to
+ * dtype), followed by its chunk's own rows of k_new / v_new (copied).
+ *   k_pages / v_pages [pool_tokens, heads_kv, dim] e4m3 ; k_new / v_new [total_q, heads_kv, dim] dtype
+ *   k_out / v_out [total_kv, heads_kv, dim] dtype, total_kv = sum_b (cache_seqlens[b] + q_len[b])
+ *   cu_seqlens_kv [batch + 1] int32 = exclusive sums of cache_seqlens[b] + q_len[b]
+ *   k_scale / v_scale: device pointers to one fp32 each
+ *
+ * tb200_fp8_cache_append writes the chunk into the pages: x8 = e4m3(x / scale), round to nearest even,
+ * saturating at +-448, at logical positions cache_seqlens[b] + i.  Cached tokens are not touched.
+ * ------------------------------------------------------------------------- */
+int tb200_fp8_cache_gather(const void* k_pages, const void* v_pages, const void* k_new, const void* v_new,
+                           void* k_out, void* v_out, const int32_t* cu_seqlens_q,
+                           const int32_t* cu_seqlens_kv, const int32_t* cache_seqlens,
+                           const int32_t* block_table, int64_t block_table_stride,
+                           const float* k_scale, const float* v_scale, int dtype, int total_kv,
+                           int batch, int heads_kv, int dim, int page_size, void* stream);
+
+int tb200_fp8_cache_append(const void* k_new, const void* v_new, void* k_pages, void* v_pages,
+                           const int32_t* cu_seqlens_q, const int32_t* cache_seqlens,
+                           const int32_t* block_table, int64_t block_table_stride,
+                           const float* k_scale, const float* v_scale, int dtype, int total_q,
+                           int batch, int heads_kv, int dim, int page_size, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

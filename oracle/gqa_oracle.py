@@ -334,6 +334,32 @@ def prefill_paged_ref(q, k_new, v_new, k_pages, v_pages, cu_seqlens_q, cache_seq
     return o, kp_after, vp_after
 
 
+def prefill_paged_fp8_cache_ref(q, k_new, v_new, k_pages, v_pages, k_scale, v_scale, cu_seqlens_q, cache_seqlens,
+                               block_table, page_size, is_causal=True, sm_scale=None, softcap=None):
+    """Paged prefill over an FP8-e4m3 cache with scalar scales; follows the reference's FP8-cache test
+    (``tests/ops/attention/test_gqa_prefill_paged.py:348-404``): cached tokens enter the attention as
+    ``(x8.float() * scale).to(q.dtype)``, the chunk's own k_new / v_new at full precision, and the pages
+    receive ``(x.float() / scale).to(float8_e4m3fn)`` at the chunk's positions.  Returns (o, k_pages_after,
+    v_pages_after)."""
+    f8 = torch.float8_e4m3fn
+    ks, vs = float(k_scale.reshape(-1)[0]), float(v_scale.reshape(-1)[0])
+    kd = (k_pages.float() * ks).to(q.dtype)
+    vd = (v_pages.float() * vs).to(q.dtype)
+    o, kd_after, _ = prefill_paged_ref(q, k_new, v_new, kd, vd, cu_seqlens_q, cache_seqlens, block_table, page_size,
+                                       is_causal, sm_scale, softcap)
+    kp_after, vp_after = k_pages.clone(), v_pages.clone()
+    cq = [int(x) for x in cu_seqlens_q.tolist()]
+    for b in range(len(cq) - 1):
+        old, n = int(cache_seqlens[b]), cq[b + 1] - cq[b]
+        if n == 0:
+            continue
+        bt_row = block_table[b].numpy() if isinstance(block_table, torch.Tensor) else np.asarray(block_table[b])
+        rows = torch.from_numpy(physical_rows(bt_row, old + n, page_size)[old:].astype(np.int64))
+        kp_after[rows] = (k_new[cq[b]:cq[b + 1]].float() / ks).to(f8)
+        vp_after[rows] = (v_new[cq[b]:cq[b + 1]].float() / vs).to(f8)
+    return o, kp_after, vp_after
+
+
 # ---------------------------------------------------------------------------
 # split / shard merge (log2-domain LSE)
 # ---------------------------------------------------------------------------

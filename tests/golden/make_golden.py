@@ -233,6 +233,38 @@ def main():
         out["rope_y_" + name] = bits(trp.ref_rope_neox_position_ids(xr, cos, sin, pos.long(), rotary_dim=rd))
     out["rope_x"] = bits(xr)
 
+    # ---- paged prefill over an FP8 cache with scalar scales: the expressions of the reference's test
+    # (test_gqa_prefill_paged.py:348-404) around its reference program
+    f8 = torch.float8_e4m3fn
+    q_lens, old_lens, H, Hkv, D, page, W = [33, 48], [67, 80], 4, 2, 32, 16, 10
+    cu = torch.tensor([0, 33, 81], dtype=torch.int32)
+    bt = torch.randperm(2 * W, generator=g).to(torch.int32).reshape(2, W)
+    ksc, vsc = torch.tensor([0.02]), torch.tensor([0.03])
+    q8 = torch.randn(81, H, D, generator=g).half()
+    kn8 = (torch.randn(81, Hkv, D, generator=g) * 0.5).half()
+    vn8 = (torch.randn(81, Hkv, D, generator=g) * 0.5).half()
+    k_old = [(torch.randn(n, Hkv, D, generator=g) * 0.5).half() for n in old_lens]
+    v_old = [(torch.randn(n, Hkv, D, generator=g) * 0.5).half() for n in old_lens]
+    k_old_q = [(t.float() / ksc[0]).to(f8) for t in k_old]
+    v_old_q = [(t.float() / vsc[0]).to(f8) for t in v_old]
+    kp8 = torch.zeros(2 * W * page, Hkv, D, dtype=f8)
+    vp8 = torch.zeros_like(kp8)
+    tpp._fill_paged_cache_from_logical(kp8, vp8, k_old_q, v_old_q, bt, page)
+    k_old_dq = [(t.float() * ksc[0]).half() for t in k_old_q]
+    v_old_dq = [(t.float() * vsc[0]).half() for t in v_old_q]
+    out["p8_q"], out["p8_k_new"], out["p8_v_new"] = bits(q8), bits(kn8), bits(vn8)
+    out["p8_k_pages"], out["p8_v_pages"] = bits(kp8), bits(vp8)
+    out["p8_cu"], out["p8_cache"], out["p8_bt"] = cu.numpy(), np.asarray(old_lens, np.int32), bt.numpy()
+    out["p8_page"], out["p8_k_scale"], out["p8_v_scale"] = np.int32(page), ksc.numpy(), vsc.numpy()
+    out["p8_o"] = bits(tpp._gqa_prefill_paged_ref(q8, kn8, vn8, k_old_dq, v_old_dq, cu, batch=2, heads=H,
+                                                   heads_kv=Hkv, is_causal=True))
+    for b_, (ql, ol) in enumerate(zip(q_lens, old_lens)):
+        for i in range(ql):
+            pos = tpp._physical_pos(bt, b_, ol + i, page)
+            kp8[pos] = (kn8[int(cu[b_]) + i].float() / ksc[0]).to(f8)
+            vp8[pos] = (vn8[int(cu[b_]) + i].float() / vsc[0]).to(f8)
+    out["p8_k_pages_after"], out["p8_v_pages_after"] = bits(kp8), bits(vp8)
+
     np.savez_compressed(os.path.join(HERE, "gqa_golden.npz"), **out)
 
     # ---- roofline formulas

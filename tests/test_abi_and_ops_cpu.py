@@ -367,7 +367,8 @@ def test_paged_prefill_op_constructor_and_selection_follow_the_reference():
         PagedOp(2, 8, 2, 0, 64, 64)
     op = PagedOp(2, 8, 2, 8, 64, 64, softcap=50.0)
     assert op.max_cache_len == 512 and op.groups == 4 and op.softcap == 50.0
-    assert sorted(op.kernel_map) == ["gqa_prefill_paged_with_kv_cache_fwd_kernel",
+    assert sorted(op.kernel_map) == ["gqa_prefill_paged_with_fp8_kv_cache_fwd_kernel",
+                                     "gqa_prefill_paged_with_kv_cache_fwd_kernel",
                                      "gqa_prefill_paged_with_kv_cache_rope_fwd_kernel"]
     from tileops_b200.ops.selection import PAGED_PREFILL_KEYS
     import dataclasses
@@ -376,14 +377,16 @@ def test_paged_prefill_op_constructor_and_selection_follow_the_reference():
         return dataclasses.replace(call, arch=100)
     assert op.select_kernel_key(PAGED_PREFILL_KEYS, on_sm100(op.attention_call(torch.float16))) == \
         "gqa_prefill_paged_with_kv_cache_fwd_kernel"
-    # an FP8 cache, pages below 16 tokens and head dim 256 have no sm_100 implementation
+    # pages below 16 tokens and head dim 256 have no sm_100 implementation
     rope = PagedOp(2, 8, 2, 8, 64, 64, fuse_rope=True, max_position=512, rotary_dim=32)
     assert rope.select_kernel_key(PAGED_PREFILL_KEYS, on_sm100(rope.attention_call(torch.float16))) == \
         "gqa_prefill_paged_with_kv_cache_rope_fwd_kernel"
     cos, sin = rope._get_rope_cos_sin(torch.device("cpu"), torch.float16)
     assert cos.shape == (512, 16) and cos.dtype == torch.float16 and float(cos[0, 0]) == 1.0 and float(sin[0, 0]) == 0.0
-    for bad in (PagedOp(2, 8, 2, 8, 64, 64, cache_dtype=torch.float8_e4m3fn),
-                PagedOp(2, 8, 2, 64, 8, 64), PagedOp(2, 8, 2, 8, 64, 256)):
+    f8op = PagedOp(2, 8, 2, 8, 64, 64, cache_dtype=torch.float8_e4m3fn)
+    assert f8op.select_kernel_key(PAGED_PREFILL_KEYS, on_sm100(f8op.attention_call(torch.float16))) == \
+        "gqa_prefill_paged_with_fp8_kv_cache_fwd_kernel"
+    for bad in (PagedOp(2, 8, 2, 64, 8, 64), PagedOp(2, 8, 2, 8, 64, 256)):
         with pytest.raises(ValueError, match="no implementation serves this call"):
             bad.select_kernel_key(PAGED_PREFILL_KEYS, on_sm100(bad.attention_call(torch.float16)))
     with pytest.raises(NotImplementedError):

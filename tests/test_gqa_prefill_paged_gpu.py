@@ -295,3 +295,66 @@ def test_paged_op_with_rope_like_the_reference_test(rotary_dim, is_causal, softc
     assert torch.equal(vpd.cpu().view(torch.int16), ref_vp.view(torch.int16))
     with pytest.raises(ValueError, match="exceeds RoPE max_position"):
         op(q.cuda(), kn.cuda(), vn.cuda(), kpd, vpd, one, one, cu.cuda(), cache.cuda() + 2, bt.cuda(), max(q_lens))
+
+
+# ---- FP8-e4m3 cache with scalar scales ---------------------------------------------------------------
+
+@pytest.mark.parametrize("is_causal,softcap,dtype,page,dim", [
+    (True, None, torch.float16, 64, 64), (False, None, torch.float16, 64, 64), (True, 2.0, torch.float16, 64, 64),
+    (True, None, torch.bfloat16, 64, 64), (True, None, torch.float16, 16, 64), (True, None, torch.float16, 128, 64),
+    (True, None, torch.bfloat16, 64, 128),
+])
+def test_paged_op_with_fp8_cache_like_the_reference_test(is_causal, softcap, dtype, page, dim):
+    # tests/ops/attention/test_gqa_prefill_paged.py:303-410 of the reference
+    from tileops_b200.ops import GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp
+    f8 = torch.float8_e4m3fn
+    g = torch.Generator().manual_seed(40)
+    q_lens, old_lens, heads, heads_kv, W = [33, 48], [67, 80], 8, 2, 8 * 64 // page
+    cu = torch.tensor([0, 33, 81], dtype=torch.int32)
+    cache = torch.tensor(old_lens, dtype=torch.int32)
+    bt = torch.randperm(2 * W, generator=g).to(torch.int32).reshape(2, W)
+    ks, vs = torch.tensor([0.02]), torch.tensor([0.025])
+    q = torch.randn(81, heads, dim, generator=g).to(dtype)
+    kn = (torch.randn(81, heads_kv, dim, generator=g) * 0.5).to(dtype)
+    vn = (torch.randn(81, heads_kv, dim, generator=g) * 0.5).to(dtype)
+    kp = torch.zeros(2 * W * page, heads_kv, dim, dtype=f8)
+    vp = torch.zeros_like(kp)
+    for b, n in enumerate(old_lens):
+        rows = torch.from_numpy(O.physical_rows(bt[b].numpy(), n, page))
+        kp[rows] = ((torch.randn(n, heads_kv, dim, generator=g) * 0.5).to(dtype).float() / ks[0]).to(f8)
+        vp[rows] = ((torch.randn(n, heads_kv, dim, generator=g) * 0.5).to(dtype).float() / vs[0]).to(f8)
+    ref_o, ref_kp, ref_vp = O.prefill_paged_fp8_cache_ref(q, kn, vn, kp, vp, ks, vs, cu, cache, bt, page,
+                                                          is_causal=is_causal, softcap=softcap)
+    op = GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp(
+        batch=2, heads=heads, heads_kv=heads_kv, max_pages_per_req=W, page_size=page, dim=dim, is_causal=is_causal,
+        cache_dtype=f8, softcap=softcap)
+    kpd, vpd = kp.cuda(), vp.cuda()
+    o = op(q.cuda(), kn.cuda(), vn.cuda(), kpd, vpd, ks.cuda(), vs.cuda(), cu.cuda(), cache.cuda(), bt.cuda(), 48)
+    torch.testing.assert_close(o.cpu().float(), ref_o.float(), **TOL[dtype])
+    # quantise-on-append is bit exact and nothing else in the pool moves
+    assert torch.equal(kpd.cpu().view(torch.uint8), ref_kp.view(torch.uint8))
+    assert torch.equal(vpd.cpu().view(torch.uint8), ref_vp.view(torch.uint8))
+    with pytest.raises(ValueError, match="finite positive"):
+        op(q.cuda(), kn.cuda(), vn.cuda(), kpd, vpd, ks.cuda() * 0, vs.cuda(), cu.cuda(), cache.cuda(), bt.cuda(), 48)
+
+
+def test_fp8_cache_golden_vectors():
+    G = np.load(os.path.join(HERE, "golden", "gqa_golden.npz"))
+
+    def h(name):
+        return torch.from_numpy(G[name].view(np.int16)).view(torch.float16)
+
+    def f8(name):
+        return torch.from_numpy(G[name]).view(torch.float8_e4m3fn)
+
+    def pad(x):   # D = 32 fixtures, the kernel serves 64: zero columns (zero is exact in e4m3 too)
+        return torch.cat([x, torch.zeros_like(x)], dim=-1).cuda()
+    kp, vp = pad(f8("p8_k_pages")), pad(f8("p8_v_pages"))
+    o = _F().gqa_prefill_paged_fp8_cache(
+        pad(h("p8_q")), pad(h("p8_k_new")), pad(h("p8_v_new")), kp, vp, torch.from_numpy(G["p8_k_scale"]).cuda(),
+        torch.from_numpy(G["p8_v_scale"]).cuda(), torch.from_numpy(G["p8_cu"]).cuda(),
+        torch.from_numpy(G["p8_cache"]).cuda(), torch.from_numpy(G["p8_bt"]).cuda(), 48, page_size=int(G["p8_page"]),
+        sm_scale=32 ** -0.5)
+    torch.testing.assert_close(o[..., :32].cpu().float(), h("p8_o").float(), atol=5e-3, rtol=1e-2)
+    assert torch.equal(kp[..., :32].cpu().view(torch.uint8), f8("p8_k_pages_after").view(torch.uint8))
+    assert torch.equal(vp[..., :32].cpu().view(torch.uint8), f8("p8_v_pages_after").view(torch.uint8))

@@ -130,6 +130,19 @@ def test_rope_neox_matches_reference_bit_for_bit(name, rd):
     assert torch.equal(y, fp16("rope_y_" + name))
 
 
+def _fp8(name):
+    return torch.from_numpy(G[name]).view(torch.float8_e4m3fn)
+
+
+def test_paged_prefill_fp8_cache_matches_reference_expressions():
+    o, kp, vp = O.prefill_paged_fp8_cache_ref(
+        fp16("p8_q"), fp16("p8_k_new"), fp16("p8_v_new"), _fp8("p8_k_pages"), _fp8("p8_v_pages"), t("p8_k_scale"),
+        t("p8_v_scale"), t("p8_cu"), t("p8_cache"), t("p8_bt"), int(G["p8_page"]))
+    torch.testing.assert_close(o.float(), fp16("p8_o").float(), atol=1e-3, rtol=1e-3)
+    assert torch.equal(kp.view(torch.uint8), _fp8("p8_k_pages_after").view(torch.uint8))
+    assert torch.equal(vp.view(torch.uint8), _fp8("p8_v_pages_after").view(torch.uint8))
+
+
 def test_bottom_right_known_answer():
     # tests/ops/attention/test_gqa.py:417-443 in the reference
     q = torch.zeros(1, 128, 4, 64); k = torch.zeros(1, 256, 2, 64); v = torch.zeros(1, 256, 2, 64)

@@ -61,6 +61,14 @@ SIGNATURES = {
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,      # x y cos sin cu_seqlens_q cache_seqlens
         c_int, c_int, c_int, c_int, c_int, c_int, c_int,              # dtype tokens B H D rotary_dim max_position
         c_void_p, c_void_p]),                                        # status stream
+    "tb200_fp8_cache_gather": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,      # k_pages v_pages k_new v_new k_out v_out
+        c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,  # cu_q cu_kv cache bt stride k_scale v_scale
+        c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),          # dtype total_kv B Hkv D page stream
+    "tb200_fp8_cache_append": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_void_p,                         # k_new v_new k_pages v_pages
+        c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,      # cu_q cache bt stride k_scale v_scale
+        c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),          # dtype total_q B Hkv D page stream
 }
 
 _lib = None

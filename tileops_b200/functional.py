@@ -330,3 +330,52 @@ def rope_neox_packed(x: torch.Tensor, cos_table: torch.Tensor, sin_table: torch.
             cu_seqlens_q.numel() - 1, H, D, rotary_dim, cos_table.shape[0], None, N.current_stream(x.device))
     N.check(st, "tb200_rope_neox_packed")
     return y
+
+
+def gqa_prefill_paged_fp8_cache(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, k_pages: torch.Tensor,
+                                v_pages: torch.Tensor, k_scale: torch.Tensor, v_scale: torch.Tensor,
+                                cu_seqlens_q: torch.Tensor, cache_seqlens: torch.Tensor, block_table: torch.Tensor,
+                                max_seqlen_q: int, *, page_size: int, is_causal: bool = True,
+                                sm_scale: Optional[float] = None, softcap: float = 0.0) -> torch.Tensor:
+    """Packed prefill of one chunk per request over an FP8-e4m3 paged cache with scalar scales
+    (``k_scale`` / ``v_scale``: fp32 tensors of shape (1,)): the cached tokens are dequantised into a packed
+    16-bit K/V next to the chunk's own rows, the packed prefill runs on it, and the chunk is quantised into
+    the pages in place.  One host read of the total KV length per call (it sizes the packed buffer)."""
+    _require_cuda(q=q, k_new=k_new, v_new=v_new, k_pages=k_pages, v_pages=v_pages, k_scale=k_scale, v_scale=v_scale,
+                  cu_seqlens_q=cu_seqlens_q, cache_seqlens=cache_seqlens, block_table=block_table)
+    f8 = getattr(torch, "float8_e4m3fn")
+    if k_pages.dtype != f8 or v_pages.dtype != f8:
+        raise ValueError("k_pages and v_pages must be torch.float8_e4m3fn")
+    if k_scale.dtype != torch.float32 or v_scale.dtype != torch.float32 or k_scale.numel() != 1 or v_scale.numel() != 1:
+        raise ValueError("k_scale and v_scale must be fp32 tensors with one element")
+    if not (k_pages.is_contiguous() and v_pages.is_contiguous()):
+        raise ValueError("k_pages and v_pages must be contiguous (they are written in place)")
+    total_q, H, D = q.shape
+    Hkv = k_new.shape[1]
+    B = cu_seqlens_q.numel() - 1
+    q, k_new, v_new = q.contiguous(), k_new.contiguous(), v_new.contiguous()
+    cu_seqlens_q, cache_seqlens = cu_seqlens_q.contiguous(), cache_seqlens.contiguous()
+    if block_table.stride(1) != 1:
+        block_table = block_table.contiguous()
+    kv_lens = cache_seqlens + (cu_seqlens_q[1:] - cu_seqlens_q[:-1])
+    cu_kv = torch.zeros(B + 1, dtype=torch.int32, device=q.device)
+    cu_kv[1:] = torch.cumsum(kv_lens, 0)
+    total_kv = int(cu_kv[-1].item())          # host read: sizes the packed K/V
+    k_all = torch.empty((total_kv, Hkv, D), dtype=q.dtype, device=q.device)
+    v_all = torch.empty_like(k_all)
+    lib, stream = N.lib(), N.current_stream(q.device)
+    with torch.cuda.device(q.device):
+        st = lib.tb200_fp8_cache_gather(
+            k_pages.data_ptr(), v_pages.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), k_all.data_ptr(),
+            v_all.data_ptr(), cu_seqlens_q.data_ptr(), cu_kv.data_ptr(), cache_seqlens.data_ptr(),
+            block_table.data_ptr(), block_table.stride(0), k_scale.data_ptr(), v_scale.data_ptr(),
+            N.dtype_code(q.dtype), total_kv, B, Hkv, D, int(page_size), stream)
+        N.check(st, "tb200_fp8_cache_gather")
+        o = gqa_prefill_paged(q, k_all, v_all, None, None, cu_seqlens_q, None, None, int(max_seqlen_q),
+                              is_causal=is_causal, sm_scale=sm_scale, softcap=softcap, cu_seqlens_kv=cu_kv)
+        st = lib.tb200_fp8_cache_append(
+            k_new.data_ptr(), v_new.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), cu_seqlens_q.data_ptr(),
+            cache_seqlens.data_ptr(), block_table.data_ptr(), block_table.stride(0), k_scale.data_ptr(),
+            v_scale.data_ptr(), N.dtype_code(q.dtype), total_q, B, Hkv, D, int(page_size), stream)
+        N.check(st, "tb200_fp8_cache_append")
+    return o

@@ -20,7 +20,7 @@ from .call_spec import ATTENTION_DTYPES, dense_prefill_region
 from .kernel_base import Kernel
 
 __all__ = ["GQAPrefillSm100Kernel", "GQAPrefillVarlenSm100Kernel", "GQAPrefillPagedSm100Kernel",
-           "GQASlidingWindowSm100Kernel", "GQASlidingWindowVarlenSm100Kernel", "GQAPrefillPagedRopeSm100Kernel"]
+           "GQASlidingWindowSm100Kernel", "GQASlidingWindowVarlenSm100Kernel", "GQAPrefillPagedRopeSm100Kernel", "GQAPrefillPagedFp8CacheSm100Kernel"]
 
 
 class GQAPrefillSm100Kernel(Kernel):
@@ -252,3 +252,28 @@ class GQAPrefillPagedRopeSm100Kernel(GQAPrefillPagedSm100Kernel):
         return F.gqa_prefill_paged(q_rot, k_rot, v_new, k_pages, v_pages, cu_seqlens_q, cache_seqlens,
                                    block_table, int(max_seqlen_q), page_size=self.page_size,
                                    is_causal=self.is_causal, sm_scale=self.sm_scale, softcap=self.softcap)
+
+
+class GQAPrefillPagedFp8CacheSm100Kernel(GQAPrefillPagedSm100Kernel):
+    """Paged prefill over an FP8-e4m3 cache with scalar scales, in the
+    ``gqa_prefill_paged_with_fp8_kv_cache_fwd_kernel`` slot (the reference's
+    ``GQAPrefillPagedWithFP8KVCacheFwdKernel``, ``src/tileops/kernels/attention/gqa_fwd.py:1005-1460``).
+    Cached tokens are dequantised into a packed 16-bit K/V (``tb200_fp8_cache_gather``), the packed tcgen05
+    prefill runs on it, and the chunk is quantised into the pages (``tb200_fp8_cache_append``): the
+    reference's dequantise-then-attend semantics, as three launches instead of one fused kernel."""
+
+    @classmethod
+    def applies(cls, call) -> bool:
+        from .call_spec import fp8_dtype
+        return (call.dtype in ATTENTION_DTYPES and call.dim in (64, 128) and not call.fuse_rope
+                and call.cache_dtype is not None and call.cache_dtype == fp8_dtype())
+
+    def forward(self, q, k_new, v_new, k_pages, v_pages, k_scale, v_scale, cu_seqlens_q, cache_seqlens,
+                block_table, max_seqlen_q, cos_table=None, sin_table=None):
+        self._require_cuda(q=q, k_new=k_new, v_new=v_new, k_pages=k_pages, v_pages=v_pages)
+        if cos_table is not None or sin_table is not None:
+            raise ValueError("GQAPrefillPagedFp8CacheSm100Kernel does not apply RoPE")
+        return F.gqa_prefill_paged_fp8_cache(q, k_new, v_new, k_pages, v_pages, k_scale, v_scale, cu_seqlens_q,
+                                             cache_seqlens, block_table, int(max_seqlen_q),
+                                             page_size=self.page_size, is_causal=self.is_causal,
+                                             sm_scale=self.sm_scale, softcap=self.softcap)

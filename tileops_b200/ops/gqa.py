@@ -26,6 +26,7 @@ from ..kernels import (
     GQADecodePagedFp8Sm100Kernel,
     GQADecodePagedSm100Kernel,
     GQADecodeSm100Kernel,
+    GQAPrefillPagedFp8CacheSm100Kernel,
     GQAPrefillPagedRopeSm100Kernel,
     GQAPrefillPagedSm100Kernel,
     GQAPrefillSm100Kernel,
@@ -439,8 +440,8 @@ class GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp(Op):
     reference (constructor, validation order and messages, positional ``forward``).  Served here:
     a cache of q's element type, head dim 64 / 128, power-of-two pages >= 16, with or without
     ``fuse_rope=True`` (GPT-NeoX rotation of q and k_new at positions ``cache_seqlens[b] + i``; the
-    pages receive the rotated keys).  An FP8 cache is accepted by the constructor as in the reference
-    but no sm_100 implementation serves it: ``forward`` raises "no implementation serves this call".
+    pages receive the rotated keys), or an FP8-e4m3 cache with scalar ``k_scale`` / ``v_scale``
+    (``cache_dtype=torch.float8_e4m3fn``: cached tokens dequantised, the chunk quantised on append).
     """
 
     def __init__(self, batch: int, heads: int, heads_kv: int, max_pages_per_req: int, page_size: int,
@@ -482,7 +483,8 @@ class GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp(Op):
     @property
     def default_kernel_map(self) -> Dict[str, type]:
         return {"gqa_prefill_paged_with_kv_cache_fwd_kernel": GQAPrefillPagedSm100Kernel,
-                "gqa_prefill_paged_with_kv_cache_rope_fwd_kernel": GQAPrefillPagedRopeSm100Kernel}
+                "gqa_prefill_paged_with_kv_cache_rope_fwd_kernel": GQAPrefillPagedRopeSm100Kernel,
+                "gqa_prefill_paged_with_fp8_kv_cache_fwd_kernel": GQAPrefillPagedFp8CacheSm100Kernel}
 
     def _resolved_cache_dtype(self, dtype: torch.dtype) -> torch.dtype:
         return dtype if self.cache_dtype is None else self.cache_dtype
