@@ -154,7 +154,8 @@ int tb200_gqa_lse_merge(const float* o_parts, const float* lse_parts, void* o, f
  * for a uniform batch:
  *   q [batch, seqlen_q, heads, dim], k/v [batch, seqlen_kv, heads_kv, dim]  dtype (F16 | BF16)
  *   o [batch, seqlen_q, heads, dim] dtype ; lse [batch, heads, seqlen_q] fp32 log2-domain or NULL
- * dim must be 64 or 128 (tcgen05 path).  Rows with no visible key give o = 0, lse = -inf.
+ * dim must be 64, 128 or 256 (tcgen05 path; 256 runs one CTA per SM).  Rows with no visible key give
+ * o = 0, lse = -inf.
  * window_left / window_right: sliding window of the reference's
  * GroupedQueryAttentionSlidingWindowFwdOp (src/tileops/ops/attention/gqa.py:1457-1627): with
  * d = seqlen_kv - seqlen_q, key j is visible to row i iff j >= i + d - window_left (when
@@ -193,7 +194,7 @@ int tb200_gqa_prefill(const void* q, const void* k, const void* v, void* o, floa
  * own new tokens (read from k_new / v_new): causal means key position <= cache_seqlens[b] + row.
  * The new K/V rows are also written into the pages at logical positions cache_seqlens[b] + i
  * (block_table[b, pos / page_size] * page_size + pos % page_size), in place, by the same launch;
- * cached tokens are never modified.  page_size: a power of two >= 16.  dim: 64 or 128.
+ * cached tokens are never modified.  page_size: a power of two >= 16.  dim: 64, 128 or 256.
  * block_table ids are trusted (range-check them on the host, as the reference operator does).
  * k_pages = v_pages = cache_seqlens = block_table = NULL: no cache, nothing appended.
  * max_seqlen_q bounds the longest request (it sizes the grid).

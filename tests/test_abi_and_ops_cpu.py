@@ -377,7 +377,7 @@ def test_paged_prefill_op_constructor_and_selection_follow_the_reference():
         return dataclasses.replace(call, arch=100)
     assert op.select_kernel_key(PAGED_PREFILL_KEYS, on_sm100(op.attention_call(torch.float16))) == \
         "gqa_prefill_paged_with_kv_cache_fwd_kernel"
-    # pages below 16 tokens and head dim 256 have no sm_100 implementation
+    # pages below 16 tokens and head dims other than 64 / 128 / 256 have no sm_100 implementation
     rope = PagedOp(2, 8, 2, 8, 64, 64, fuse_rope=True, max_position=512, rotary_dim=32)
     assert rope.select_kernel_key(PAGED_PREFILL_KEYS, on_sm100(rope.attention_call(torch.float16))) == \
         "gqa_prefill_paged_with_kv_cache_rope_fwd_kernel"
@@ -386,7 +386,7 @@ def test_paged_prefill_op_constructor_and_selection_follow_the_reference():
     f8op = PagedOp(2, 8, 2, 8, 64, 64, cache_dtype=torch.float8_e4m3fn)
     assert f8op.select_kernel_key(PAGED_PREFILL_KEYS, on_sm100(f8op.attention_call(torch.float16))) == \
         "gqa_prefill_paged_with_fp8_kv_cache_fwd_kernel"
-    for bad in (PagedOp(2, 8, 2, 64, 8, 64), PagedOp(2, 8, 2, 8, 64, 256)):
+    for bad in (PagedOp(2, 8, 2, 64, 8, 64), PagedOp(2, 8, 2, 8, 64, 96)):
         with pytest.raises(ValueError, match="no implementation serves this call"):
             bad.select_kernel_key(PAGED_PREFILL_KEYS, on_sm100(bad.attention_call(torch.float16)))
     with pytest.raises(NotImplementedError):

@@ -69,6 +69,21 @@ def test_head_dim_64(B, Sq, Skv, H, Hkv, causal, dtype):
     assert F.prefill_status("cuda:0") == 0
 
 
+@pytest.mark.parametrize("B,Sq,Skv,H,Hkv,causal,dtype", [
+    (1, 256, 256, 4, 1, True, torch.float16),
+    (2, 200, 333, 4, 2, True, torch.bfloat16),
+    (1, 640, 640, 8, 2, False, torch.bfloat16),
+    (1, 1024, 1024, 8, 2, True, torch.bfloat16),
+])
+def test_head_dim_256(B, Sq, Skv, H, Hkv, causal, dtype):
+    q, k, v = W.make_prefill(46, B, Sq, Skv, H, Hkv, 256, dtype, "cuda")
+    o, lse = F.gqa_prefill(q, k, v, is_causal=causal, return_lse=True)
+    ro, rl = O.prefill_ref(q.cpu(), k.cpu(), v.cpu(), causal, return_lse=True)
+    close(o, ro)
+    torch.testing.assert_close(lse.cpu(), rl, atol=2e-3, rtol=1e-3)
+    assert F.prefill_status("cuda:0") == 0
+
+
 @pytest.mark.parametrize("Sq,Skv,causal", [(128, 256, True), (512, 4096, True), (96, 150, True),
                                            (150, 406, True), (256, 128, False), (64, 1000, False)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])

@@ -85,6 +85,32 @@ def test_ragged_multi_tile(dim, dtype):
     _check([300, 1, 129, 257], [0, 5, 1000, 333], 8, 2, dim, 16, dtype, seed=3)
 
 
+def test_head_dim_256_with_partial_rope_like_the_qwen_workloads():
+    # manifest workloads "qwen35-9b-prefill-paged-*": head dim 256, rotary_dim 64, page 64 (lengths scaled down)
+    from tileops_b200.ops import GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp
+    q_lens, old_lens, heads, heads_kv, dim, page, W_ = [130, 70, 257], [500, 64, 3], 8, 2, 256, 64, 16
+    dtype = torch.float16
+    q, kn, vn, kp, vp, cu, cache, bt = _case(q_lens, old_lens, heads, heads_kv, dim, page, dtype, seed=33,
+                                             pages_per_req=W_)
+    _check(q_lens, old_lens, heads, heads_kv, dim, page, dtype, seed=33, pages_per_req=W_)
+    max_position = W_ * page
+    op = GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp(
+        batch=3, heads=heads, heads_kv=heads_kv, max_pages_per_req=W_, page_size=page, dim=dim, fuse_rope=True,
+        max_position=max_position, rotary_dim=64)
+    # the operator builds its tables on the device (as the reference does); device and host cos / sin may
+    # differ in the last bit, so the oracle rotates with the operator's own tables
+    cos, sin = (t.cpu() for t in op._get_rope_cos_sin(torch.device("cuda", 0), dtype))
+    torch.testing.assert_close(cos.float(), O.rope_tables_ref(64, max_position, dtype=dtype)[0].float(), atol=2e-3, rtol=0)
+    q_rot = O.rope_neox_packed_ref(q, cos, sin, cu, cache, 64)
+    k_rot = O.rope_neox_packed_ref(kn, cos, sin, cu, cache, 64)
+    ref_o, ref_kp, _ = O.prefill_paged_ref(q_rot, k_rot, vn, kp, vp, cu, cache, bt, page)
+    kpd, vpd = kp.cuda(), vp.cuda()
+    one = torch.ones(1, device="cuda")
+    o = op(q.cuda(), kn.cuda(), vn.cuda(), kpd, vpd, one, one.clone(), cu.cuda(), cache.cuda(), bt.cuda(), max(q_lens))
+    torch.testing.assert_close(o.cpu().float(), ref_o.float(), **TOL[dtype])
+    assert torch.equal(kpd.cpu().view(torch.int16), ref_kp.view(torch.int16))
+
+
 def test_softcap_and_noncausal_dim128():
     _check([200, 77], [130, 64], 16, 4, 128, 64, torch.bfloat16, softcap=30.0, seed=4)
     _check([200, 77], [130, 64], 16, 4, 128, 64, torch.bfloat16, is_causal=False, seed=5)
@@ -279,14 +305,14 @@ def test_paged_op_with_rope_like_the_reference_test(rotary_dim, is_causal, softc
     max_position = max(o + n for o, n in zip(old_lens, q_lens)) + 1
     q, kn, vn, kp, vp, cu, cache, bt = _case(q_lens, old_lens, heads, heads_kv, dim, page, dtype, seed=31,
                                              pages_per_req=W)
-    cos, sin = O.rope_tables_ref(rotary_dim or dim, max_position, dtype=dtype)
+    op = GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp(
+        batch=2, heads=heads, heads_kv=heads_kv, max_pages_per_req=W, page_size=page, dim=dim, is_causal=is_causal,
+        softcap=softcap, fuse_rope=True, max_position=max_position, rotary_dim=rotary_dim)
+    cos, sin = (t.cpu() for t in op._get_rope_cos_sin(torch.device("cuda", 0), dtype))   # the operator's tables
     q_rot = O.rope_neox_packed_ref(q, cos, sin, cu, cache, rotary_dim)
     k_rot = O.rope_neox_packed_ref(kn, cos, sin, cu, cache, rotary_dim)
     ref_o, ref_kp, ref_vp = O.prefill_paged_ref(q_rot, k_rot, vn, kp, vp, cu, cache, bt, page, is_causal=is_causal,
                                                 softcap=softcap)
-    op = GroupedQueryAttentionPrefillPagedWithKVCacheFwdOp(
-        batch=2, heads=heads, heads_kv=heads_kv, max_pages_per_req=W, page_size=page, dim=dim, is_causal=is_causal,
-        softcap=softcap, fuse_rope=True, max_position=max_position, rotary_dim=rotary_dim)
     kpd, vpd = kp.cuda(), vp.cuda()
     one = torch.ones(1, device="cuda")
     o = op(q.cuda(), kn.cuda(), vn.cuda(), kpd, vpd, one, one.clone(), cu.cuda(), cache.cuda(), bt.cuda(), max(q_lens))

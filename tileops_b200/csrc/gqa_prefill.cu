@@ -52,7 +52,10 @@ constexpr int kStages = 2;                   // K, V and S buffers
 constexpr int kQPanel = kBM * 128;           // 128 rows x 128 B (64 head dims)
 constexpr int kKvPanel = kBN * 128;          // 64 rows x 128 B
 constexpr int kThreads = 192;
-constexpr uint32_t kTmemCols = 256;
+// TMEM columns a CTA allocates: S0 | S1 | O = 64 + 64 + HD, rounded up to a power of two.  Head dims
+// up to 128 leave room for two CTAs per SM (2 x 256 of 512 columns); 256 takes the whole TMEM.
+__host__ __device__ constexpr uint32_t tmem_cols(int hd) { return hd <= 128 ? 256u : 512u; }
+__host__ __device__ constexpr int ctas_per_sm(int hd) { return hd <= 128 ? 2 : 1; }
 constexpr uint32_t kColS = 0, kColO = 128;    // S buffer s at columns [64 s, 64 s + 64)
 #ifndef TB200_PF_TIE
 #define TB200_PF_TIE 1
@@ -285,13 +288,14 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) { return pack2
 // map_k / map_v, causal inside the chunk).  CTAs of the first q head of a KV group also copy their
 // 128 new K/V rows into the pages; attention never reads those copies, so no CTA waits for another.
 template <typename T, bool kSoftcap, int HD, bool kPaged>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, ctas_per_sm(HD))
 gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_kp,
                    const __grid_constant__ CUtensorMap map_vp, PrefillParams p) {
   using SmemLayout = SmemLayoutT<HD>;
   constexpr int kHD = HD;
   constexpr int kQBytes = SmemLayout::kQBytes, kKvBytes = SmemLayout::kKvBytes;
+  constexpr uint32_t kTmemCols = tmem_cols(HD);
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -809,8 +813,8 @@ extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, vo
   if (batch <= 0 || seqlen_q <= 0 || seqlen_kv <= 0 || heads <= 0 || heads_kv <= 0)
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "batch, seqlen_q, seqlen_kv, heads and heads_kv must be positive");
   if (heads % heads_kv != 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "heads must be divisible by heads_kv");
-  if (dim != 128 && dim != 64)
-    TB200_FAIL(TB200_ERR_UNSUPPORTED, "head dim %d (the tcgen05 prefill kernel serves 64 and 128)", dim);
+  if (dim != 128 && dim != 64 && dim != 256)
+    TB200_FAIL(TB200_ERR_UNSUPPORTED, "head dim %d (the tcgen05 prefill kernel serves 64, 128 and 256)", dim);
   if (dtype != TB200_BF16 && dtype != TB200_F16) TB200_FAIL(TB200_ERR_UNSUPPORTED, "dtype must be F16 or BF16");
   if (!(sm_scale > 0.f)) TB200_FAIL(TB200_ERR_UNSUPPORTED, "sm_scale must be positive");
   if (softcap < 0.f) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "softcap must be non-negative");
@@ -833,6 +837,7 @@ extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, vo
   p.is_causal = is_causal; p.sm_scale = sm_scale; p.softcap = softcap;
   p.win_left = window_left; p.win_right = window_right;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dim == 256) return dispatch_prefill<256, false>(dtype, m, p, s);
   return dim == 128 ? dispatch_prefill<128, false>(dtype, m, p, s) : dispatch_prefill<64, false>(dtype, m, p, s);
 }
 
@@ -852,8 +857,8 @@ extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const v
   if (total_q <= 0 || total_kv <= 0 || batch <= 0 || max_seqlen_q <= 0 || heads <= 0 || heads_kv <= 0)
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "total_q, total_kv, batch, max_seqlen_q, heads and heads_kv must be positive");
   if (heads % heads_kv != 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "heads must be divisible by heads_kv");
-  if (dim != 128 && dim != 64)
-    TB200_FAIL(TB200_ERR_UNSUPPORTED, "head dim %d (the tcgen05 prefill kernel serves 64 and 128)", dim);
+  if (dim != 128 && dim != 64 && dim != 256)
+    TB200_FAIL(TB200_ERR_UNSUPPORTED, "head dim %d (the tcgen05 prefill kernel serves 64, 128 and 256)", dim);
   if (dtype != TB200_BF16 && dtype != TB200_F16) TB200_FAIL(TB200_ERR_UNSUPPORTED, "dtype must be F16 or BF16");
   if (!(sm_scale > 0.f)) TB200_FAIL(TB200_ERR_UNSUPPORTED, "sm_scale must be positive");
   if (softcap < 0.f) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "softcap must be non-negative");
@@ -902,5 +907,6 @@ extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const v
   p.cu_q = cu_seqlens_q; p.cu_kv = cu_seqlens_kv; p.cache_lens = cache_seqlens; p.bt = block_table; p.bt_stride = block_table_stride;
   p.k_new = k_new; p.v_new = v_new; p.k_pages = k_pages; p.v_pages = v_pages; p.total_q = total_q;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dim == 256) return dispatch_prefill<256, true>(dtype, m, p, s);
   return dim == 128 ? dispatch_prefill<128, true>(dtype, m, p, s) : dispatch_prefill<64, true>(dtype, m, p, s);
 }

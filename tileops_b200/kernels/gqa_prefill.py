@@ -19,6 +19,8 @@ from .. import functional as F
 from .call_spec import ATTENTION_DTYPES, dense_prefill_region
 from .kernel_base import Kernel
 
+_PREFILL_DIMS = (64, 128, 256)   # head dims the tcgen05 prefill kernel is instantiated for
+
 __all__ = ["GQAPrefillSm100Kernel", "GQAPrefillVarlenSm100Kernel", "GQAPrefillPagedSm100Kernel",
            "GQASlidingWindowSm100Kernel", "GQASlidingWindowVarlenSm100Kernel", "GQAPrefillPagedRopeSm100Kernel", "GQAPrefillPagedFp8CacheSm100Kernel"]
 
@@ -29,15 +31,15 @@ class GQAPrefillSm100Kernel(Kernel):
 
     @classmethod
     def applies(cls, call) -> bool:
-        return dense_prefill_region(call) and call.dim in (64, 128) and call.dtype in ATTENTION_DTYPES
+        return dense_prefill_region(call) and call.dim in _PREFILL_DIMS and call.dtype in ATTENTION_DTYPES
 
     def __init__(self, batch, heads, heads_kv, max_seqlen_q, max_seqlen_kv, dim, is_causal, dtype,
                  sm_scale=None, softcap=0.0, window_size_left=-1, window_size_right=-1,
                  accum_dtype=torch.float32, config: Optional[dict] = None, tune: bool = False,
                  device_index=None) -> None:
         super().__init__(device_index=device_index)
-        if dim not in (64, 128):
-            raise ValueError(f"GQAPrefillSm100Kernel supports head dim 64 and 128, got {dim}")
+        if dim not in _PREFILL_DIMS:
+            raise ValueError(f"GQAPrefillSm100Kernel supports head dim 64, 128 and 256, got {dim}")
         self.window_size_left, self.window_size_right = window_size_left, window_size_right
         self.batch, self.heads, self.heads_kv, self.dim = batch, heads, heads_kv, dim
         self.max_seqlen_q, self.max_seqlen_kv = max_seqlen_q, max_seqlen_kv
@@ -90,15 +92,15 @@ class GQAPrefillVarlenSm100Kernel(Kernel):
 
     @classmethod
     def applies(cls, call) -> bool:
-        return varlen_prefill_region(call) and call.dim in (64, 128) and call.dtype in ATTENTION_DTYPES
+        return varlen_prefill_region(call) and call.dim in _PREFILL_DIMS and call.dtype in ATTENTION_DTYPES
 
     def __init__(self, batch, heads, heads_kv, max_seqlen_q, max_seqlen_kv, dim, is_causal, dtype,
                  sm_scale=None, softcap=0.0, window_size_left=-1, window_size_right=-1,
                  accum_dtype=torch.float32, config: Optional[dict] = None, tune: bool = False,
                  device_index=None) -> None:
         super().__init__(device_index=device_index)
-        if dim not in (64, 128):
-            raise ValueError(f"{type(self).__name__} supports head dim 64 and 128, got {dim}")
+        if dim not in _PREFILL_DIMS:
+            raise ValueError(f"{type(self).__name__} supports head dim 64, 128 and 256, got {dim}")
         self.window_size_left, self.window_size_right = window_size_left, window_size_right
         self.batch, self.heads, self.heads_kv, self.dim = batch, heads, heads_kv, dim
         self.max_seqlen_q, self.max_seqlen_kv = max_seqlen_q, max_seqlen_kv
@@ -133,7 +135,7 @@ class GQASlidingWindowVarlenSm100Kernel(GQAPrefillVarlenSm100Kernel):
     def applies(cls, call) -> bool:
         from .call_spec import uses_sliding_window
         return (uses_sliding_window(call) and not call.is_fp8 and call.backend in ("auto", "sliding_window")
-                and call.dim in (64, 128) and call.dtype in ATTENTION_DTYPES)
+                and call.dim in _PREFILL_DIMS and call.dtype in ATTENTION_DTYPES)
 
 
 class GQASlidingWindowSm100Kernel(Kernel):
@@ -147,13 +149,13 @@ class GQASlidingWindowSm100Kernel(Kernel):
 
     @classmethod
     def applies(cls, call) -> bool:
-        return call.dim in (64, 128) and call.dtype in ATTENTION_DTYPES
+        return call.dim in _PREFILL_DIMS and call.dtype in ATTENTION_DTYPES
 
     def __init__(self, batch, heads, heads_kv, seq_len, dim, is_causal, window_size_left, window_size_right,
                  dtype, config: Optional[dict] = None, tune: bool = False, device_index=None) -> None:
         super().__init__(device_index=device_index)
-        if dim not in (64, 128):
-            raise ValueError(f"GQASlidingWindowSm100Kernel supports head dim 64 and 128, got {dim}")
+        if dim not in _PREFILL_DIMS:
+            raise ValueError(f"GQASlidingWindowSm100Kernel supports head dim 64, 128 and 256, got {dim}")
         self.batch, self.heads, self.heads_kv, self.seq_len, self.dim = batch, heads, heads_kv, seq_len, dim
         self.is_causal, self.dtype = is_causal, dtype
         self.window_size_left, self.window_size_right = window_size_left, window_size_right
@@ -185,15 +187,15 @@ class GQAPrefillPagedSm100Kernel(Kernel):
 
     @classmethod
     def applies(cls, call) -> bool:
-        return (call.dtype in ATTENTION_DTYPES and call.dim in (64, 128) and not call.fuse_rope
+        return (call.dtype in ATTENTION_DTYPES and call.dim in _PREFILL_DIMS and not call.fuse_rope
                 and call.cache_dtype in (None, call.dtype) and call.page_size >= 16)
 
     def __init__(self, batch, heads, heads_kv, max_pages_per_req, page_size, dim, is_causal, dtype,
                  sm_scale=None, softcap=0.0, max_position=None, rotary_dim=None,
                  config: Optional[dict] = None, tune: bool = False, device_index=None) -> None:
         super().__init__(device_index=device_index)
-        if dim not in (64, 128):
-            raise ValueError(f"GQAPrefillPagedSm100Kernel supports head dim 64 and 128, got {dim}")
+        if dim not in _PREFILL_DIMS:
+            raise ValueError(f"GQAPrefillPagedSm100Kernel supports head dim 64, 128 and 256, got {dim}")
         if page_size < 16 or page_size & (page_size - 1):
             raise ValueError(f"GQAPrefillPagedSm100Kernel supports power-of-two pages >= 16, got {page_size}")
         self.batch, self.heads, self.heads_kv, self.dim = batch, heads, heads_kv, dim
@@ -229,7 +231,7 @@ class GQAPrefillPagedRopeSm100Kernel(GQAPrefillPagedSm100Kernel):
 
     @classmethod
     def applies(cls, call) -> bool:
-        return (call.dtype in ATTENTION_DTYPES and call.dim in (64, 128) and call.fuse_rope
+        return (call.dtype in ATTENTION_DTYPES and call.dim in _PREFILL_DIMS and call.fuse_rope
                 and call.cache_dtype in (None, call.dtype) and call.page_size >= 16)
 
     def __init__(self, batch, heads, heads_kv, max_pages_per_req, page_size, dim, is_causal, dtype,
@@ -265,7 +267,7 @@ class GQAPrefillPagedFp8CacheSm100Kernel(GQAPrefillPagedSm100Kernel):
     @classmethod
     def applies(cls, call) -> bool:
         from .call_spec import fp8_dtype
-        return (call.dtype in ATTENTION_DTYPES and call.dim in (64, 128) and not call.fuse_rope
+        return (call.dtype in ATTENTION_DTYPES and call.dim in _PREFILL_DIMS and not call.fuse_rope
                 and call.cache_dtype is not None and call.cache_dtype == fp8_dtype())
 
     def forward(self, q, k_new, v_new, k_pages, v_pages, k_scale, v_scale, cu_seqlens_q, cache_seqlens,
