@@ -56,15 +56,38 @@ __global__ void __launch_bounds__(kThreads) fp8_cache_gather_kernel(
     const int page = bt[(long long)b * bt_stride + t / page_size];
     const size_t src = (size_t(page) * page_size + t % page_size) * row_elems;
     const float ks = *k_scale, vs = *v_scale;
-    for (int i = threadIdx.x; i < row_elems; i += kThreads) {
-      ko[i] = T(e4m3_to_float(k_pages[src + i]) * ks);
-      vo[i] = T(e4m3_to_float(v_pages[src + i]) * vs);
+    if (row_elems % 8 == 0) {           // 8 elements per step: 8-byte loads, 16-byte stores (rows are 8-element aligned)
+      for (int i = threadIdx.x * 8; i < row_elems; i += kThreads * 8) {
+        alignas(8) unsigned char kb[8], vb[8];
+        alignas(16) T kq[8], vq[8];
+        *reinterpret_cast<uint2*>(kb) = *reinterpret_cast<const uint2*>(k_pages + src + i);
+        *reinterpret_cast<uint2*>(vb) = *reinterpret_cast<const uint2*>(v_pages + src + i);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          kq[e] = T(e4m3_to_float(kb[e]) * ks);
+          vq[e] = T(e4m3_to_float(vb[e]) * vs);
+        }
+        *reinterpret_cast<uint4*>(ko + i) = *reinterpret_cast<const uint4*>(kq);
+        *reinterpret_cast<uint4*>(vo + i) = *reinterpret_cast<const uint4*>(vq);
+      }
+    } else {
+      for (int i = threadIdx.x; i < row_elems; i += kThreads) {
+        ko[i] = T(e4m3_to_float(k_pages[src + i]) * ks);
+        vo[i] = T(e4m3_to_float(v_pages[src + i]) * vs);
+      }
     }
   } else {
     const size_t src = size_t(cu_q[b] + t - old) * row_elems;
-    for (int i = threadIdx.x; i < row_elems; i += kThreads) {
-      ko[i] = k_new[src + i];
-      vo[i] = v_new[src + i];
+    if (row_elems % 8 == 0) {
+      for (int i = threadIdx.x * 8; i < row_elems; i += kThreads * 8) {
+        *reinterpret_cast<uint4*>(ko + i) = *reinterpret_cast<const uint4*>(k_new + src + i);
+        *reinterpret_cast<uint4*>(vo + i) = *reinterpret_cast<const uint4*>(v_new + src + i);
+      }
+    } else {
+      for (int i = threadIdx.x; i < row_elems; i += kThreads) {
+        ko[i] = k_new[src + i];
+        vo[i] = v_new[src + i];
+      }
     }
   }
 }
@@ -83,9 +106,25 @@ __global__ void __launch_bounds__(kThreads) fp8_cache_append_kernel(
   const size_t dst = (size_t(page) * page_size + pos % page_size) * row_elems;
   const size_t src = size_t(t) * row_elems;
   const float ks = *k_scale, vs = *v_scale;
-  for (int i = threadIdx.x; i < row_elems; i += kThreads) {
-    k_pages[dst + i] = float_to_e4m3(__fdiv_rn(float(k_new[src + i]), ks));
-    v_pages[dst + i] = float_to_e4m3(__fdiv_rn(float(v_new[src + i]), vs));
+  if (row_elems % 8 == 0) {
+    for (int i = threadIdx.x * 8; i < row_elems; i += kThreads * 8) {
+      alignas(16) T kq[8], vq[8];
+      alignas(8) unsigned char kb[8], vb[8];
+      *reinterpret_cast<uint4*>(kq) = *reinterpret_cast<const uint4*>(k_new + src + i);
+      *reinterpret_cast<uint4*>(vq) = *reinterpret_cast<const uint4*>(v_new + src + i);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        kb[e] = float_to_e4m3(__fdiv_rn(float(kq[e]), ks));
+        vb[e] = float_to_e4m3(__fdiv_rn(float(vq[e]), vs));
+      }
+      *reinterpret_cast<uint2*>(k_pages + dst + i) = *reinterpret_cast<const uint2*>(kb);
+      *reinterpret_cast<uint2*>(v_pages + dst + i) = *reinterpret_cast<const uint2*>(vb);
+    }
+  } else {
+    for (int i = threadIdx.x; i < row_elems; i += kThreads) {
+      k_pages[dst + i] = float_to_e4m3(__fdiv_rn(float(k_new[src + i]), ks));
+      v_pages[dst + i] = float_to_e4m3(__fdiv_rn(float(v_new[src + i]), vs));
+    }
   }
 }
 
