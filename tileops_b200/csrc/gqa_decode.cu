@@ -97,7 +97,11 @@ struct DecodeParams {
   float* part_ml;  // [max_items][hb][2]
 };
 
-template <int D, bool FP8>
+// WIDE (16-bit caches, up to 8 q heads per KV head): 3 CTAs per SM with a 2-stage ring instead of 2
+// CTAs with 3 stages.  Measured on B200: +7.5 % on 131k-token contexts (6.5 TB/s, the copy peak),
+// -1 % on ragged 0.5k-8k contexts, -12 % on short uniform batches, so the host picks it only where
+// every sequence may be long.
+template <int D, bool FP8, bool WIDE = false>
 struct Cfg {
   static constexpr int kEsize = FP8 ? 1 : 2;
   static constexpr int kRowBytes = D * kEsize;
@@ -105,19 +109,19 @@ struct Cfg {
   static constexpr int kChunksPerRow = kRowBytes / 16;
   static constexpr int kTileBytes = kTile * kRowStride;
   static constexpr int kStageBytes = 2 * kTileBytes + (FP8 ? 2 * kTile * 4 : 0);
-  static constexpr int kStages = FP8 ? TB200_DEC_STAGES8 : TB200_DEC_STAGES16;
+  static constexpr int kStages = FP8 ? TB200_DEC_STAGES8 : (WIDE ? 2 : TB200_DEC_STAGES16);
   static constexpr int kOStride = D + 4;  // fp32 words per head in the cross-warp merge area
 };
 
 // Resident CTAs per SM the kernel is compiled for (it bounds the registers per thread): the FP8
 // kernel for up to 8 q heads per KV head fits 128 registers, the 16-head one does not.
-__host__ __device__ constexpr int min_blocks(bool fp8, int nt) {
-  return fp8 ? (nt == 1 ? TB200_DEC_BLOCKS8 : 3) : TB200_DEC_BLOCKS16;
+__host__ __device__ constexpr int min_blocks(bool fp8, int nt, bool wide = false) {
+  return fp8 ? (nt == 1 ? TB200_DEC_BLOCKS8 : 3) : (wide ? 3 : TB200_DEC_BLOCKS16);
 }
 
-template <int D, bool FP8>
+template <int D, bool FP8, bool WIDE = false>
 size_t smem_bytes(int batch, int nt) {
-  using C = Cfg<D, FP8>;
+  using C = Cfg<D, FP8, WIDE>;
   size_t ring = size_t(C::kStages) * C::kStageBytes;
   size_t merge = size_t(kWarps) * (8 * nt) * (C::kOStride + 2) * 4;
   size_t a = ring > merge ? ring : merge;
@@ -136,9 +140,9 @@ __device__ __forceinline__ float apply_softcap(float x, float cap, float inv_cap
 //      S^T = K q_hi^T + K q_lo^T (two MMAs per 32 dims) and O^T += [V^T V^T] [P_hi; P_lo] (hi and
 //      lo stacked on the k axis of one MMA).  Needs one scale per tile and tensor: tiles that lie
 //      inside one page (page_size a multiple of 64); other layouts use the f16 expansion path.
-template <int D, bool FP8, typename T, int NT, typename TO, bool F8M = false>
-__global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT)) gqa_decode_kernel(DecodeParams p) {
-  using C = Cfg<D, FP8>;
+template <int D, bool FP8, typename T, int NT, typename TO, bool F8M = false, bool WIDE = false>
+__global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decode_kernel(DecodeParams p) {
+  using C = Cfg<D, FP8, WIDE>;
   constexpr int kKSteps = D / 16;  // MMAs per 16 tokens for S^T, and m-tiles of O^T
   extern __shared__ __align__(128) unsigned char smem[];
 
@@ -888,13 +892,13 @@ struct Layout {
   int hb, n_hb, nt, target_items, max_items, grid;
 };
 
-Layout make_layout(int batch, int heads, int heads_kv, int dim, bool fp8) {
+Layout make_layout(int batch, int heads, int heads_kv, int dim, bool fp8, bool wide = false) {
   Layout L{};
   const int group = heads / heads_kv;
   L.hb = group < 16 ? group : 16;
   L.nt = L.hb <= 8 ? 1 : 2;
   L.n_hb = (group + L.hb - 1) / L.hb;
-  const int blocks_per_sm = min_blocks(fp8, L.nt);
+  const int blocks_per_sm = min_blocks(fp8, L.nt, wide && L.nt == 1);
   L.grid = sm_count() * blocks_per_sm;
   L.target_items = sm_count() * 3 * kItemsPerCta;  // independent of the cache dtype
   L.max_items = batch * heads_kv * L.n_hb + L.target_items;
@@ -906,10 +910,10 @@ Layout make_layout(int batch, int heads, int heads_kv, int dim, bool fp8) {
   return L;
 }
 
-template <int D, bool FP8, typename T, int NT, typename TO, bool F8M = false>
+template <int D, bool FP8, typename T, int NT, typename TO, bool F8M = false, bool WIDE = false>
 int launch(const DecodeParams& p, int grid, cudaStream_t stream) {
-  auto kern = gqa_decode_kernel<D, FP8, T, NT, TO, F8M>;
-  const size_t smem = smem_bytes<D, FP8>(p.batch, NT);
+  auto kern = gqa_decode_kernel<D, FP8, T, NT, TO, F8M, WIDE>;
+  const size_t smem = smem_bytes<D, FP8, WIDE>(p.batch, NT);
   static thread_local size_t configured[16] = {0};
   int dev = 0;
   TB200_CUDA_CHECK(cudaGetDevice(&dev));
@@ -924,18 +928,18 @@ int launch(const DecodeParams& p, int grid, cudaStream_t stream) {
   return TB200_OK;
 }
 
-template <int D, bool FP8, typename T, int NT, bool F8M = false>
+template <int D, bool FP8, typename T, int NT, bool F8M = false, bool WIDE = false>
 int launch_o(const DecodeParams& p, int o_dtype, int grid, cudaStream_t s) {
   switch (o_dtype) {
-    case TB200_F32: return launch<D, FP8, T, NT, float, F8M>(p, grid, s);
-    case TB200_BF16: return launch<D, FP8, T, NT, __nv_bfloat16, F8M>(p, grid, s);
-    case TB200_F16: return launch<D, FP8, T, NT, __half, F8M>(p, grid, s);
+    case TB200_F32: return launch<D, FP8, T, NT, float, F8M, WIDE>(p, grid, s);
+    case TB200_BF16: return launch<D, FP8, T, NT, __nv_bfloat16, F8M, WIDE>(p, grid, s);
+    case TB200_F16: return launch<D, FP8, T, NT, __half, F8M, WIDE>(p, grid, s);
   }
   TB200_FAIL(TB200_ERR_UNSUPPORTED, "o_dtype %d is not F16, BF16 or F32", o_dtype);
 }
 
 template <int D, int NT>
-int launch_t(const DecodeParams& p, int q_dtype, int kv_dtype, int o_dtype, int grid, cudaStream_t s) {
+int launch_t(const DecodeParams& p, int q_dtype, int kv_dtype, int o_dtype, int grid, bool wide, cudaStream_t s) {
   if (kv_dtype == TB200_E4M3) {
     // The f16 expansion path is the default: on B200 the e4m3 mma.sync path measured slower
     // (3.7 vs 4.4 TB/s on 128 x 4096-token sequences).  TB200_DECODE_FP8_MMA=1 selects it where
@@ -943,6 +947,12 @@ int launch_t(const DecodeParams& p, int q_dtype, int kv_dtype, int o_dtype, int 
     const char* e = getenv("TB200_DECODE_FP8_MMA");
     if (p.tile_in_page && e && e[0] == '1') return launch_o<D, true, __half, NT, true>(p, o_dtype, grid, s);
     return launch_o<D, true, __half, NT>(p, o_dtype, grid, s);
+  }
+  if constexpr (NT == 1) {
+    if (wide) {
+      if (q_dtype == TB200_BF16) return launch_o<D, false, __nv_bfloat16, NT, false, true>(p, o_dtype, grid, s);
+      return launch_o<D, false, __half, NT, false, true>(p, o_dtype, grid, s);
+    }
   }
   if (q_dtype == TB200_BF16) return launch_o<D, false, __nv_bfloat16, NT>(p, o_dtype, grid, s);
   return launch_o<D, false, __half, NT>(p, o_dtype, grid, s);
@@ -998,7 +1008,13 @@ extern "C" int tb200_gqa_decode(const void* q, const void* k, const void* v, voi
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "kv_token_stride must be positive");
 
   const bool fp8 = kv_dtype == TB200_E4M3;
-  const Layout L = make_layout(batch, heads, heads_kv, dim, fp8);
+  // tokens a sequence may hold, as far as the host can tell without reading the lengths
+  const long long capacity = block_table ? (long long)block_table_stride * (page_size > 0 ? page_size : 1)
+                             : real_seqlen_kv ? (kv_token_stride > 0 ? kv_batch_stride / kv_token_stride : 0)
+                                              : (long long)uniform_seqlen;
+  bool wide = !fp8 && heads / heads_kv <= 8 && capacity >= 16384;
+  if (const char* e = getenv("TB200_DECODE_WIDE")) wide = !fp8 && heads / heads_kv <= 8 && e[0] == '1';
+  const Layout L = make_layout(batch, heads, heads_kv, dim, fp8, wide);
   if (!workspace || workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255))
     TB200_FAIL(TB200_ERR_WORKSPACE, "workspace must be 256-byte aligned and hold %zu bytes (got %zu)",
                L.total, workspace_bytes);
@@ -1027,10 +1043,10 @@ extern "C" int tb200_gqa_decode(const void* q, const void* k, const void* v, voi
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dim == 128)
-    return L.nt == 1 ? launch_t<128, 1>(p, q_dtype, kv_dtype, o_dtype, L.grid, s)
-                     : launch_t<128, 2>(p, q_dtype, kv_dtype, o_dtype, L.grid, s);
-  return L.nt == 1 ? launch_t<64, 1>(p, q_dtype, kv_dtype, o_dtype, L.grid, s)
-                   : launch_t<64, 2>(p, q_dtype, kv_dtype, o_dtype, L.grid, s);
+    return L.nt == 1 ? launch_t<128, 1>(p, q_dtype, kv_dtype, o_dtype, L.grid, wide, s)
+                     : launch_t<128, 2>(p, q_dtype, kv_dtype, o_dtype, L.grid, wide, s);
+  return L.nt == 1 ? launch_t<64, 1>(p, q_dtype, kv_dtype, o_dtype, L.grid, wide, s)
+                   : launch_t<64, 2>(p, q_dtype, kv_dtype, o_dtype, L.grid, wide, s);
 }
 
 
