@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory from the REFERENCE's own code.
 
 Run once in a container that has the tile-ai/TileOPs tree mounted (its path is the
-first argument, default ``/root/reference``); the resulting ``*.npz`` / ``*.json``
+first argument); the resulting ``*.npz`` / ``*.json``
 files are committed and are what the CPU test-suite pins ``oracle/gqa_oracle.py``
 against on machines where the reference is absent.
 
@@ -33,7 +33,9 @@ import types
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py <path to a checkout of tile-ai/TileOPs>")
+REF = sys.argv[1]
 HERE = os.path.dirname(os.path.abspath(__file__))
 SEED = 1235  # the reference's own test seed (tests/conftest.py:45)
 
