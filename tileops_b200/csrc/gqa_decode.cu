@@ -159,6 +159,11 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
   int* s_prefix = reinterpret_cast<int*>(smem + kArea);  // [batch + 1] run counts, exclusive scan
   int* s_misc = s_prefix + p.batch + 1;                   // [1] ticket, [2..5] plan scratch, [6],[7] item ids
 
+  // id of this CTA's first work item: requested now, so that the round trip of the atomic runs
+  // under the plan computation; it is stored to shared memory after the plan
+  int first_item_id = 0;
+  if (tid == 0) first_item_id = atomicAdd(&p.counters[0], 1);
+
   const int lanes_per_run = p.heads_kv * p.n_hb;
 
   // ---- plan: cut every sequence into runs of tiles (identical in every CTA) -------------
@@ -367,7 +372,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
 
   // Item ids are fetched one item ahead (two alternating slots), so the round trip of the
   // atomic is hidden behind the loads of the current item instead of sitting between two items.
-  if (tid == 0) s_misc[6] = atomicAdd(&p.counters[0], 1);
+  if (tid == 0) s_misc[6] = first_item_id;
   for (int round = 0;; ++round) {
     __syncthreads();  // previous item's use of the ring / merge area is over; next id is visible
     const int item = s_misc[6 + (round & 1)];

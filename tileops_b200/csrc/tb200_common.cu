@@ -23,4 +23,4 @@ int sm_count() {
 }  // namespace tb200
 
 extern "C" const char* tb200_last_error(void) { return tb200::error_buffer(); }
-extern "C" int tb200_version(void) { return 1; }
+extern "C" int tb200_version(void) { return 102; }  // 1.02: prefill entry points take window sizes; paged prefill, RoPE and FP8-cache entry points
