@@ -444,13 +444,35 @@ def run_cfg5(rank, world, device, steps, warmup, peaks):
     # one CUDA graph per step (decode launch + NCCL all-gather + merge launch): at 4+ GPUs the GPU work of a
     # step is shorter than the time Python needs to issue the three calls.  Every rank takes the same branch.
     graphed = os.environ.get("TB200_BENCH_GRAPH", "1") != "0"
+    # exchange: stores over NVLink from the decode kernel into every rank's symmetric buffer (fused compute +
+    # exchange); falls back to the NCCL all-gather if symmetric memory cannot be set up.  All ranks agree.
+    exchange = "nccl_all_gather"
+    if world > 1 and os.environ.get("TB200_BENCH_PEER", "1") != "0":
+        import torch.distributed as dist
+        ok = torch.ones(1, device=device)
+        try:
+            op.enable_peer_exchange(device)
+        except Exception as exc:  # noqa: BLE001 - reported below, never hidden
+            ok.zero_()
+            print(f"[bench] rank {rank}: peer exchange unavailable ({exc!r}); using the NCCL all-gather", file=sys.stderr)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() > 0:
+            exchange = "peer_stores"
+        else:
+            op._peer = None
     if graphed:
         fn = op.graphed(inp.q, inp.k, inp.v, inp.real_seqlen_kv, inp.block_table)
     ms = max_over_ranks(time_steps(fn, steps, warmup, world), world, device) / steps
+    peer_status = op.peer_status()
+    # drop the graph and the symmetric buffer before the process group is torn down
+    del fn
+    op._peer = None
+    torch.cuda.synchronize(device)
     total = 2 * B * ctx * Hkv * D * 2 + 2 * B * H * D * 2 + 4 * B * (ctx // page) + 4 * B
     return {"gbs": total / (ms * 1e-3) / 1e9, "frac_of_peak": total / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "ms_per_step": ms, "tokens_per_s": B / (ms * 1e-3), "scaling": "strong",
-            "exchange_bytes_per_rank": B * H * (D + 1) * 4 * world, "cuda_graph": graphed,
+            "exchange_bytes_per_rank": B * H * (D + 1) * 4 * world, "cuda_graph": graphed, "exchange": exchange,
+            "peer_wait_status": peer_status,
             "gpu_launches": steps * (2 if world > 1 else 2)}
 
 

@@ -147,6 +147,43 @@ int tb200_gqa_lse_merge(const float* o_parts, const float* lse_parts, void* o, f
                         int64_t lse_part_stride, int o_dtype, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * KV-sequence sharded decode across the GPUs of one node, fused with its exchange (no reference
+ * counterpart: the reference has no multi-GPU attention; same split-KV algebra as its combine grid,
+ * src/tileops/kernels/attention/gqa_decode_paged.py:176-395, taken across ranks).
+ *
+ * Rank `rank` of `world` (2..8) holds a slice of every sequence's KV.  tb200_gqa_decode_sharded runs the
+ * decode kernel on the slice and stores the normalised fp32 partial O and its log2-domain LSE straight
+ * into EVERY rank's exchange buffer through peer-mapped pointers (NVLink stores from the decode kernel
+ * itself; no collective call), then raises this rank's flag on every rank.  tb200_gqa_lse_merge_wait
+ * (next on the same stream) waits, bounded (~0.5 s, then code 501 in *status), for all ranks' flags
+ * and merges the parts from local memory.
+ *   peer_buffers[r]: base of rank r's exchange buffer as mapped into this process, 16-byte aligned:
+ *       float [2 parities][world slots][batch * heads * (dim + 1)]   (slot = O [batch*heads][dim], then LSE)
+ *   peer_flags[r]:   address of this rank's flag word on rank r: int flags[world] on every rank, zeroed
+ *       once before the first step; peer_flags[r] = &flags_of_rank_r[rank]
+ *   step_counter:    local device int, zeroed once; advanced by every step (a launch reads its step number
+ *       and buffer parity from it, so the pair of launches can be replayed from a CUDA graph)
+ * All ranks must run the same sequence of steps; consecutive steps alternate the buffer parity, which is
+ * enough because a rank cannot start step s + 2 before every rank has merged step s.
+ * Merge arguments: o_parts = own buffer base, o_part_stride = slot size in floats,
+ * lse_parts = o_parts + batch * heads * dim, lse_part_stride = slot size, parity_stride = world * slot size.
+ * ------------------------------------------------------------------------- */
+int tb200_gqa_decode_sharded(const void* q, const void* k, const void* v,
+                             const int32_t* real_seqlen_kv, int32_t uniform_seqlen,
+                             const int32_t* block_table, int32_t block_table_stride,
+                             const float* k_scale, const float* v_scale, int q_dtype, int kv_dtype,
+                             int batch, int heads, int heads_kv, int dim, int page_size,
+                             int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
+                             float sm_scale, float softcap, void* const* peer_buffers,
+                             int* const* peer_flags, int* step_counter, int world, int rank,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+int tb200_gqa_lse_merge_wait(const float* o_parts, const float* lse_parts, void* o, float* lse,
+                             int parts, int64_t rows, int dim, int64_t o_part_stride,
+                             int64_t lse_part_stride, int64_t parity_stride, int o_dtype,
+                             const int* flags, const int* step_counter, int* status, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Dense GQA prefill (flash attention forward), BSHD, bottom-right aligned causal mask.
  *
  * Replaces the forward of GQAPrefillFwdKernel (src/tileops/kernels/attention/gqa_fwd.py:519-597)

@@ -45,6 +45,17 @@ SIGNATURES = {
         c_int64, c_int64, c_int64,
         c_float, c_float,
         c_void_p]),                                            # stream (no workspace arguments)
+    "tb200_gqa_decode_sharded": (c_int, [
+        c_void_p, c_void_p, c_void_p,                          # q k v
+        c_void_p, c_int32, c_void_p, c_int32,                  # lens uniform bt bt_stride
+        c_void_p, c_void_p, c_int, c_int,                      # k_scale v_scale q/kv dtype
+        c_int, c_int, c_int, c_int, c_int,                     # batch heads heads_kv dim page
+        c_int64, c_int64, c_int64, c_float, c_float,           # strides sm_scale softcap
+        c_void_p, c_void_p, c_void_p, c_int, c_int,            # peer_buffers peer_flags step_counter world rank
+        c_void_p, c_size_t, c_void_p]),                        # workspace bytes stream
+    "tb200_gqa_lse_merge_wait": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int64, c_int64, c_int64, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p]),              # flags step_counter status stream
     "tb200_gqa_lse_merge": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int,
                                     c_int64, c_int64, c_int, c_void_p]),
     "tb200_gqa_prefill_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),

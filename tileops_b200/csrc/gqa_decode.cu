@@ -68,6 +68,7 @@ constexpr int kMinChunkTiles = 2;  // never cut a sequence into runs shorter tha
 #endif
 constexpr int kItemsPerCta = TB200_DEC_ITEMS_PER_CTA;  // target number of work items per resident CTA
 constexpr int kMaxBatch = 4096;
+constexpr int kMaxPeers = 8;
 
 struct DecodeParams {
   const void* q;
@@ -95,6 +96,16 @@ struct DecodeParams {
   int* counters;   // [0] next item, [1] CTAs done, [2 + (b*heads_kv + hk)*n_hb + hb] tickets
   float* part_o;   // [max_items][hb][D]
   float* part_ml;  // [max_items][hb][2]
+  // KV-sequence sharding over GPUs (world > 1): the fp32 result and its LSE are stored straight into
+  // every rank's exchange buffer over NVLink instead of p.o / p.lse, and the last CTA raises this
+  // rank's flag on every rank.  Step number and buffer parity come from a device counter, so the
+  // launch can be replayed from a CUDA graph.
+  int world;
+  float* peer_o[kMaxPeers];     // rank r's buffer base (this rank's slot is selected in the kernel)
+  int* peer_flag[kMaxPeers];    // this rank's flag word on rank r
+  int* step_counter;            // local; step = *step_counter + 1, written back by the last CTA
+  long long slot_floats;        // floats of one rank's slot: batch * heads * (D + 1)
+  int rank;
 };
 
 // WIDE (16-bit caches, up to 8 q heads per KV head): 3 CTAs per SM with a 2-stage ring instead of 2
@@ -132,6 +143,28 @@ __device__ __forceinline__ float apply_softcap(float x, float cap, float inv_cap
   return cap * fast_tanh(x * inv_cap);
 }
 
+// Final (normalised) output element and LSE of a (sequence, q head).  Single GPU: to p.o / p.lse.
+// Sharded over GPUs: the same fp32 value goes to this rank's slot of the current parity in every
+// rank's exchange buffer (plain stores through peer-mapped pointers), O at [row][d], LSE behind it.
+template <typename TO>
+__device__ __forceinline__ void emit_out(const DecodeParams& p, int parity, size_t row, int d, int dim, float val) {
+  if (p.world > 1) {
+    const size_t off = (size_t(parity) * p.world + p.rank) * size_t(p.slot_floats) + row * dim + d;
+    for (int r = 0; r < p.world; ++r) p.peer_o[r][off] = val;
+  } else {
+    store_out<TO>(reinterpret_cast<TO*>(p.o) + row * dim + d, val);
+  }
+}
+__device__ __forceinline__ void emit_lse(const DecodeParams& p, int parity, size_t row, int dim, float val) {
+  if (p.world > 1) {
+    const size_t off = (size_t(parity) * p.world + p.rank) * size_t(p.slot_floats) +
+                       size_t(p.batch) * p.heads * dim + row;
+    for (int r = 0; r < p.world; ++r) p.peer_o[r][off] = val;
+  } else if (p.lse) {
+    p.lse[row] = val;
+  }
+}
+
 // T  : MMA element type (bf16 or f16).  For FP8 caches T is f16 and q is converted.
 // TO : output element type.
 // F8M: FP8 cache consumed by e4m3 tensor-core MMAs (m16n8k32) with no expansion at all.  K and V
@@ -163,6 +196,10 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
   // under the plan computation; it is stored to shared memory after the plan
   int first_item_id = 0;
   if (tid == 0) first_item_id = atomicAdd(&p.counters[0], 1);
+  // sharded over GPUs: number of this step (every CTA reads the same value: the counter is advanced
+  // by the last CTA of a launch) and the half of the exchange buffers it uses
+  const int step = p.world > 1 ? *reinterpret_cast<volatile int*>(p.step_counter) + 1 : 0;
+  const int parity = step & 1;
 
   const int lanes_per_run = p.heads_kv * p.n_hb;
 
@@ -327,7 +364,6 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
     // One pass over the runs with a running maximum.  Each thread owns kOut outputs and issues
     // the loads of a run for all of them before using any, so a merge costs about one memory
     // round trip per run instead of one per run and output.
-    TO* out = reinterpret_cast<TO*>(p.o);
     constexpr int kOut = (8 * NT * D) / kThreads;
     float acc[kOut], L[kOut], M[kOut];
 #pragma unroll
@@ -362,9 +398,9 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
       const int idx = tid + k * kThreads;
       if (idx < n_out) {
         const int hn = idx / D, d = idx - hn * D;
-        store_out<TO>(out + (size_t(pend.b) * p.heads + pend.head0 + hn) * D + d, L[k] > 0.f ? acc[k] / L[k] : 0.f);
-        if (d == 0 && p.lse)
-          p.lse[size_t(pend.b) * p.heads + pend.head0 + hn] = L[k] > 0.f ? M[k] + log2f(L[k]) : -INFINITY;
+        const size_t orow = size_t(pend.b) * p.heads + pend.head0 + hn;
+        emit_out<TO>(p, parity, orow, d, D, L[k] > 0.f ? acc[k] / L[k] : 0.f);
+        if (d == 0) emit_lse(p, parity, orow, D, L[k] > 0.f ? M[k] + log2f(L[k]) : -INFINITY);
       }
     }
     if (tid == 0) *pend.ticket = 0;  // leave the workspace zeroed for the next launch
@@ -838,7 +874,6 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
     const bool single = (n_runs == 1);
     float* po = p.part_o + size_t(item) * p.hb * D;
     float* pml = p.part_ml + size_t(item) * p.hb * 2;
-    TO* out = reinterpret_cast<TO*>(p.o);
     for (int idx = tid; idx < n_heads * D; idx += kThreads) {
       const int hn = idx / D, d = idx - hn * D;
       float mw[kWarps], M = kNegFloor;
@@ -855,8 +890,9 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
         L += e * s_ml[(w * (8 * NT) + hn) * 2 + 1];
       }
       if (single) {
-        store_out<TO>(out + (size_t(b) * p.heads + head0 + hn) * D + d, L > 0.f ? acc / L : 0.f);
-        if (d == 0 && p.lse) p.lse[size_t(b) * p.heads + head0 + hn] = L > 0.f ? M + log2f(L) : -INFINITY;
+        const size_t orow = size_t(b) * p.heads + head0 + hn;
+        emit_out<TO>(p, parity, orow, d, D, L > 0.f ? acc / L : 0.f);
+        if (d == 0) emit_lse(p, parity, orow, D, L > 0.f ? M + log2f(L) : -INFINITY);
       } else {
         po[hn * D + d] = acc;
         if (d == 0) { pml[hn * 2] = M; pml[hn * 2 + 1] = L; }
@@ -879,6 +915,11 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
   resolve_pending();
 
   // ---- the last CTA to leave resets the scheduler counters ------------------------------
+  if (p.world > 1) {
+    // every thread pushes its stores to the other GPUs out to system scope before the CTA reports
+    __threadfence_system();
+    __syncthreads();
+  }
   if (tid == 0) {
     __threadfence();
     const int done = atomicAdd(&p.counters[1], 1);
@@ -886,6 +927,13 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
       p.counters[0] = 0;
       p.counters[1] = 0;
       __threadfence();
+      if (p.world > 1) {
+        // all CTAs of this launch have reported: every rank's copy of this rank's result is complete
+        *p.step_counter = step;
+        __threadfence_system();
+        for (int r = 0; r < p.world; ++r)
+          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer_flag[r]), "r"(step) : "memory");
+      }
     }
   }
 }
@@ -973,16 +1021,24 @@ extern "C" size_t tb200_gqa_decode_workspace_bytes(int batch, int heads, int hea
   return make_layout(batch, heads, heads_kv, dim, false).total;
 }
 
-extern "C" int tb200_gqa_decode(const void* q, const void* k, const void* v, void* o, float* lse,
-                                const int32_t* real_seqlen_kv, int32_t uniform_seqlen,
-                                const int32_t* block_table, int32_t block_table_stride,
-                                const float* k_scale, const float* v_scale,
-                                int q_dtype, int kv_dtype, int o_dtype,
-                                int batch, int heads, int heads_kv, int dim, int page_size,
-                                int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
-                                float sm_scale, float softcap,
-                                void* workspace, size_t workspace_bytes, void* stream) {
-  if (!q || !k || !v || !o) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k, v and o must be non-null");
+namespace {
+struct PeerTargets {
+  int world, rank;
+  void* const* buffers;   // [world] base of every rank's exchange buffer, as mapped into this process
+  int* const* flags;      // [world] this rank's flag word on every rank
+  int* step_counter;      // local device int
+};
+
+int decode_impl(const void* q, const void* k, const void* v, void* o, float* lse,
+                const int32_t* real_seqlen_kv, int32_t uniform_seqlen,
+                const int32_t* block_table, int32_t block_table_stride,
+                const float* k_scale, const float* v_scale,
+                int q_dtype, int kv_dtype, int o_dtype,
+                int batch, int heads, int heads_kv, int dim, int page_size,
+                int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
+                float sm_scale, float softcap,
+                void* workspace, size_t workspace_bytes, void* stream, const PeerTargets* peers) {
+  if (!q || !k || !v || (!o && !peers)) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k, v and o must be non-null");
   if (batch <= 0 || heads <= 0 || heads_kv <= 0 || dim <= 0)
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "batch, heads, heads_kv and dim must be positive");
   if (heads % heads_kv != 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "heads must be divisible by heads_kv");
@@ -1041,6 +1097,14 @@ extern "C" int tb200_gqa_decode(const void* q, const void* k, const void* v, voi
     const char* e = getenv("TB200_DECODE_CHUNK_TILES");
     p.force_chunk = e ? atoi(e) : 0;
   }
+  if (peers) {
+    p.world = peers->world; p.rank = peers->rank; p.step_counter = peers->step_counter;
+    p.slot_floats = (long long)batch * heads * (dim + 1);
+    for (int r = 0; r < peers->world; ++r) {
+      p.peer_o[r] = static_cast<float*>(peers->buffers[r]);
+      p.peer_flag[r] = peers->flags[r];
+    }
+  }
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   p.counters = reinterpret_cast<int*>(ws);
   p.part_o = reinterpret_cast<float*>(ws + L.counters_bytes);
@@ -1052,6 +1116,44 @@ extern "C" int tb200_gqa_decode(const void* q, const void* k, const void* v, voi
                      : launch_t<128, 2>(p, q_dtype, kv_dtype, o_dtype, L.grid, wide, s);
   return L.nt == 1 ? launch_t<64, 1>(p, q_dtype, kv_dtype, o_dtype, L.grid, wide, s)
                    : launch_t<64, 2>(p, q_dtype, kv_dtype, o_dtype, L.grid, wide, s);
+}
+}  // namespace
+
+extern "C" int tb200_gqa_decode(const void* q, const void* k, const void* v, void* o, float* lse,
+                                const int32_t* real_seqlen_kv, int32_t uniform_seqlen,
+                                const int32_t* block_table, int32_t block_table_stride,
+                                const float* k_scale, const float* v_scale,
+                                int q_dtype, int kv_dtype, int o_dtype,
+                                int batch, int heads, int heads_kv, int dim, int page_size,
+                                int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
+                                float sm_scale, float softcap,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  return decode_impl(q, k, v, o, lse, real_seqlen_kv, uniform_seqlen, block_table, block_table_stride, k_scale,
+                     v_scale, q_dtype, kv_dtype, o_dtype, batch, heads, heads_kv, dim, page_size, kv_token_stride,
+                     kv_head_stride, kv_batch_stride, sm_scale, softcap, workspace, workspace_bytes, stream, nullptr);
+}
+
+extern "C" int tb200_gqa_decode_sharded(const void* q, const void* k, const void* v,
+                                        const int32_t* real_seqlen_kv, int32_t uniform_seqlen,
+                                        const int32_t* block_table, int32_t block_table_stride,
+                                        const float* k_scale, const float* v_scale, int q_dtype, int kv_dtype,
+                                        int batch, int heads, int heads_kv, int dim, int page_size,
+                                        int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
+                                        float sm_scale, float softcap, void* const* peer_buffers,
+                                        int* const* peer_flags, int* step_counter, int world, int rank,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+  if (world < 2 || world > kMaxPeers || rank < 0 || rank >= world)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "world must be 2..%d and rank inside it", kMaxPeers);
+  if (!peer_buffers || !peer_flags || !step_counter)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "peer_buffers, peer_flags and step_counter must be non-null");
+  for (int r = 0; r < world; ++r)
+    if (!peer_buffers[r] || !peer_flags[r] || (reinterpret_cast<uintptr_t>(peer_buffers[r]) & 15))
+      TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "peer buffer / flag %d is null or misaligned", r);
+  const PeerTargets peers{world, rank, peer_buffers, peer_flags, step_counter};
+  return decode_impl(q, k, v, nullptr, nullptr, real_seqlen_kv, uniform_seqlen, block_table, block_table_stride,
+                     k_scale, v_scale, q_dtype, kv_dtype, TB200_F32, batch, heads, heads_kv, dim, page_size,
+                     kv_token_stride, kv_head_stride, kv_batch_stride, sm_scale, softcap, workspace, workspace_bytes,
+                     stream, &peers);
 }
 
 

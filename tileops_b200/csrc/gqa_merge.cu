@@ -9,30 +9,61 @@
 namespace tb200 {
 namespace {
 
+// Arrival flags of a KV-sequence sharded step (flags != null): the parts are written into this GPU's
+// memory by the other ranks' decode kernels over NVLink; rank r then stores the step number to
+// flags[r] (release, system scope).  Every block waits until all flags have reached the step this
+// GPU's own decode kernel just finished (*step_counter), at most ~0.5 s; on a timeout it records
+// code 501 in *status and leaves its output untouched.  With flags the parts of a step live in the
+// half of the buffers chosen by the step's parity (parity_stride floats apart).
 template <typename TO>
-__global__ void __launch_bounds__(128) lse_merge_kernel(const float* __restrict__ o_parts,
-                                                        const float* __restrict__ lse_parts,
+__global__ void __launch_bounds__(128) lse_merge_kernel(const float* o_parts, const float* lse_parts,
                                                         TO* __restrict__ o, float* __restrict__ lse,
                                                         int parts, int64_t rows, int dim,
-                                                        int64_t o_stride, int64_t lse_stride) {
+                                                        int64_t o_stride, int64_t lse_stride,
+                                                        const int* flags, const int* step_counter,
+                                                        int64_t parity_stride, int* status) {
   const int64_t row = blockIdx.x;
   if (row >= rows) return;
+  if (flags) {
+    __shared__ int s_ok;
+    int step = 0;
+    if (threadIdx.x == 0) {
+      step = *reinterpret_cast<const volatile int*>(step_counter);
+      const long long t0 = clock64();
+      int ok = 1;
+      for (int r = 0; r < parts && ok; ++r) {
+        int seen;
+        do {
+          asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flags + r) : "memory");
+          if (seen - step >= 0) break;
+          if (clock64() - t0 > 1000000000LL) { ok = 0; break; }
+        } while (true);
+      }
+      if (!ok && status) atomicCAS(status, 0, 501);
+      s_ok = ok ? step + 1 : 0;          // step >= 1, so 0 is free to mean "gave up"
+    }
+    __syncthreads();
+    if (s_ok == 0) return;
+    const int64_t shift = int64_t((s_ok - 1) & 1) * parity_stride;
+    o_parts += shift;
+    lse_parts += shift;
+  }
   float M = kNegFloor;
   for (int r = 0; r < parts; ++r) {
-    float l = lse_parts[int64_t(r) * lse_stride + row];
+    float l = __ldcg(lse_parts + int64_t(r) * lse_stride + row);
     if (l > -1e29f) M = fmaxf(M, l);   // -inf and the finite floor both mean "empty"
   }
   float den = 0.f;
   for (int r = 0; r < parts; ++r) {
-    float l = lse_parts[int64_t(r) * lse_stride + row];
+    float l = __ldcg(lse_parts + int64_t(r) * lse_stride + row);
     if (l > -1e29f) den += fast_exp2(l - M);
   }
   const float inv = den > 0.f ? 1.f / den : 0.f;
   for (int d = threadIdx.x; d < dim; d += blockDim.x) {
     float acc = 0.f;
     for (int r = 0; r < parts; ++r) {
-      float l = lse_parts[int64_t(r) * lse_stride + row];
-      if (l > -1e29f) acc += fast_exp2(l - M) * o_parts[int64_t(r) * o_stride + row * dim + d];
+      float l = __ldcg(lse_parts + int64_t(r) * lse_stride + row);
+      if (l > -1e29f) acc += fast_exp2(l - M) * __ldcg(o_parts + int64_t(r) * o_stride + row * dim + d);
     }
     store_out<TO>(o + row * dim + d, acc * inv);
   }
@@ -44,9 +75,10 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const float* __restrict_
 
 using namespace tb200;
 
-extern "C" int tb200_gqa_lse_merge(const float* o_parts, const float* lse_parts, void* o, float* lse,
-                                   int parts, int64_t rows, int dim, int64_t o_part_stride,
-                                   int64_t lse_part_stride, int o_dtype, void* stream) {
+namespace {
+int merge_impl(const float* o_parts, const float* lse_parts, void* o, float* lse, int parts, int64_t rows, int dim,
+               int64_t o_part_stride, int64_t lse_part_stride, int o_dtype, const int* flags,
+               const int* step_counter, int64_t parity_stride, int* status, void* stream) {
   if (!o_parts || !lse_parts || !o) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "o_parts, lse_parts and o must be non-null");
   if (parts <= 0 || rows <= 0 || dim <= 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "parts, rows and dim must be positive");
   if (o_part_stride == 0) o_part_stride = rows * dim;
@@ -58,17 +90,34 @@ extern "C" int tb200_gqa_lse_merge(const float* o_parts, const float* lse_parts,
   const unsigned grid = static_cast<unsigned>(rows);
   switch (o_dtype) {
     case TB200_F32:
-      lse_merge_kernel<float><<<grid, 128, 0, s>>>(o_parts, lse_parts, static_cast<float*>(o), lse, parts, rows, dim, o_part_stride, lse_part_stride);
+      lse_merge_kernel<float><<<grid, 128, 0, s>>>(o_parts, lse_parts, static_cast<float*>(o), lse, parts, rows, dim, o_part_stride, lse_part_stride, flags, step_counter, parity_stride, status);
       break;
     case TB200_BF16:
-      lse_merge_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(o_parts, lse_parts, static_cast<__nv_bfloat16*>(o), lse, parts, rows, dim, o_part_stride, lse_part_stride);
+      lse_merge_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(o_parts, lse_parts, static_cast<__nv_bfloat16*>(o), lse, parts, rows, dim, o_part_stride, lse_part_stride, flags, step_counter, parity_stride, status);
       break;
     case TB200_F16:
-      lse_merge_kernel<__half><<<grid, 128, 0, s>>>(o_parts, lse_parts, static_cast<__half*>(o), lse, parts, rows, dim, o_part_stride, lse_part_stride);
+      lse_merge_kernel<__half><<<grid, 128, 0, s>>>(o_parts, lse_parts, static_cast<__half*>(o), lse, parts, rows, dim, o_part_stride, lse_part_stride, flags, step_counter, parity_stride, status);
       break;
     default:
       TB200_FAIL(TB200_ERR_UNSUPPORTED, "o_dtype %d is not F16, BF16 or F32", o_dtype);
   }
   TB200_CUDA_CHECK(cudaGetLastError());
   return TB200_OK;
+}
+}  // namespace
+
+extern "C" int tb200_gqa_lse_merge(const float* o_parts, const float* lse_parts, void* o, float* lse,
+                                   int parts, int64_t rows, int dim, int64_t o_part_stride,
+                                   int64_t lse_part_stride, int o_dtype, void* stream) {
+  return merge_impl(o_parts, lse_parts, o, lse, parts, rows, dim, o_part_stride, lse_part_stride, o_dtype, nullptr,
+                    nullptr, 0, nullptr, stream);
+}
+
+extern "C" int tb200_gqa_lse_merge_wait(const float* o_parts, const float* lse_parts, void* o, float* lse,
+                                        int parts, int64_t rows, int dim, int64_t o_part_stride,
+                                        int64_t lse_part_stride, int64_t parity_stride, int o_dtype,
+                                        const int* flags, const int* step_counter, int* status, void* stream) {
+  if (!flags || !step_counter) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "flags and step_counter must be non-null");
+  return merge_impl(o_parts, lse_parts, o, lse, parts, rows, dim, o_part_stride, lse_part_stride, o_dtype, flags,
+                    step_counter, parity_stride, status, stream);
 }

@@ -58,6 +58,7 @@ class KVSequenceShardedPagedDecode:
         self._decode = decode_fn or self._cuda_decode
         self._merge = merge_fn or self._cuda_merge
         self._buffers: dict = {}
+        self._peer = None
 
     # default compute: the CUDA kernels
     def _cuda_decode(self, q, k, v, lens, bt, out, lse_out):
@@ -83,6 +84,8 @@ class KVSequenceShardedPagedDecode:
         B, H, D = self.batch, self.heads, self.dim
         if tuple(q.shape) != (B, H, D):
             raise ValueError(f"q must have shape {(B, H, D)}, got {tuple(q.shape)}")
+        if getattr(self, "_peer", None) is not None:
+            return self._forward_peer(q, k, v, local_seqlen_kv, local_block_table)
         send, recv = self._comm_buffers(q.device)
         n_o = B * H * D
         o_part = send[:n_o].view(B, H, D)
@@ -98,13 +101,80 @@ class KVSequenceShardedPagedDecode:
 
     __call__ = forward
 
+    # ---- fused exchange over peer memory ---------------------------------------------------
+    def enable_peer_exchange(self, device: torch.device) -> None:
+        """Switch the exchange from the NCCL all-gather to stores over NVLink issued by the decode kernel
+        itself (``tb200_gqa_decode_sharded`` / ``tb200_gqa_lse_merge_wait``).  The exchange buffer is
+        symmetric memory (``torch.distributed._symmetric_memory``): every rank maps every rank's buffer.
+        Collective: all ranks call it.  Raises if symmetric memory is not available; the NCCL path is
+        untouched in that case."""
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+        if self.world < 2 or self.world > 8:
+            raise RuntimeError("peer exchange serves 2..8 ranks")
+        n = self.batch * self.heads * (self.dim + 1)
+        flag_words = 64
+        buf = symm_mem.empty(2 * self.world * n + flag_words, dtype=torch.float32, device=device)
+        buf.zero_()
+        group = self.group if self.group is not None else dist.group.WORLD
+        hdl = symm_mem.rendezvous(buf, group)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        if len(ptrs) != self.world or ptrs[self.rank] != buf.data_ptr():
+            raise RuntimeError("symmetric memory rendezvous returned unexpected buffer pointers")
+        flags_off = 2 * self.world * n * 4
+        self._peer = {
+            "buf": buf, "hdl": hdl, "slot": n,
+            "buffers": (ctypes.c_void_p * self.world)(*ptrs),
+            "flags": (ctypes.c_void_p * self.world)(*[p + flags_off + self.rank * 4 for p in ptrs]),
+            "own_flags": buf.data_ptr() + flags_off,
+            "step": torch.zeros(1, dtype=torch.int32, device=device),
+            "status": torch.zeros(1, dtype=torch.int32, device=device),
+        }
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)      # every buffer is zeroed before any rank stores into it
+
+    def peer_status(self) -> int:
+        """0, or 501 if a merge gave up waiting for another rank's flag (synchronises)."""
+        return int(self._peer["status"].item()) if getattr(self, "_peer", None) else 0
+
+    def _forward_peer(self, q, k, v, lens, bt) -> torch.Tensor:
+        import ctypes
+
+        from . import _native as N
+        B, H, D, P = self.batch, self.heads, self.dim, self._peer
+        Hkv = k.shape[1]
+        fp8 = k.dtype == getattr(torch, "float8_e4m3fn", None)
+        if fp8:
+            raise ValueError("the peer exchange path serves 16-bit caches")
+        q, k, v, lens, bt = q.contiguous(), k.contiguous(), v.contiguous(), lens.contiguous(), bt.contiguous()
+        ws = F._decode_workspace(q.device, B, H, Hkv, D)
+        out = torch.empty((B, H, D), dtype=q.dtype, device=q.device)
+        lib, stream = N.lib(), N.current_stream(q.device)
+        with torch.cuda.device(q.device):
+            st = lib.tb200_gqa_decode_sharded(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), lens.data_ptr(), 0, bt.data_ptr(), bt.shape[1], None, None,
+                N.dtype_code(q.dtype), N.dtype_code(k.dtype), B, H, Hkv, D, self.page_size, k.stride(0), k.stride(1), 0,
+                float(self.sm_scale), float(self.softcap), ctypes.addressof(P["buffers"]), ctypes.addressof(P["flags"]),
+                P["step"].data_ptr(), self.world, self.rank, ws.data_ptr(), ws.numel(), stream)
+            N.check(st, "tb200_gqa_decode_sharded")
+            base = P["buf"].data_ptr()
+            st = lib.tb200_gqa_lse_merge_wait(
+                base, base + B * H * D * 4, out.data_ptr(), None, self.world, B * H, D, P["slot"], P["slot"],
+                self.world * P["slot"], N.dtype_code(q.dtype), P["own_flags"], P["step"].data_ptr(),
+                P["status"].data_ptr(), stream)
+            N.check(st, "tb200_gqa_lse_merge_wait")
+        return out
+
     def graphed(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, local_seqlen_kv: torch.Tensor,
                 local_block_table: torch.Tensor, warmup: int = 3) -> Callable[[], torch.Tensor]:
         """Capture one ``forward`` on these tensors (decode launch, all-gather, merge launch) in a CUDA
         graph and return a callable that replays it and returns the (static) output tensor.  At 4+
         GPUs a long-context step is ~0.1 ms of GPU work, less than the host spends issuing the three
         calls from Python; the replay is one launch.  The tensors are read in place at every replay
-        (update them in place between replays); every rank must capture and replay in step.
+        (update them in place between replays); every rank must capture and replay in step.  Drop the
+        returned callable before the process group is destroyed: tearing down a communicator that a live
+        graph still references blocks.
         """
         args = (q, k, v, local_seqlen_kv, local_block_table)
         side = torch.cuda.Stream(device=q.device)
