@@ -242,30 +242,31 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
       const int c = i == kCand - 1 ? max_tiles : ((i & 1) ? 12 : 8) << (i >> 1);
       return min(max(c, c_min), max(max_tiles, c_min));
     };
-    int it_[kCand], sp_[kCand], mx_[kCand];
-#pragma unroll
-    for (int i = 0; i < kCand; ++i) { it_[i] = 0; sp_[i] = 0; mx_[i] = 0; }
-    for (int b = tid; b < p.batch; b += kThreads) {
-      const int len = p.lens ? p.lens[b] : p.uniform_len;
-      const int t = (max(len, 0) + kTile - 1) / kTile;
-#pragma unroll
-      for (int i = 0; i < kCand; ++i) {
-        const int c = cand(i);
+    // Thread t scores candidate t % 16 over the sequences b with b % 8 == t / 16: a short rolled loop
+    // (the code runs once per CTA straight from a cold instruction cache, so it is kept small) with its
+    // three partial results in registers; the 8 threads of a candidate meet in shared memory.
+    {
+      static_assert(kCand == 16 && kThreads == 128, "the mapping below assumes 16 candidates and 128 threads");
+      const int ci = tid & (kCand - 1);
+      const int c = cand(ci);
+      int it = 0, sp = 0, mx = 0;
+#pragma unroll 1
+      for (int b = tid >> 4; b < p.batch; b += kThreads / kCand) {
+        const int len = p.lens ? p.lens[b] : p.uniform_len;
+        const int t = (max(len, 0) + kTile - 1) / kTile;
         const int n = max(1, (t + c - 1) / c);
-        it_[i] += n;
-        sp_[i] += n > 1 ? n : 0;
-        mx_[i] = max(mx_[i], (t + n - 1) / n);
+        it += n;
+        sp += n > 1 ? n : 0;
+        mx = max(mx, (t + n - 1) / n);
       }
-    }
-#pragma unroll
-    for (int i = 0; i < kCand; ++i) {
-      const int a0 = __reduce_add_sync(0xffffffffu, it_[i]);
-      const int a1 = __reduce_add_sync(0xffffffffu, sp_[i]);
-      const int a2 = __reduce_max_sync(0xffffffffu, mx_[i]);
-      if (lane == 0) {
-        atomicAdd(&s_cand[i * 3], a0);
-        atomicAdd(&s_cand[i * 3 + 1], a1);
-        atomicMax(&s_cand[i * 3 + 2], a2);
+      // lanes l and l + 16 hold the same candidate
+      it += __shfl_xor_sync(0xffffffffu, it, 16);
+      sp += __shfl_xor_sync(0xffffffffu, sp, 16);
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      if (lane < kCand) {
+        atomicAdd(&s_cand[ci * 3], it);
+        atomicAdd(&s_cand[ci * 3 + 1], sp);
+        atomicMax(&s_cand[ci * 3 + 2], mx);
       }
     }
     __syncthreads();
