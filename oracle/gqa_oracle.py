@@ -10,7 +10,9 @@ CPU-baseline leg do, and only as the checker.
 Pinning: every function below is checked against the reference's own code run in
 the build container (fixtures under ``tests/golden/`` produced by
 ``tests/golden/make_golden.py``, which imports the reference's workloads and test
-references).  Two functions have no reference counterpart and are therefore
+references: decode, paged decode, dense / packed / sliding-window prefill, paged prefill with append and
+its FP8-cache form, GPT-NeoX RoPE, the FP8 quantiser, the roofline formulas).  Two functions have no
+reference counterpart and are therefore
 *parity unpinned* beyond their own definition: the per-(page, KV-head) FP8
 quantiser/dequantiser (the reference only has one scalar scale per cache,
 ``tests/ops/attention/test_gqa_prefill_paged.py:348-356``) and the multi-shard
