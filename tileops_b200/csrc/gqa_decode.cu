@@ -54,6 +54,12 @@ constexpr int kMinChunkTiles = 2;  // never cut a sequence into runs shorter tha
 #ifndef TB200_DEC_PREFETCH_NEXT
 #define TB200_DEC_PREFETCH_NEXT 0
 #endif
+#ifndef TB200_DEC_ITEM_COST16
+#define TB200_DEC_ITEM_COST16 2.f
+#endif
+#ifndef TB200_DEC_SPLIT_COST16
+#define TB200_DEC_SPLIT_COST16 3.f
+#endif
 #ifndef TB200_DEC_ITEM_COST8
 #define TB200_DEC_ITEM_COST8 2.f
 #endif
@@ -216,7 +222,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
     constexpr int kCand = 16;
     // fixed cost of a work item and of a split item, in units of one tile's time; an FP8 tile is half
     // the bytes of a 16-bit one, so the same microseconds are more tiles
-    constexpr float kItemCost = FP8 ? TB200_DEC_ITEM_COST8 : 2.f, kSplitCost = FP8 ? TB200_DEC_SPLIT_COST8 : 3.f;
+    constexpr float kItemCost = FP8 ? TB200_DEC_ITEM_COST8 : TB200_DEC_ITEM_COST16, kSplitCost = FP8 ? TB200_DEC_SPLIT_COST8 : TB200_DEC_SPLIT_COST16;
     int* s_cand = reinterpret_cast<int*>(smem);   // [kCand][3]: items, split items, largest run (ring not in use yet)
     int* s_tot = s_cand + kCand * 3;              // [2]: all tiles, longest sequence in tiles
     if (tid < kCand * 3 + 2) s_cand[tid] = 0;
