@@ -142,7 +142,7 @@ size_t smem_bytes(int batch, int nt) {
   size_t ring = size_t(C::kStages) * C::kStageBytes;
   size_t merge = size_t(kWarps) * (8 * nt) * (C::kOStride + 2) * 4;
   size_t a = ring > merge ? ring : merge;
-  return a + size_t(batch + 1) * 4 + 128;
+  return a + size_t(2 * batch + 1) * 4 + 128;   // run-count prefix [batch + 1] and the lengths [batch]
 }
 
 __device__ __forceinline__ float apply_softcap(float x, float cap, float inv_cap) {
@@ -196,7 +196,8 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
   constexpr size_t kMerge = size_t(kWarps) * (8 * NT) * (C::kOStride + 2) * 4;
   constexpr size_t kArea = kRing > kMerge ? kRing : kMerge;
   int* s_prefix = reinterpret_cast<int*>(smem + kArea);  // [batch + 1] run counts, exclusive scan
-  int* s_misc = s_prefix + p.batch + 1;                   // [1] ticket, [2..5] plan scratch, [6],[7] item ids
+  int* s_lens = s_prefix + p.batch + 1;                   // [batch] context lengths (one global read per CTA)
+  int* s_misc = s_lens + p.batch;                         // [1] ticket, [2..5] plan scratch, [6],[7] item ids
 
   // id of this CTA's first work item: requested now, so that the round trip of the atomic runs
   // under the plan computation; it is stored to shared memory after the plan
@@ -230,6 +231,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
     int local = 0, local_max = 0;
     for (int b = tid; b < p.batch; b += kThreads) {
       const int len = p.lens ? p.lens[b] : p.uniform_len;
+      s_lens[b] = len;              // every later use reads this copy (visible after the barrier below)
       const int t = (max(len, 0) + kTile - 1) / kTile;
       local += t;
       local_max = max(local_max, t);
@@ -258,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
       int it = 0, sp = 0, mx = 0;
 #pragma unroll 1
       for (int b = tid >> 4; b < p.batch; b += kThreads / kCand) {
-        const int len = p.lens ? p.lens[b] : p.uniform_len;
+        const int len = s_lens[b];
         const int t = (max(len, 0) + kTile - 1) / kTile;
         const int n = max(1, (t + c - 1) / c);
         it += n;
@@ -300,7 +302,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
     for (int i = 0; i < per; ++i) {
       int b = b0 + i;
       if (b < p.batch) {
-        int len = p.lens ? p.lens[b] : p.uniform_len;
+        int len = s_lens[b];
         int tiles = (max(len, 0) + kTile - 1) / kTile;
         sum += max(1, (tiles + chunk - 1) / chunk);
       }
@@ -320,7 +322,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
       int b = b0 + i;
       if (b < p.batch) {
         s_prefix[b] = run;
-        int len = p.lens ? p.lens[b] : p.uniform_len;
+        int len = s_lens[b];
         int tiles = (max(len, 0) + kTile - 1) / kTile;
         run += max(1, (tiles + chunk - 1) / chunk);
       }
@@ -432,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
       if (s_prefix[mid] <= run) lo = mid; else hi = mid - 1;
     }
     const int b = lo;
-    const int len = max(p.lens ? p.lens[b] : p.uniform_len, 0);
+    const int len = max(s_lens[b], 0);
     const int tiles_b = (len + kTile - 1) / kTile;
     const int n_runs = s_prefix[b + 1] - s_prefix[b];
     const int j = run - s_prefix[b];
@@ -586,7 +588,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
         if (s_prefix[mid] <= nrun) lo2 = mid; else hi2 = mid - 1;
       }
       nb = lo2;
-      nlen = max(p.lens ? p.lens[nb] : p.uniform_len, 0);
+      nlen = max(s_lens[nb], 0);
       const int ntiles = (nlen + kTile - 1) / kTile;
       const int nruns = s_prefix[nb + 1] - s_prefix[nb];
       const int nrt = (ntiles + nruns - 1) / nruns;
