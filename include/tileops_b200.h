@@ -73,6 +73,12 @@ int tb200_version(void);
  *   kv_token_stride / kv_head_stride / kv_batch_stride: in ELEMENTS of the KV dtype; the last
  *                  dim is contiguous.  kv_batch_stride is used only when block_table == NULL.
  *   sm_scale       multiplies q.k ; softcap > 0 applies cap*tanh(score/cap) before the softmax
+ *   kv_pool_tokens token rows behind k / v (paged: rows of the pool; contiguous: ignored, the row
+ *                  count per sequence is kv_batch_stride / kv_token_stride).  It bounds what the
+ *                  TMA kernel may touch; <= 0 means "not known" (then only the block table bounds it).
+ *   flags          0, or an OR of TB200_DECODE_* values (below): the tuning surface that the
+ *                  reference exposes as config= / autotune_configs
+ *                  (src/tileops/kernels/kernel_base.py:161-202); no environment variable is read.
  *   workspace      tb200_gqa_decode_workspace_bytes(...) bytes, 256-byte aligned, zeroed once.
  *                  The kernel leaves its counters zeroed, so the same buffer serves every later
  *                  call with the SAME (batch, heads, heads_kv, dim); zero it again before using
@@ -82,7 +88,23 @@ int tb200_version(void);
  * A sequence of length 0 produces a zero output row.  Page ids are not range checked.
  * The kernel never blocks on another CTA: split-KV partials are merged by whichever CTA
  * finishes a (sequence, KV head) last.
+ *
+ * Two kernels serve this entry point.  Where every 64-token tile is contiguous in memory (no block
+ * table, or page_size a multiple of 64), token rows are 128 or 256 bytes, q is 16-byte aligned and
+ * a KV head has at most 8 q heads, a producer warp streams K/V tiles by TMA ahead of the math
+ * warps, across work-item boundaries; every other layout is served by a kernel whose math warps
+ * issue cp.async gathers themselves.  Waits inside the TMA kernel are bounded (about 0.5 s): if one
+ * runs out the launch stops early and the int at byte offset 8 of the workspace is set to a
+ * non-zero code (601 producer, 602 math warps); the outputs of that launch are then undefined and
+ * the workspace must be zeroed again before its next use.
  * ------------------------------------------------------------------------- */
+#define TB200_DECODE_WIDE_ON 1   /* 16-bit cache: force the 3-CTA / 2-stage cp.async kernel (long contexts) */
+#define TB200_DECODE_WIDE_OFF 2  /* never pick it */
+#define TB200_DECODE_FP8_MMA 4   /* e4m3 cache: e4m3 tensor-core path (page_size % 64 == 0) */
+#define TB200_DECODE_NO_TMA 8    /* keep the cp.async kernel where the TMA kernel would apply */
+#define TB200_DECODE_CHUNK_TILES_SHIFT 8 /* bits 8..23: fixed split-KV run length in 64-token tiles (0 = cost model) */
+#define TB200_DECODE_CHUNK_TILES(n) (((n) & 0xFFFF) << TB200_DECODE_CHUNK_TILES_SHIFT)
+
 size_t tb200_gqa_decode_workspace_bytes(int batch, int heads, int heads_kv, int dim);
 
 int tb200_gqa_decode(const void* q, const void* k, const void* v, void* o, float* lse,
@@ -92,7 +114,7 @@ int tb200_gqa_decode(const void* q, const void* k, const void* v, void* o, float
                      int q_dtype, int kv_dtype, int o_dtype,
                      int batch, int heads, int heads_kv, int dim, int page_size,
                      int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
-                     float sm_scale, float softcap,
+                     float sm_scale, float softcap, int64_t kv_pool_tokens, int flags,
                      void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------
@@ -155,8 +177,10 @@ int tb200_gqa_lse_merge(const float* o_parts, const float* lse_parts, void* o, f
  * decode kernel on the slice and stores the normalised fp32 partial O and its log2-domain LSE straight
  * into EVERY rank's exchange buffer through peer-mapped pointers (NVLink stores from the decode kernel
  * itself; no collective call), then raises this rank's flag on every rank.  tb200_gqa_lse_merge_wait
- * (next on the same stream) waits, bounded (~0.5 s, then code 501 in *status), for all ranks' flags
- * and merges the parts from local memory.
+ * (next on the same stream) waits for all ranks' flags and merges the parts from local memory.  The wait
+ * is bounded: wait_cycles GPU clock ticks (<= 0: about 0.5 s).  When it runs out the kernel records code 501
+ * in *status, fills the rows it could not merge with NaN (o) and -inf (lse), and returns; blocks that start
+ * after *status is set give up at once, so a launch never waits more than about one limit in total.
  *   peer_buffers[r]: base of rank r's exchange buffer as mapped into this process, 16-byte aligned:
  *       float [2 parities][world slots][batch * heads * (dim + 1)]   (slot = O [batch*heads][dim], then LSE)
  *   peer_flags[r]:   address of this rank's flag word on rank r: int flags[world] on every rank, zeroed
@@ -174,14 +198,16 @@ int tb200_gqa_decode_sharded(const void* q, const void* k, const void* v,
                              const float* k_scale, const float* v_scale, int q_dtype, int kv_dtype,
                              int batch, int heads, int heads_kv, int dim, int page_size,
                              int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
-                             float sm_scale, float softcap, void* const* peer_buffers,
+                             float sm_scale, float softcap, int64_t kv_pool_tokens, int flags,
+                             void* const* peer_buffers,
                              int* const* peer_flags, int* step_counter, int world, int rank,
                              void* workspace, size_t workspace_bytes, void* stream);
 
 int tb200_gqa_lse_merge_wait(const float* o_parts, const float* lse_parts, void* o, float* lse,
                              int parts, int64_t rows, int dim, int64_t o_part_stride,
                              int64_t lse_part_stride, int64_t parity_stride, int o_dtype,
-                             const int* flags, const int* step_counter, int* status, void* stream);
+                             const int* flags, const int* step_counter, int* status,
+                             int64_t wait_cycles, void* stream);
 
 /* ---------------------------------------------------------------------------
  * Dense GQA prefill (flash attention forward), BSHD, bottom-right aligned causal mask.

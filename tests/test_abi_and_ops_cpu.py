@@ -46,15 +46,15 @@ def test_abi_rejects_bad_arguments_without_touching_a_gpu():
     assert lib.tb200_gqa_decode_workspace_bytes(4, 30, 8, 128) == 0
     assert lib.tb200_gqa_decode_workspace_bytes(64, 32, 8, 128) > 0
     st = lib.tb200_gqa_decode(None, None, None, None, None, None, 0, None, 0, None, None, 1, 1, 1,
-                              1, 8, 2, 64, 16, 128, 64, 0, 1.0, 0.0, None, 0, None)
+                              1, 8, 2, 64, 16, 128, 64, 0, 1.0, 0.0, 0, 0, None, 0, None)
     assert st == 1 and b"non-null" in lib.tb200_last_error()
     buf = ctypes.create_string_buffer(64)
     p = ctypes.addressof(buf)
     st = lib.tb200_gqa_decode(p, p, p, p, None, None, 16, None, 0, None, None, 1, 1, 1,
-                              1, 8, 3, 64, 16, 128, 64, 0, 1.0, 0.0, None, 0, None)
+                              1, 8, 3, 64, 16, 128, 64, 0, 1.0, 0.0, 0, 0, None, 0, None)
     assert st == 1 and b"divisible" in lib.tb200_last_error()
     st = lib.tb200_gqa_decode(p, p, p, p, None, None, 16, None, 0, None, None, 1, 1, 1,
-                              1, 8, 2, 96, 16, 192, 96, 0, 1.0, 0.0, None, 0, None)
+                              1, 8, 2, 96, 16, 192, 96, 0, 1.0, 0.0, 0, 0, None, 0, None)
     assert st == 2 and b"head dim" in lib.tb200_last_error()
     st = lib.tb200_gqa_lse_merge(None, None, None, None, 2, 4, 64, 0, 0, 3, None)
     assert st == 1

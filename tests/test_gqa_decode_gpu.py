@@ -277,15 +277,14 @@ def test_sharded_decode_graph_replay_matches_eager():
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_wide_variant_for_long_capacity_caches(dtype, monkeypatch):
+def test_wide_variant_for_long_capacity_caches(dtype):
     # 3 CTAs per SM with a 2-stage ring: chosen by the library when a sequence may hold >= 16k tokens;
     # forced here on a ragged batch, and reached naturally by a table with 16k-token capacity
     inp = W.make_paged_decode(62, 6, 32, 8, 128, 64, len_range=(100, 5000), dtype=dtype, device="cuda")
     ref = O.paged_decode_ref(inp.q.cpu(), inp.k.cpu(), inp.v.cpu(), inp.real_seqlen_kv.cpu(), inp.block_table.cpu(), 64)
-    monkeypatch.setenv("TB200_DECODE_WIDE", "1")
-    o = F.gqa_decode(inp.q, inp.k, inp.v, real_seqlen_kv=inp.real_seqlen_kv, block_table=inp.block_table, page_size=64)
+    o = F.gqa_decode(inp.q, inp.k, inp.v, real_seqlen_kv=inp.real_seqlen_kv, block_table=inp.block_table, page_size=64,
+                     config={"wide": True})
     close(o, ref)
-    monkeypatch.delenv("TB200_DECODE_WIDE")
     long = W.make_paged_decode(63, 2, 16, 4, 128, 128, lens=[16384, 9000], dtype=dtype, device="cuda")
     assert long.block_table.shape[1] * 128 >= 16384
     o = F.gqa_decode(long.q, long.k, long.v, real_seqlen_kv=long.real_seqlen_kv, block_table=long.block_table,

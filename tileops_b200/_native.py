@@ -11,12 +11,40 @@ from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_
 
 import torch
 
-#: ``TB200_LIBRARY`` points at another build of the same library (comparing kernel variants)
-_LIB_PATH = os.environ.get("TB200_LIBRARY") or os.path.join(
-    os.path.dirname(os.path.abspath(__file__)), "_lib", "libtileops_b200.so")
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_lib", "libtileops_b200.so")
+
+
+def use_library(path: str) -> None:
+    """Load another build of the same library instead of the in-tree one (comparing kernel variants).
+    Must be called before the first kernel call."""
+    global _LIB_PATH, _lib
+    _LIB_PATH, _lib = path, None
 
 OK = 0
 F16, BF16, E4M3, F32 = 0, 1, 2, 3
+# variant flags of tb200_gqa_decode (TB200_DECODE_* in include/tileops_b200.h)
+DECODE_WIDE_ON, DECODE_WIDE_OFF, DECODE_FP8_MMA, DECODE_NO_TMA = 1, 2, 4, 8
+DECODE_CHUNK_TILES_SHIFT = 8
+
+
+def decode_flags(config: "dict | None") -> int:
+    """Variant flags from a kernel ``config`` dict: ``wide`` (True / False / absent = the library's
+    choice), ``fp8_mma``, ``tma`` (False keeps the cp.async kernel), ``chunk_tiles`` (fixed split-KV
+    run length in 64-token tiles)."""
+    if not config:
+        return 0
+    flags = 0
+    wide = config.get("wide")
+    if wide is not None:
+        flags |= DECODE_WIDE_ON if wide else DECODE_WIDE_OFF
+    if config.get("fp8_mma"):
+        flags |= DECODE_FP8_MMA
+    if config.get("tma") is False:
+        flags |= DECODE_NO_TMA
+    chunk = int(config.get("chunk_tiles") or 0)
+    if not 0 <= chunk <= 0xFFFF:
+        raise ValueError(f"chunk_tiles={chunk} is outside [0, 65535]")
+    return flags | (chunk << DECODE_CHUNK_TILES_SHIFT)
 
 _DTYPE_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
 if hasattr(torch, "float8_e4m3fn"):
@@ -34,7 +62,7 @@ SIGNATURES = {
         c_int, c_int, c_int,                                   # q/kv/o dtype
         c_int, c_int, c_int, c_int, c_int,                     # batch heads heads_kv dim page
         c_int64, c_int64, c_int64,                             # strides
-        c_float, c_float,                                      # sm_scale softcap
+        c_float, c_float, c_int64, c_int,                      # sm_scale softcap kv_pool_tokens flags
         c_void_p, c_size_t, c_void_p]),                        # workspace bytes stream
     "tb200_gqa_decode_noalloc": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -51,11 +79,12 @@ SIGNATURES = {
         c_void_p, c_void_p, c_int, c_int,                      # k_scale v_scale q/kv dtype
         c_int, c_int, c_int, c_int, c_int,                     # batch heads heads_kv dim page
         c_int64, c_int64, c_int64, c_float, c_float,           # strides sm_scale softcap
+        c_int64, c_int,                                        # kv_pool_tokens flags
         c_void_p, c_void_p, c_void_p, c_int, c_int,            # peer_buffers peer_flags step_counter world rank
         c_void_p, c_size_t, c_void_p]),                        # workspace bytes stream
     "tb200_gqa_lse_merge_wait": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int64, c_int64, c_int64, c_int,
-        c_void_p, c_void_p, c_void_p, c_void_p]),              # flags step_counter status stream
+        c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),     # flags step_counter status wait_cycles stream
     "tb200_gqa_lse_merge": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int,
                                     c_int64, c_int64, c_int, c_void_p]),
     "tb200_gqa_prefill_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),

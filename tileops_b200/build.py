@@ -85,6 +85,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    for obj in objs:                 # only the library is shipped; objects would ride along in every copy
+        os.remove(obj)
     with open(stamp, "w") as fh:
         fh.write(digest)
     return LIB

@@ -22,20 +22,11 @@
 //   * partial (O, max, sum) of an item go to a workspace in fp32; the CTA that finishes a
 //     (sequence, KV head) last merges them (acq_rel atomic ticket taken after the next
 //     item's loads are issued; nobody waits).
-#include <stdlib.h>
-
-#include "tb200_common.cuh"
+#include "gqa_decode.cuh"
 
 namespace tb200 {
 namespace {
 
-constexpr int kTile = 64;          // tokens per shared-memory tile
-constexpr int kThreads = 128;      // 4 warps x 16 tokens
-constexpr int kWarps = 4;
-constexpr int kMinChunkTiles = 2;  // never cut a sequence into runs shorter than this
-#ifndef TB200_DEC_ITEMS_PER_CTA
-#define TB200_DEC_ITEMS_PER_CTA 8
-#endif
 #ifndef TB200_DEC_DEFER
 #define TB200_DEC_DEFER 1
 #endif
@@ -54,65 +45,12 @@ constexpr int kMinChunkTiles = 2;  // never cut a sequence into runs shorter tha
 #ifndef TB200_DEC_PREFETCH_NEXT
 #define TB200_DEC_PREFETCH_NEXT 0
 #endif
-#ifndef TB200_DEC_ITEM_COST16
-#define TB200_DEC_ITEM_COST16 2.f
-#endif
-#ifndef TB200_DEC_SPLIT_COST16
-#define TB200_DEC_SPLIT_COST16 3.f
-#endif
-#ifndef TB200_DEC_ITEM_COST8
-#define TB200_DEC_ITEM_COST8 2.f
-#endif
-#ifndef TB200_DEC_SPLIT_COST8
-#define TB200_DEC_SPLIT_COST8 3.f
-#endif
 #ifndef TB200_DEC_STAGES8
 #define TB200_DEC_STAGES8 3
 #endif
 #ifndef TB200_DEC_BLOCKS8
 #define TB200_DEC_BLOCKS8 4
 #endif
-constexpr int kItemsPerCta = TB200_DEC_ITEMS_PER_CTA;  // target number of work items per resident CTA
-constexpr int kMaxBatch = 4096;
-constexpr int kMaxPeers = 8;
-
-struct DecodeParams {
-  const void* q;
-  const void* k;
-  const void* v;
-  void* o;
-  float* lse;
-  const int32_t* lens;
-  int32_t uniform_len;
-  const int32_t* bt;
-  int32_t bt_stride;
-  const float* k_scale;
-  const float* v_scale;
-  int batch, heads, heads_kv, group;
-  int hb;       // q heads handled by one item (<= 8*NT)
-  int n_hb;     // head blocks per KV head
-  int page_size;
-  int tile_in_page;  // 1 when page_size % 64 == 0: a tile never straddles two pages
-  int64_t tok_stride, head_stride, batch_stride;  // elements
-  float sm_scale, softcap;
-  int q_is_bf16;
-  int target_items;
-  int max_items;
-  int force_chunk;  // > 0: run length in tiles (debug switch TB200_DECODE_CHUNK_TILES)
-  int* counters;   // [0] next item, [1] CTAs done, [2 + (b*heads_kv + hk)*n_hb + hb] tickets
-  float* part_o;   // [max_items][hb][D]
-  float* part_ml;  // [max_items][hb][2]
-  // KV-sequence sharding over GPUs (world > 1): the fp32 result and its LSE are stored straight into
-  // every rank's exchange buffer over NVLink instead of p.o / p.lse, and the last CTA raises this
-  // rank's flag on every rank.  Step number and buffer parity come from a device counter, so the
-  // launch can be replayed from a CUDA graph.
-  int world;
-  float* peer_o[kMaxPeers];     // rank r's buffer base (this rank's slot is selected in the kernel)
-  int* peer_flag[kMaxPeers];    // this rank's flag word on rank r
-  int* step_counter;            // local; step = *step_counter + 1, written back by the last CTA
-  long long slot_floats;        // floats of one rank's slot: batch * heads * (D + 1)
-  int rank;
-};
 
 // WIDE (16-bit caches, up to 8 q heads per KV head): 3 CTAs per SM with a 2-stage ring instead of 2
 // CTAs with 3 stages.  Measured on B200: +7.5 % on 131k-token contexts (6.5 TB/s, the copy peak),
@@ -143,32 +81,6 @@ size_t smem_bytes(int batch, int nt) {
   size_t merge = size_t(kWarps) * (8 * nt) * (C::kOStride + 2) * 4;
   size_t a = ring > merge ? ring : merge;
   return a + size_t(2 * batch + 1) * 4 + 128;   // run-count prefix [batch + 1] and the lengths [batch]
-}
-
-__device__ __forceinline__ float apply_softcap(float x, float cap, float inv_cap) {
-  return cap * fast_tanh(x * inv_cap);
-}
-
-// Final (normalised) output element and LSE of a (sequence, q head).  Single GPU: to p.o / p.lse.
-// Sharded over GPUs: the same fp32 value goes to this rank's slot of the current parity in every
-// rank's exchange buffer (plain stores through peer-mapped pointers), O at [row][d], LSE behind it.
-template <typename TO>
-__device__ __forceinline__ void emit_out(const DecodeParams& p, int parity, size_t row, int d, int dim, float val) {
-  if (p.world > 1) {
-    const size_t off = (size_t(parity) * p.world + p.rank) * size_t(p.slot_floats) + row * dim + d;
-    for (int r = 0; r < p.world; ++r) p.peer_o[r][off] = val;
-  } else {
-    store_out<TO>(reinterpret_cast<TO*>(p.o) + row * dim + d, val);
-  }
-}
-__device__ __forceinline__ void emit_lse(const DecodeParams& p, int parity, size_t row, int dim, float val) {
-  if (p.world > 1) {
-    const size_t off = (size_t(parity) * p.world + p.rank) * size_t(p.slot_floats) +
-                       size_t(p.batch) * p.heads * dim + row;
-    for (int r = 0; r < p.world; ++r) p.peer_o[r][off] = val;
-  } else if (p.lse) {
-    p.lse[row] = val;
-  }
 }
 
 // T  : MMA element type (bf16 or f16).  For FP8 caches T is f16 and q is converted.
@@ -210,126 +122,10 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
 
   const int lanes_per_run = p.heads_kv * p.n_hb;
 
-  // ---- plan: cut every sequence into runs of tiles (identical in every CTA) -------------
-  // The run length is chosen from a short list by a cost model in units of one tile's time:
-  //   cost(c) = max(W/P, largest run if there are fewer runs than CTAs)
-  //           + (items per CTA) * kItemCost + (split items per CTA) * kSplitCost
-  //           + half a run of tail imbalance when CTAs take more than one item
-  // (W = all tiles, P = CTAs).  Short runs balance ragged batches; long runs avoid the refill of
-  // the load pipeline, the partial results and the merge; an unsplit sequence costs least per
-  // item.  Integer sums and maxima are reduced with order-independent atomics, so every CTA
-  // arrives at the same plan.
-  {
-    constexpr int kCand = 16;
-    // fixed cost of a work item and of a split item, in units of one tile's time; an FP8 tile is half
-    // the bytes of a 16-bit one, so the same microseconds are more tiles
-    constexpr float kItemCost = FP8 ? TB200_DEC_ITEM_COST8 : TB200_DEC_ITEM_COST16, kSplitCost = FP8 ? TB200_DEC_SPLIT_COST8 : TB200_DEC_SPLIT_COST16;
-    int* s_cand = reinterpret_cast<int*>(smem);   // [kCand][3]: items, split items, largest run (ring not in use yet)
-    int* s_tot = s_cand + kCand * 3;              // [2]: all tiles, longest sequence in tiles
-    if (tid < kCand * 3 + 2) s_cand[tid] = 0;
-    __syncthreads();
-    int local = 0, local_max = 0;
-    for (int b = tid; b < p.batch; b += kThreads) {
-      const int len = p.lens ? p.lens[b] : p.uniform_len;
-      s_lens[b] = len;              // every later use reads this copy (visible after the barrier below)
-      const int t = (max(len, 0) + kTile - 1) / kTile;
-      local += t;
-      local_max = max(local_max, t);
-    }
-    local = __reduce_add_sync(0xffffffffu, local);
-    local_max = __reduce_max_sync(0xffffffffu, local_max);
-    if (lane == 0) { atomicAdd(&s_tot[0], local); atomicMax(&s_tot[1], local_max); }
-    __syncthreads();
-    const long long total_tiles = s_tot[0];
-    const int max_tiles = max(s_tot[1], 1);
-    // the workspace holds batch*lanes + target_items partials: never cut finer than this
-    const int c_min = (int)max((long long)kMinChunkTiles,
-                               (total_tiles * lanes_per_run + p.target_items - 1) / p.target_items);
-    auto cand = [&](int i) {
-      // 8, 12, 16, 24, 32, 48, ... , 1024, then "do not split"
-      const int c = i == kCand - 1 ? max_tiles : ((i & 1) ? 12 : 8) << (i >> 1);
-      return min(max(c, c_min), max(max_tiles, c_min));
-    };
-    // Thread t scores candidate t % 16 over the sequences b with b % 8 == t / 16: a short rolled loop
-    // (the code runs once per CTA straight from a cold instruction cache, so it is kept small) with its
-    // three partial results in registers; the 8 threads of a candidate meet in shared memory.
-    {
-      static_assert(kCand == 16 && kThreads == 128, "the mapping below assumes 16 candidates and 128 threads");
-      const int ci = tid & (kCand - 1);
-      const int c = cand(ci);
-      int it = 0, sp = 0, mx = 0;
-#pragma unroll 1
-      for (int b = tid >> 4; b < p.batch; b += kThreads / kCand) {
-        const int len = s_lens[b];
-        const int t = (max(len, 0) + kTile - 1) / kTile;
-        const int n = max(1, (t + c - 1) / c);
-        it += n;
-        sp += n > 1 ? n : 0;
-        mx = max(mx, (t + n - 1) / n);
-      }
-      // lanes l and l + 16 hold the same candidate
-      it += __shfl_xor_sync(0xffffffffu, it, 16);
-      sp += __shfl_xor_sync(0xffffffffu, sp, 16);
-      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-      if (lane < kCand) {
-        atomicAdd(&s_cand[ci * 3], it);
-        atomicAdd(&s_cand[ci * 3 + 1], sp);
-        atomicMax(&s_cand[ci * 3 + 2], mx);
-      }
-    }
-    __syncthreads();
-    int chunk = cand(kCand - 1);
-    if (p.force_chunk > 0) {
-      chunk = max(p.force_chunk, c_min);
-    } else {
-      const float P = float(gridDim.x);
-      const float w_per_cta = float(total_tiles) * lanes_per_run / P;
-      float best = 3.0e38f;
-      for (int i = 0; i < kCand; ++i) {
-        const float k = float(s_cand[i * 3]) * lanes_per_run / P;
-        const float ks = float(s_cand[i * 3 + 1]) * lanes_per_run / P;
-        const float big = float(s_cand[i * 3 + 2]);
-        const float cost = fmaxf(w_per_cta, k <= 1.f ? big : 0.f) + k * kItemCost + ks * kSplitCost +
-                           (k > 1.f ? 0.5f * big : 0.f);
-        if (cost <= best) { best = cost; chunk = cand(i); }   // ties go to the longer run
-      }
-    }
-    __syncthreads();   // s_cand lives in the ring
-
-    const int per = (p.batch + kThreads - 1) / kThreads;
-    const int b0 = tid * per;
-    int sum = 0;
-    for (int i = 0; i < per; ++i) {
-      int b = b0 + i;
-      if (b < p.batch) {
-        int len = s_lens[b];
-        int tiles = (max(len, 0) + kTile - 1) / kTile;
-        sum += max(1, (tiles + chunk - 1) / chunk);
-      }
-    }
-    int incl = sum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      int n = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += n;
-    }
-    if (lane == 31) s_misc[2 + warp] = incl;
-    __syncthreads();
-    int base = 0;
-    for (int w = 0; w < warp; ++w) base += s_misc[2 + w];
-    int run = base + incl - sum;
-    for (int i = 0; i < per; ++i) {
-      int b = b0 + i;
-      if (b < p.batch) {
-        s_prefix[b] = run;
-        int len = s_lens[b];
-        int tiles = (max(len, 0) + kTile - 1) / kTile;
-        run += max(1, (tiles + chunk - 1) / chunk);
-      }
-      if (b == p.batch - 1) s_prefix[p.batch] = run;
-    }
-    __syncthreads();
-  }
+  // ---- plan: cut every sequence into runs of tiles (identical in every CTA); its scratch lives in the
+  // ring, which is not in use yet
+  decode_plan<FP8>(p, tid, reinterpret_cast<int*>(smem), s_prefix, s_lens, s_misc + 2, [] { __syncthreads(); });
+  __syncthreads();
   const int total_items = s_prefix[p.batch] * lanes_per_run;
 
   const float qk_scale = p.softcap > 0.f ? p.sm_scale : p.sm_scale * kLog2e;
@@ -911,7 +707,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
       // the ticket for this (sequence, KV head, head block) is taken at the start of the next
       // item, after that item's first loads are in flight
       pend.valid = true;
-      pend.ticket = p.counters + 2 + (size_t(b) * p.heads_kv + hk) * p.n_hb + hbi;
+      pend.ticket = p.counters + kCounterWords + (size_t(b) * p.heads_kv + hk) * p.n_hb + hbi;
       pend.n_runs = n_runs;
       pend.first_item = s_prefix[b] * lanes_per_run + rem;
       pend.b = b; pend.head0 = head0; pend.n_heads = n_heads;
@@ -949,75 +745,62 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
 
 // ---- host side ------------------------------------------------------------------------------
 
-struct Layout {
-  size_t counters_bytes, part_o_bytes, part_ml_bytes, total;
-  int hb, n_hb, nt, target_items, max_items, grid;
-};
-
-Layout make_layout(int batch, int heads, int heads_kv, int dim, bool fp8, bool wide = false) {
-  Layout L{};
-  const int group = heads / heads_kv;
-  L.hb = group < 16 ? group : 16;
-  L.nt = L.hb <= 8 ? 1 : 2;
-  L.n_hb = (group + L.hb - 1) / L.hb;
-  const int blocks_per_sm = min_blocks(fp8, L.nt, wide && L.nt == 1);
-  L.grid = sm_count() * blocks_per_sm;
-  L.target_items = sm_count() * 3 * kItemsPerCta;  // independent of the cache dtype
-  L.max_items = batch * heads_kv * L.n_hb + L.target_items;
-  auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
-  L.counters_bytes = up(size_t(2 + size_t(batch) * heads_kv * L.n_hb) * 4);
-  L.part_o_bytes = up(size_t(L.max_items) * L.hb * dim * 4);
-  L.part_ml_bytes = up(size_t(L.max_items) * L.hb * 2 * 4);
-  L.total = L.counters_bytes + L.part_o_bytes + L.part_ml_bytes;
-  return L;
-}
-
 template <int D, bool FP8, typename T, int NT, typename TO, bool F8M = false, bool WIDE = false>
-int launch(const DecodeParams& p, int grid, cudaStream_t stream) {
+int launch(const DecodeParams& p, cudaStream_t stream) {
   auto kern = gqa_decode_kernel<D, FP8, T, NT, TO, F8M, WIDE>;
   const size_t smem = smem_bytes<D, FP8, WIDE>(p.batch, NT);
-  static thread_local size_t configured[16] = {0};
+  // per device: the largest dynamic shared memory size configured so far, and the number of CTAs an
+  // SM holds at the size of the last launch (the grid is one CTA per resident slot: a CTA that starts
+  // late finds the item queue empty and only costs its plan)
+  static thread_local size_t configured[64] = {0};
+  static thread_local size_t sized_for[64] = {0};
+  static thread_local int resident[64] = {0};
   int dev = 0;
   TB200_CUDA_CHECK(cudaGetDevice(&dev));
-  if (dev < 16 && configured[dev] < smem) {
+  if (dev < 0 || dev >= 64) TB200_FAIL(TB200_ERR_UNSUPPORTED, "device index %d is outside [0, 64)", dev);
+  if (configured[dev] < smem) {
     TB200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured[dev] = smem;
-  } else if (dev >= 16) {
-    TB200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
-  kern<<<grid, kThreads, smem, stream>>>(p);
+  if (sized_for[dev] != smem) {
+    int n = 0;
+    TB200_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem));
+    if (n <= 0) TB200_FAIL(TB200_ERR_UNSUPPORTED, "the decode kernel does not fit an SM with %zu bytes of shared memory", smem);
+    sized_for[dev] = smem;
+    resident[dev] = n < min_blocks(FP8, NT, WIDE) ? n : min_blocks(FP8, NT, WIDE);
+  }
+  kern<<<sm_count() * resident[dev], kThreads, smem, stream>>>(p);
   TB200_CUDA_CHECK(cudaGetLastError());
   return TB200_OK;
 }
 
 template <int D, bool FP8, typename T, int NT, bool F8M = false, bool WIDE = false>
-int launch_o(const DecodeParams& p, int o_dtype, int grid, cudaStream_t s) {
+int launch_o(const DecodeParams& p, int o_dtype, cudaStream_t s) {
   switch (o_dtype) {
-    case TB200_F32: return launch<D, FP8, T, NT, float, F8M, WIDE>(p, grid, s);
-    case TB200_BF16: return launch<D, FP8, T, NT, __nv_bfloat16, F8M, WIDE>(p, grid, s);
-    case TB200_F16: return launch<D, FP8, T, NT, __half, F8M, WIDE>(p, grid, s);
+    case TB200_F32: return launch<D, FP8, T, NT, float, F8M, WIDE>(p, s);
+    case TB200_BF16: return launch<D, FP8, T, NT, __nv_bfloat16, F8M, WIDE>(p, s);
+    case TB200_F16: return launch<D, FP8, T, NT, __half, F8M, WIDE>(p, s);
   }
   TB200_FAIL(TB200_ERR_UNSUPPORTED, "o_dtype %d is not F16, BF16 or F32", o_dtype);
 }
 
 template <int D, int NT>
-int launch_t(const DecodeParams& p, int q_dtype, int kv_dtype, int o_dtype, int grid, bool wide, cudaStream_t s) {
+int launch_t(const DecodeParams& p, int q_dtype, int kv_dtype, int o_dtype, bool wide, bool fp8_mma, cudaStream_t s) {
   if (kv_dtype == TB200_E4M3) {
     // The f16 expansion path is the default: on B200 the e4m3 mma.sync path measured slower
-    // (3.7 vs 4.4 TB/s on 128 x 4096-token sequences).  TB200_DECODE_FP8_MMA=1 selects it where
+    // (3.7 vs 4.4 TB/s on 128 x 4096-token sequences).  TB200_DECODE_FP8_MMA selects it where
     // its precondition holds (one scale per tile, i.e. page_size a multiple of 64).
-    const char* e = getenv("TB200_DECODE_FP8_MMA");
-    if (p.tile_in_page && e && e[0] == '1') return launch_o<D, true, __half, NT, true>(p, o_dtype, grid, s);
-    return launch_o<D, true, __half, NT>(p, o_dtype, grid, s);
+    if (p.tile_in_page && fp8_mma) return launch_o<D, true, __half, NT, true>(p, o_dtype, s);
+    return launch_o<D, true, __half, NT>(p, o_dtype, s);
   }
   if constexpr (NT == 1) {
     if (wide) {
-      if (q_dtype == TB200_BF16) return launch_o<D, false, __nv_bfloat16, NT, false, true>(p, o_dtype, grid, s);
-      return launch_o<D, false, __half, NT, false, true>(p, o_dtype, grid, s);
+      if (q_dtype == TB200_BF16) return launch_o<D, false, __nv_bfloat16, NT, false, true>(p, o_dtype, s);
+      return launch_o<D, false, __half, NT, false, true>(p, o_dtype, s);
     }
   }
-  if (q_dtype == TB200_BF16) return launch_o<D, false, __nv_bfloat16, NT>(p, o_dtype, grid, s);
-  return launch_o<D, false, __half, NT>(p, o_dtype, grid, s);
+  if (q_dtype == TB200_BF16) return launch_o<D, false, __nv_bfloat16, NT>(p, o_dtype, s);
+  return launch_o<D, false, __half, NT>(p, o_dtype, s);
 }
 
 }  // namespace
@@ -1027,7 +810,7 @@ using namespace tb200;
 
 extern "C" size_t tb200_gqa_decode_workspace_bytes(int batch, int heads, int heads_kv, int dim) {
   if (batch <= 0 || heads <= 0 || heads_kv <= 0 || dim <= 0 || heads % heads_kv != 0) return 0;
-  return make_layout(batch, heads, heads_kv, dim, false).total;
+  return make_layout(batch, heads, heads_kv, dim).total;
 }
 
 namespace {
@@ -1045,7 +828,7 @@ int decode_impl(const void* q, const void* k, const void* v, void* o, float* lse
                 int q_dtype, int kv_dtype, int o_dtype,
                 int batch, int heads, int heads_kv, int dim, int page_size,
                 int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
-                float sm_scale, float softcap,
+                float sm_scale, float softcap, int64_t kv_pool_tokens, int flags,
                 void* workspace, size_t workspace_bytes, void* stream, const PeerTargets* peers) {
   if (!q || !k || !v || (!o && !peers)) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k, v and o must be non-null");
   if (batch <= 0 || heads <= 0 || heads_kv <= 0 || dim <= 0)
@@ -1076,15 +859,17 @@ int decode_impl(const void* q, const void* k, const void* v, void* o, float* lse
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "k/v base and strides must be 16-byte aligned (q 8-byte)");
   if (!block_table && kv_token_stride <= 0)
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "kv_token_stride must be positive");
+  if (flags < 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "flags must be a combination of TB200_DECODE_* values");
 
   const bool fp8 = kv_dtype == TB200_E4M3;
+  const DecodeVariant var = parse_variant(flags);
   // tokens a sequence may hold, as far as the host can tell without reading the lengths
   const long long capacity = block_table ? (long long)block_table_stride * (page_size > 0 ? page_size : 1)
                              : real_seqlen_kv ? (kv_token_stride > 0 ? kv_batch_stride / kv_token_stride : 0)
                                               : (long long)uniform_seqlen;
   bool wide = !fp8 && heads / heads_kv <= 8 && capacity >= 16384;
-  if (const char* e = getenv("TB200_DECODE_WIDE")) wide = !fp8 && heads / heads_kv <= 8 && e[0] == '1';
-  const Layout L = make_layout(batch, heads, heads_kv, dim, fp8, wide);
+  if (var.wide >= 0) wide = !fp8 && heads / heads_kv <= 8 && var.wide == 1;
+  const Layout L = make_layout(batch, heads, heads_kv, dim);
   if (!workspace || workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255))
     TB200_FAIL(TB200_ERR_WORKSPACE, "workspace must be 256-byte aligned and hold %zu bytes (got %zu)",
                L.total, workspace_bytes);
@@ -1102,10 +887,8 @@ int decode_impl(const void* q, const void* k, const void* v, void* o, float* lse
   p.sm_scale = sm_scale; p.softcap = softcap;
   p.q_is_bf16 = q_dtype == TB200_BF16;
   p.target_items = L.target_items; p.max_items = L.max_items;
-  {
-    const char* e = getenv("TB200_DECODE_CHUNK_TILES");
-    p.force_chunk = e ? atoi(e) : 0;
-  }
+  p.force_chunk = var.chunk_tiles;
+  p.wait_cycles = 1000000000LL;   // ~0.5 s
   if (peers) {
     p.world = peers->world; p.rank = peers->rank; p.step_counter = peers->step_counter;
     p.slot_floats = (long long)batch * heads * (dim + 1);
@@ -1120,11 +903,18 @@ int decode_impl(const void* q, const void* k, const void* v, void* o, float* lse
   p.part_ml = reinterpret_cast<float*>(ws + L.counters_bytes + L.part_o_bytes);
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The TMA kernel serves caches whose 64-token tiles are contiguous (no table, or pages that are
+  // multiples of 64 tokens) with 128- or 256-byte token rows and up to 8 q heads per KV head; it
+  // declines everything else, and the cp.async kernel below serves every layout.
+  if (!var.no_tma && !var.fp8_mma && var.wide != 1 && !(wide && var.wide < 0)) {
+    const int st = launch_decode_tma(p, q_dtype, kv_dtype, o_dtype, dim, L.nt, kv_pool_tokens, s);
+    if (st != kTmaNotApplicable) return st;
+  }
   if (dim == 128)
-    return L.nt == 1 ? launch_t<128, 1>(p, q_dtype, kv_dtype, o_dtype, L.grid, wide, s)
-                     : launch_t<128, 2>(p, q_dtype, kv_dtype, o_dtype, L.grid, wide, s);
-  return L.nt == 1 ? launch_t<64, 1>(p, q_dtype, kv_dtype, o_dtype, L.grid, wide, s)
-                   : launch_t<64, 2>(p, q_dtype, kv_dtype, o_dtype, L.grid, wide, s);
+    return L.nt == 1 ? launch_t<128, 1>(p, q_dtype, kv_dtype, o_dtype, wide, var.fp8_mma, s)
+                     : launch_t<128, 2>(p, q_dtype, kv_dtype, o_dtype, wide, var.fp8_mma, s);
+  return L.nt == 1 ? launch_t<64, 1>(p, q_dtype, kv_dtype, o_dtype, wide, var.fp8_mma, s)
+                   : launch_t<64, 2>(p, q_dtype, kv_dtype, o_dtype, wide, var.fp8_mma, s);
 }
 }  // namespace
 
@@ -1135,11 +925,12 @@ extern "C" int tb200_gqa_decode(const void* q, const void* k, const void* v, voi
                                 int q_dtype, int kv_dtype, int o_dtype,
                                 int batch, int heads, int heads_kv, int dim, int page_size,
                                 int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
-                                float sm_scale, float softcap,
+                                float sm_scale, float softcap, int64_t kv_pool_tokens, int flags,
                                 void* workspace, size_t workspace_bytes, void* stream) {
   return decode_impl(q, k, v, o, lse, real_seqlen_kv, uniform_seqlen, block_table, block_table_stride, k_scale,
                      v_scale, q_dtype, kv_dtype, o_dtype, batch, heads, heads_kv, dim, page_size, kv_token_stride,
-                     kv_head_stride, kv_batch_stride, sm_scale, softcap, workspace, workspace_bytes, stream, nullptr);
+                     kv_head_stride, kv_batch_stride, sm_scale, softcap, kv_pool_tokens, flags, workspace,
+                     workspace_bytes, stream, nullptr);
 }
 
 extern "C" int tb200_gqa_decode_sharded(const void* q, const void* k, const void* v,
@@ -1148,7 +939,8 @@ extern "C" int tb200_gqa_decode_sharded(const void* q, const void* k, const void
                                         const float* k_scale, const float* v_scale, int q_dtype, int kv_dtype,
                                         int batch, int heads, int heads_kv, int dim, int page_size,
                                         int64_t kv_token_stride, int64_t kv_head_stride, int64_t kv_batch_stride,
-                                        float sm_scale, float softcap, void* const* peer_buffers,
+                                        float sm_scale, float softcap, int64_t kv_pool_tokens, int flags,
+                                        void* const* peer_buffers,
                                         int* const* peer_flags, int* step_counter, int world, int rank,
                                         void* workspace, size_t workspace_bytes, void* stream) {
   if (world < 2 || world > kMaxPeers || rank < 0 || rank >= world)
@@ -1161,8 +953,8 @@ extern "C" int tb200_gqa_decode_sharded(const void* q, const void* k, const void
   const PeerTargets peers{world, rank, peer_buffers, peer_flags, step_counter};
   return decode_impl(q, k, v, nullptr, nullptr, real_seqlen_kv, uniform_seqlen, block_table, block_table_stride,
                      k_scale, v_scale, q_dtype, kv_dtype, TB200_F32, batch, heads, heads_kv, dim, page_size,
-                     kv_token_stride, kv_head_stride, kv_batch_stride, sm_scale, softcap, workspace, workspace_bytes,
-                     stream, &peers);
+                     kv_token_stride, kv_head_stride, kv_batch_stride, sm_scale, softcap, kv_pool_tokens, flags,
+                     workspace, workspace_bytes, stream, &peers);
 }
 
 
@@ -1195,7 +987,8 @@ extern "C" int tb200_gqa_decode_noalloc(const void* q, const void* k, const void
                                         float sm_scale, float softcap, void* stream) {
   if (batch <= 0 || heads <= 0 || heads_kv <= 0 || dim <= 0 || heads % heads_kv != 0)
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "batch, heads, heads_kv and dim must be positive and heads divisible by heads_kv");
-  const Layout L = make_layout(batch, heads, heads_kv, dim, kv_dtype == TB200_E4M3);
+  // (the scratch layout is the same for every kernel variant the library may pick)
+  const Layout L = make_layout(batch, heads, heads_kv, dim);
   if (L.total > kDecodeStaticScratchBytes)
     TB200_FAIL(TB200_ERR_WORKSPACE,
                "this problem needs %zu bytes of scratch but the built-in scratch holds %zu; use "
@@ -1213,6 +1006,6 @@ extern "C" int tb200_gqa_decode_noalloc(const void* q, const void* k, const void
   TB200_CUDA_CHECK(cudaMemsetAsync(g_scratch_addr[dev], 0, L.counters_bytes, static_cast<cudaStream_t>(stream)));
   return tb200_gqa_decode(q, k, v, o, lse, real_seqlen_kv, uniform_seqlen, block_table, block_table_stride,
                           k_scale, v_scale, q_dtype, kv_dtype, o_dtype, batch, heads, heads_kv, dim, page_size,
-                          kv_token_stride, kv_head_stride, kv_batch_stride, sm_scale, softcap,
-                          g_scratch_addr[dev], kDecodeStaticScratchBytes, stream);
+                          kv_token_stride, kv_head_stride, kv_batch_stride, sm_scale, softcap, /*kv_pool_tokens=*/0,
+                          /*flags=*/0, g_scratch_addr[dev], kDecodeStaticScratchBytes, stream);
 }

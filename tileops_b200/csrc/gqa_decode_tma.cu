@@ -1,0 +1,728 @@
+// Single-token GQA decode, sm_100a: a TMA producer warp that streams K/V tiles ahead of the math
+// warps, across work-item boundaries.
+//
+// Role in the reference: the same as gqa_decode.cu (GQADecodeKernel / GQADecodePagedKernel and their
+// split-KV combine, src/tileops/kernels/attention/gqa_decode.py:23-306, gqa_decode_paged.py:44-395 in
+// tile-ai/TileOPs); the producer / consumer split is what the reference's Hopper batch-1 kernels do
+// with a TMA warp and a consumer warpgroup (gqa_decode_bs1_common.py:57-292), here for any batch.
+//
+// Why a second kernel: in gqa_decode.cu the math warps issue their own cp.async gathers, so the
+// load pipeline drains at the end of every work item and refills at the start of the next; on
+// ragged batches that is the largest loss.  Here
+//   * warp 4 owns the shared-memory ring: per 64-token tile it issues one TMA box per 128-byte panel
+//     of K and of V (swizzled, no padding), waits only for a free stage, and walks the CTA's items
+//     back to back, so the next item's first tiles are in flight while the math warps finish the
+//     current one; it also pulls the item ids, copies the item's q rows into shared memory and reads
+//     the block-table entries (32 tiles per global read, one lane each);
+//   * warps 0-3 are the math warps of gqa_decode.cu (tokens on the MMA M dimension, q heads on N = 8,
+//     mma.sync.m16n8k16, movmatrix for P^T, FP8 expanded with cvt.rn.f16x2.e4m3x2), without a single
+//     load instruction or address computation for K/V; stages are handed over with mbarriers, one
+//     arrival per warp; the four warps meet once per item in an 8.7 KB area of its own, half of the
+//     head dims at a time.
+// Served layouts: 64-token tiles contiguous in memory (no block table, or page_size % 64 == 0), token
+// rows of 128 or 256 bytes, up to 8 q heads per KV head.  Everything else goes to gqa_decode.cu.
+//
+// Rows of the last tile behind the sequence end are whatever the pool holds: their scores are
+// replaced by -inf, and their V rows are zeroed in shared memory by the warp that owns them before
+// it reads them (0 x NaN would be NaN).
+//
+// Every wait is bounded (the math warps also meet at an mbarrier, not at a hardware barrier); when
+// one runs out the CTA records a code in counters[2] (601 producer, 602 math warps waiting for data,
+// 603 math warps waiting for each other), raises a flag the other roles poll, and every role leaves.
+#include "gqa_decode.cuh"
+#include "tb200_async.cuh"
+
+namespace tb200 {
+namespace {
+
+#ifndef TB200_DEC_TMA_STAGES16
+#define TB200_DEC_TMA_STAGES16 3
+#endif
+#ifndef TB200_DEC_TMA_BLOCKS16
+#define TB200_DEC_TMA_BLOCKS16 2
+#endif
+#ifndef TB200_DEC_TMA_STAGES8
+#define TB200_DEC_TMA_STAGES8 3
+#endif
+#ifndef TB200_DEC_TMA_BLOCKS8
+#define TB200_DEC_TMA_BLOCKS8 3
+#endif
+
+constexpr int kTmaThreads = kThreads + 32;   // 4 math warps + the producer warp
+constexpr int kItemSlots = 2;                // item descriptors (id + q rows) the producer may post ahead
+constexpr int kMathBarrier = 1;              // named barrier of the 128 math threads (plan only: nothing can give up there)
+
+template <int D, bool FP8>
+struct TmaCfg {
+  static constexpr int kEsize = FP8 ? 1 : 2;
+  static constexpr int kRowBytes = D * kEsize;               // 128 or 256
+  static constexpr int kPanels = kRowBytes / 128;            // 128-byte swizzled panels per row
+  static constexpr int kPanelElems = 128 / kEsize;
+  static constexpr int kPanelBytes = kTile * 128;
+  static constexpr int kTensorBytes = kPanels * kPanelBytes; // K (or V) of one tile
+  static constexpr int kStageBytes = 2 * kTensorBytes;
+  static constexpr int kStages = FP8 ? TB200_DEC_TMA_STAGES8 : TB200_DEC_TMA_STAGES16;
+  static constexpr int kBlocks = FP8 ? TB200_DEC_TMA_BLOCKS8 : TB200_DEC_TMA_BLOCKS16;
+  static constexpr int kQSlotBytes = 8 * D * 2;              // up to 8 q heads, 16-bit
+  static constexpr int kHalf = D / 2;                        // head dims merged per pass
+  static constexpr int kMergeStride = kHalf + 4;             // fp32 words per head in the merge area
+  static constexpr int kMergeBytes = kWarps * 8 * kMergeStride * 4;
+  static constexpr int kMlBytes = kWarps * 8 * 2 * 4;
+  // offsets from the 1024-byte aligned base
+  static constexpr int ring = 0;
+  static constexpr int qslots = ring + kStages * kStageBytes;
+  static constexpr int merge = qslots + kItemSlots * kQSlotBytes;
+  static constexpr int ml = merge + kMergeBytes;
+  static constexpr int scales = ml + kMlBytes;               // [kStages][2] fp32 (FP8 only)
+  static constexpr int bars = scales + 64;                   // full[kStages], empty[kStages], item_full[2], item_empty[2], math
+  static constexpr int misc = bars + 8 * (2 * kStages + 2 * kItemSlots + 1);  // 16 ints
+  static constexpr int plan = misc + 64;                     // s_prefix [batch + 1], s_lens [batch]
+  static_assert(kRowBytes == 128 || kRowBytes == 256, "token rows must be one or two 128-byte panels");
+  static_assert(kStages * 2 * 4 <= 64, "scale slots");
+};
+
+template <int D, bool FP8>
+size_t tma_smem_bytes(int batch) {
+  return size_t(TmaCfg<D, FP8>::plan) + size_t(2 * batch + 1) * 4 + 1024;   // + alignment slack
+}
+
+// T : MMA element type (bf16 or f16; f16 for FP8 caches, q is converted).  TO : output type.
+template <int D, bool FP8, typename T, typename TO>
+__global__ void __launch_bounds__(kTmaThreads, TmaCfg<D, FP8>::kBlocks)
+gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                      DecodeParams p) {
+  using C = TmaCfg<D, FP8>;
+  constexpr int NT = 1;
+  constexpr int kKSteps = D / 16;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::bars);
+  auto bar_full = [&](int s) { return smem_u32(bars + s); };
+  auto bar_empty = [&](int s) { return smem_u32(bars + C::kStages + s); };
+  auto bar_item_full = [&](int s) { return smem_u32(bars + 2 * C::kStages + s); };
+  auto bar_item_empty = [&](int s) { return smem_u32(bars + 2 * C::kStages + kItemSlots + s); };
+  const uint32_t bar_math = smem_u32(bars + 2 * C::kStages + 2 * kItemSlots);
+  int* s_misc = reinterpret_cast<int*>(smem + C::misc);    // [0] abort, [1] ticket, [2..5] warp sums, [6],[7] item ids
+  volatile int* s_abort = s_misc;
+  int* s_item = s_misc + 6;
+  int* s_prefix = reinterpret_cast<int*>(smem + C::plan);  // [batch + 1]
+  int* s_lens = s_prefix + p.batch + 1;                    // [batch]
+  float* s_scales = reinterpret_cast<float*>(smem + C::scales);
+  int* status = p.counters + 2;
+
+  // id of this CTA's first work item: requested now, its round trip runs under the plan
+  int next_id = 0;
+  if (tid == kThreads) next_id = atomicAdd(&p.counters[0], 1);
+  if (tid == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_empty(s), kWarps);
+    }
+    for (int s = 0; s < kItemSlots; ++s) {
+      mbar_init(bar_item_full(s), 1);
+      mbar_init(bar_item_empty(s), kWarps);
+    }
+    mbar_init(bar_math, kWarps);
+    s_misc[0] = 0;
+    mbar_fence_init();
+  }
+  const int step = p.world > 1 ? *reinterpret_cast<volatile int*>(p.step_counter) + 1 : 0;
+  const int parity = step & 1;
+  const int lanes_per_run = p.heads_kv * p.n_hb;
+
+  if (warp < kWarps)
+    decode_plan<FP8>(p, tid, reinterpret_cast<int*>(smem + C::merge), s_prefix, s_lens, s_misc + 2,
+                     [] { named_barrier(kMathBarrier, kThreads); });
+  __syncthreads();
+  const int total_items = s_prefix[p.batch] * lanes_per_run;
+  const long long limit = p.wait_cycles;
+
+  if (warp == kWarps) {
+    // ================= producer: item ids, q rows, K/V tiles =================
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+    }
+    int stage = 0;
+    uint32_t stage_par = 0;
+    bool alive = true;
+    for (int round = 0; alive; ++round) {
+      const int slot = round & 1;
+      const uint32_t slot_par = (round >> 1) & 1;
+      const int item = __shfl_sync(0xffffffffu, next_id, 0);
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait_bounded(bar_item_empty(slot), slot_par ^ 1, s_abort, status, 601, limit) ? 1 : 0;
+      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+      if (item >= total_items) {
+        if (lane == 0) {
+          s_item[slot] = -1;
+          mbar_arrive(bar_item_full(slot));
+        }
+        break;
+      }
+      if (lane == 0) next_id = atomicAdd(&p.counters[0], 1);   // id of the following item, in flight from now
+      const ItemDesc d = decode_item(p, item, s_prefix, s_lens);
+      const int head0 = d.hk * p.group + d.hbi * p.hb;
+      const int n_heads = min(p.hb, p.group - d.hbi * p.hb);
+      if (lane == 0) {
+        s_item[slot] = item;
+        const uint32_t q_bytes = uint32_t(n_heads) * D * 2;
+        mbar_expect_tx(bar_item_full(slot), q_bytes);
+        bulk_load(sbase + C::qslots + slot * C::kQSlotBytes,
+                  reinterpret_cast<const unsigned char*>(p.q) + (size_t(d.b) * p.heads + head0) * D * 2, q_bytes,
+                  bar_item_full(slot));
+      }
+      const int32_t* bt_row = p.bt ? p.bt + size_t(d.b) * p.bt_stride : nullptr;
+      const int coord_b = p.bt ? 0 : d.b;
+      for (int t0 = d.tile0; t0 < d.tile1 && alive; t0 += 32) {
+        // 32 tiles per round: lane l reads the table entry (and the scales) of tile t0 + l
+        const int t = t0 + lane;
+        int tok = 0;
+        float ks = 0.f, vs = 0.f;
+        if (t < d.tile1) {
+          tok = t * kTile;
+          if (bt_row) {
+            const int pg = bt_row[tok / p.page_size];
+            tok = pg * p.page_size + tok % p.page_size;
+            if constexpr (FP8) {
+              ks = p.k_scale[size_t(pg) * p.heads_kv + d.hk];
+              vs = p.v_scale[size_t(pg) * p.heads_kv + d.hk];
+            }
+          }
+        }
+        const int n = min(32, d.tile1 - t0);
+        for (int i = 0; i < n; ++i) {
+          const int tok_i = __shfl_sync(0xffffffffu, tok, i);
+          const float ks_i = FP8 ? __shfl_sync(0xffffffffu, ks, i) : 0.f;
+          const float vs_i = FP8 ? __shfl_sync(0xffffffffu, vs, i) : 0.f;
+          if (lane == 0) {
+            if (mbar_wait_bounded(bar_empty(stage), stage_par ^ 1, s_abort, status, 601, limit)) {
+              if constexpr (FP8) {
+                s_scales[stage * 2] = ks_i;
+                s_scales[stage * 2 + 1] = vs_i;
+              }
+              mbar_expect_tx(bar_full(stage), C::kStageBytes);
+              const uint32_t dst = sbase + C::ring + stage * C::kStageBytes;
+#pragma unroll
+              for (int pn = 0; pn < C::kPanels; ++pn)
+                tma_load_4d(dst + pn * C::kPanelBytes, &map_k, bar_full(stage), pn * C::kPanelElems, d.hk, tok_i, coord_b);
+#pragma unroll
+              for (int pn = 0; pn < C::kPanels; ++pn)
+                tma_load_4d(dst + C::kTensorBytes + pn * C::kPanelBytes, &map_v, bar_full(stage), pn * C::kPanelElems,
+                            d.hk, tok_i, coord_b);
+            } else {
+              ok = 0;
+            }
+          }
+          if (!__shfl_sync(0xffffffffu, ok, 0)) { alive = false; break; }
+          if (++stage == C::kStages) { stage = 0; stage_par ^= 1; }
+        }
+      }
+    }
+  } else {
+    // ================= math warps =================
+    const int g8 = lane >> 2;  // "groupID" of the mma fragment layouts
+    const int t4 = lane & 3;   // "threadID_in_group"
+    const float qk_scale = p.softcap > 0.f ? p.sm_scale : p.sm_scale * kLog2e;
+    const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+
+    // Per-lane ldmatrix offsets inside a swizzled tile.  Row r of a panel is 128 bytes at r * 128 and
+    // its 16-byte chunk c sits at (c ^ (r & 7)) * 16.  A k-step (16 elements of a 16-bit cache, 32 of
+    // an FP8 one) is two chunks, 2*step and 2*step + 1; the lane's chunk parity and row are fixed, so
+    // the four possible values of (2*step) & 7 give four offsets, and the panel is an immediate.
+    //   K (both paths) and FP8 V: row = (l&7) + ((l>>3)&1)*8, chunk parity = l>>4
+    //   16-bit V (trans):         row = (l&7) + ((l>>4)&1)*8, chunk parity = (l>>3)&1
+    uint32_t ka[4], va[4];
+    {
+      const int x = lane & 7;
+      const int row_a = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int col_a = lane >> 4;
+      const int row_v = FP8 ? row_a : warp * 16 + (lane & 7) + ((lane >> 4) & 1) * 8;
+      const int col_v = FP8 ? col_a : (lane >> 3) & 1;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        ka[i] = row_a * 128 + ((i * 32) ^ ((col_a ^ x) << 4));
+        va[i] = C::kTensorBytes + row_v * 128 + ((i * 32) ^ ((col_v ^ x) << 4));
+      }
+    }
+
+    // Barrier of the four math warps with a bounded wait (an mbarrier, one arrival per warp): a warp
+    // that has given up simply never arrives, and the others give up too instead of waiting forever
+    // at a hardware barrier.
+    uint32_t math_par = 0;
+    bool alive = true;
+    auto math_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_math);
+      const bool ok = mbar_wait_bounded(bar_math, math_par, s_abort, status, 603, limit);
+      math_par ^= 1;
+      if (!ok) alive = false;
+      return ok;
+    };
+
+    // ---- split-KV merge, deferred (as in gqa_decode.cu) ---------------------------------------
+    struct Pending {
+      bool valid;
+      int* ticket;
+      int n_runs, first_item, b, head0, n_heads;
+    } pend{false, nullptr, 0, 0, 0, 0, 0};
+    auto resolve_pending = [&]() {
+      if (!pend.valid) return;           // uniform across the math warps
+      pend.valid = false;
+      if (tid == 0) {
+        int t;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(t) : "l"(pend.ticket) : "memory");
+        s_misc[1] = t;
+      }
+      if (!math_sync()) return;
+      const bool last = s_misc[1] == pend.n_runs - 1;
+      if (!math_sync()) return;   // s_misc[1] may be rewritten by the next item's ticket
+      if (!last) return;
+      constexpr int kOut = (8 * NT * D) / kThreads;
+      float acc[kOut], L[kOut], M[kOut];
+#pragma unroll
+      for (int k = 0; k < kOut; ++k) { acc[k] = 0.f; L[k] = 0.f; M[k] = kNegFloor; }
+      const int n_out = pend.n_heads * D;
+#pragma unroll 2
+      for (int r = 0; r < pend.n_runs; ++r) {
+        const size_t it2 = size_t(pend.first_item) + size_t(r) * lanes_per_run;
+        const float* ml = p.part_ml + it2 * p.hb * 2;
+        const float* po2 = p.part_o + it2 * p.hb * D;
+        float mt[kOut], lt[kOut], ot[kOut];
+#pragma unroll
+        for (int k = 0; k < kOut; ++k) {
+          const int idx = tid + k * kThreads;
+          const bool ok = idx < n_out;
+          const int hn = ok ? idx / D : 0;
+          mt[k] = ok ? __ldcg(ml + hn * 2) : kNegFloor;
+          lt[k] = ok ? __ldcg(ml + hn * 2 + 1) : 0.f;
+          ot[k] = ok ? __ldcg(po2 + idx) : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < kOut; ++k) {
+          const float mn = fmaxf(M[k], mt[k]);
+          const float ea = fast_exp2(M[k] - mn), eb = fast_exp2(mt[k] - mn);
+          acc[k] = acc[k] * ea + ot[k] * eb;
+          L[k] = L[k] * ea + lt[k] * eb;
+          M[k] = mn;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < kOut; ++k) {
+        const int idx = tid + k * kThreads;
+        if (idx < n_out) {
+          const int hn = idx / D, d = idx - hn * D;
+          const size_t orow = size_t(pend.b) * p.heads + pend.head0 + hn;
+          emit_out<TO>(p, parity, orow, d, D, L[k] > 0.f ? acc[k] / L[k] : 0.f);
+          if (d == 0) emit_lse(p, parity, orow, D, L[k] > 0.f ? M[k] + log2f(L[k]) : -INFINITY);
+        }
+      }
+      if (tid == 0) *pend.ticket = 0;  // leave the workspace zeroed for the next launch
+    };
+
+    int stage = 0;
+    uint32_t stage_par = 0;
+    for (int round = 0; alive; ++round) {
+      const int slot = round & 1;
+      if (!mbar_wait_bounded(bar_item_full(slot), (round >> 1) & 1, s_abort, status, 602, limit)) break;
+      const int item = s_item[slot];
+      if (item < 0) break;
+      const ItemDesc d = decode_item(p, item, s_prefix, s_lens);
+      const int b = d.b, hk = d.hk, len = d.len;
+      const int n_tiles = d.tile1 - d.tile0;
+      const int head0 = hk * p.group + d.hbi * p.hb;
+      const int n_heads = min(p.hb, p.group - d.hbi * p.hb);
+
+      // ---- q fragments (B operand of S^T = K Q^T) from the item slot ----------------------------
+      uint32_t qf[kKSteps][2];
+      {
+        const unsigned char* qs = smem + C::qslots + slot * C::kQSlotBytes;
+        const bool ok = g8 < n_heads;
+#pragma unroll
+        for (int ks = 0; ks < kKSteps; ++ks) {
+          if constexpr (!FP8) {
+            const uint32_t* qp = reinterpret_cast<const uint32_t*>(qs + (size_t(g8) * D + ks * 16 + t4 * 2) * 2);
+            qf[ks][0] = ok ? qp[0] : 0u;
+            qf[ks][1] = ok ? qp[4] : 0u;
+          } else {
+            // k index 2t,2t+1 <-> d = 16ks+4t+{0,1}; k index 2t+8,2t+9 <-> d = 16ks+4t+{2,3}
+            float f[4] = {0.f, 0.f, 0.f, 0.f};
+            if (ok) {
+              const uint2 w = *reinterpret_cast<const uint2*>(qs + (size_t(g8) * D + ks * 16 + t4 * 4) * 2);
+              if (p.q_is_bf16) {
+                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&w.x);
+                const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&w.y);
+                f[0] = __low2float(a); f[1] = __high2float(a); f[2] = __low2float(c); f[3] = __high2float(c);
+              } else {
+                const __half2 a = *reinterpret_cast<const __half2*>(&w.x);
+                const __half2 c = *reinterpret_cast<const __half2*>(&w.y);
+                f[0] = __low2float(a); f[1] = __high2float(a); f[2] = __low2float(c); f[3] = __high2float(c);
+              }
+            }
+            qf[ks][0] = pack2<__half>(f[0], f[1]);
+            qf[ks][1] = pack2<__half>(f[2], f[3]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_item_empty(slot));   // id and q rows are in registers
+      resolve_pending();   // ticket / merge of the previous item, while the producer streams this one
+      if (!alive) break;
+
+      // ---- running state ----------------------------------------------------------------
+      float oacc[kKSteps][4];
+      float m_run[2] = {kNegFloor, kNegFloor}, l_run[2] = {0.f, 0.f};
+#pragma unroll
+      for (int mt = 0; mt < kKSteps; ++mt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oacc[mt][e] = 0.f;
+
+      for (int it = 0; it < n_tiles; ++it) {
+        if (!mbar_wait_bounded(bar_full(stage), stage_par, s_abort, status, 602, limit)) { alive = false; break; }
+        const uint32_t st_base = sbase + C::ring + stage * C::kStageBytes;
+        const int tok0 = (d.tile0 + it) * kTile;
+        const int tok_a = tok0 + warp * 16 + g8;  // token of c0/c1; c2/c3 is +8
+        if (tok0 + kTile > len) {
+          // ragged last tile of the sequence: clear this warp's V rows behind the end
+          constexpr int kChunks = C::kRowBytes / 16;
+          for (int idx = lane; idx < 16 * kChunks; idx += 32) {
+            const int row = warp * 16 + idx / kChunks, ch = idx % kChunks;
+            if (tok0 + row >= len)
+              *reinterpret_cast<uint4*>(smem + C::ring + stage * C::kStageBytes + C::kTensorBytes +
+                                        (ch >> 3) * C::kPanelBytes + row * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // before the stage goes back to the TMA
+          __syncwarp();
+        }
+
+        // ---- S^T = K Q^T  (16 tokens x 8 heads per warp) ------------------------------------
+        float sacc[4] = {0.f, 0.f, 0.f, 0.f}, sacc2[4] = {0.f, 0.f, 0.f, 0.f};
+        if constexpr (!FP8) {
+#pragma unroll
+          for (int ks = 0; ks < kKSteps; ++ks) {
+            uint32_t a[4];
+            ldmatrix_x4(a, st_base + (ks >> 2) * C::kPanelBytes + ka[ks & 3]);
+            mma_16816<T>((ks & 1) ? sacc2 : sacc, a, qf[ks]);
+          }
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < D / 32; ++jj) {
+            uint32_t r[4];
+            ldmatrix_x4(r, st_base + (jj >> 2) * C::kPanelBytes + ka[jj & 3]);
+            uint32_t a0[4] = {e4m3x2_to_f16x2_scaled<0x1404>(r[0]), e4m3x2_to_f16x2_scaled<0x1404>(r[1]),
+                              e4m3x2_to_f16x2_scaled<0x3424>(r[0]), e4m3x2_to_f16x2_scaled<0x3424>(r[1])};
+            uint32_t a1[4] = {e4m3x2_to_f16x2_scaled<0x1404>(r[2]), e4m3x2_to_f16x2_scaled<0x1404>(r[3]),
+                              e4m3x2_to_f16x2_scaled<0x3424>(r[2]), e4m3x2_to_f16x2_scaled<0x3424>(r[3])};
+            mma_16816<T>(sacc, a0, qf[2 * jj]);
+            mma_16816<T>(sacc2, a1, qf[2 * jj + 1]);
+          }
+        }
+
+        // ---- scale, softcap, mask, online softmax ----------------------------------------
+        float sc = qk_scale, vsc = 1.f;    // one K scale and one V scale per tile: the tile lies in one page
+        if constexpr (FP8) {
+          sc *= s_scales[stage * 2] * kE4m3Unit;
+          vsc = s_scales[stage * 2 + 1] * kE4m3Unit;
+        }
+        const bool ok_lo = tok_a < len, ok_hi = tok_a + 8 < len;
+        uint32_t pb[2];
+        {
+          float s0 = (sacc[0] + sacc2[0]) * sc, s1 = (sacc[1] + sacc2[1]) * sc;
+          float s2 = (sacc[2] + sacc2[2]) * sc, s3 = (sacc[3] + sacc2[3]) * sc;
+          if (p.softcap > 0.f) {
+            s0 = apply_softcap(s0, p.softcap, inv_cap) * kLog2e;
+            s1 = apply_softcap(s1, p.softcap, inv_cap) * kLog2e;
+            s2 = apply_softcap(s2, p.softcap, inv_cap) * kLog2e;
+            s3 = apply_softcap(s3, p.softcap, inv_cap) * kLog2e;
+          }
+          if (!ok_lo) { s0 = -INFINITY; s1 = -INFINITY; }
+          if (!ok_hi) { s2 = -INFINITY; s3 = -INFINITY; }
+          float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+#pragma unroll
+          for (int o = 4; o < 32; o <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+          }
+          const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+          const float al0 = fast_exp2(m_run[0] - mn0), al1 = fast_exp2(m_run[1] - mn1);
+          m_run[0] = mn0; m_run[1] = mn1;
+          const float p0 = fast_exp2(s0 - mn0), p1 = fast_exp2(s1 - mn1);
+          const float p2 = fast_exp2(s2 - mn0), p3 = fast_exp2(s3 - mn1);
+          l_run[0] = l_run[0] * al0 + p0 + p2;
+          l_run[1] = l_run[1] * al1 + p1 + p3;
+#pragma unroll
+          for (int mt = 0; mt < kKSteps; ++mt) {
+            oacc[mt][0] *= al0; oacc[mt][1] *= al1;
+            oacc[mt][2] *= al0; oacc[mt][3] *= al1;
+          }
+          // P^T as the B operand: transpose the two 8x8 (token x head) blocks across the warp
+          pb[0] = movmatrix_trans(pack2<T>(p0 * vsc, p1 * vsc));
+          pb[1] = movmatrix_trans(pack2<T>(p2 * vsc, p3 * vsc));
+        }
+
+        // ---- O^T += V^T P^T ------------------------------------------------------------------
+        if constexpr (!FP8) {
+#pragma unroll
+          for (int mt = 0; mt < kKSteps; ++mt) {
+            uint32_t a[4];
+            ldmatrix_x4_trans(a, st_base + (mt >> 2) * C::kPanelBytes + va[mt & 3]);
+            mma_16816<T>(oacc[mt], a, pb);
+          }
+        } else {
+#pragma unroll
+          for (int ii = 0; ii < D / 32; ++ii) {
+            uint32_t r[4];
+            ldmatrix_x4_trans(r, st_base + (ii >> 2) * C::kPanelBytes + va[ii & 3]);
+            // register = 2 tokens x 2 dims; bytes (0,2) are dim 2*g8, bytes (1,3) dim 2*g8+1
+            uint32_t a0[4] = {e4m3x2_to_f16x2_scaled<0x2404>(r[0]), e4m3x2_to_f16x2_scaled<0x3414>(r[0]),
+                              e4m3x2_to_f16x2_scaled<0x2404>(r[1]), e4m3x2_to_f16x2_scaled<0x3414>(r[1])};
+            uint32_t a1[4] = {e4m3x2_to_f16x2_scaled<0x2404>(r[2]), e4m3x2_to_f16x2_scaled<0x3414>(r[2]),
+                              e4m3x2_to_f16x2_scaled<0x2404>(r[3]), e4m3x2_to_f16x2_scaled<0x3414>(r[3])};
+            mma_16816<T>(oacc[2 * ii], a0, pb);
+            mma_16816<T>(oacc[2 * ii + 1], a1, pb);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty(stage));
+        if (++stage == C::kStages) { stage = 0; stage_par ^= 1; }
+      }
+      if (!alive) break;
+
+      // ---- the 4 warps meet: per-warp (m, l, O^T) -> shared memory, half of the head dims per pass ----
+      float* s_o = reinterpret_cast<float*>(smem + C::merge);   // [warp][8][kMergeStride]
+      float* s_ml = reinterpret_cast<float*>(smem + C::ml);     // [warp][8][2]
+      {
+        float l0 = l_run[0], l1 = l_run[1];
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+          l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+        }
+        if (g8 == 0) {
+          float* ml = s_ml + (warp * 8 + t4 * 2) * 2;
+          ml[0] = m_run[0]; ml[1] = l0; ml[2] = m_run[1]; ml[3] = l1;
+        }
+      }
+      const bool single = (d.n_runs == 1);
+      float* po = p.part_o + size_t(item) * p.hb * D;
+      float* pml = p.part_ml + size_t(item) * p.hb * 2;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float* so0 = s_o + (warp * 8 + t4 * 2) * C::kMergeStride;
+        float* so1 = so0 + C::kMergeStride;
+#pragma unroll
+        for (int m2 = 0; m2 < kKSteps / 2; ++m2) {
+          const int mt = half * (kKSteps / 2) + m2;
+          // fragment rows -> head dims: 16-bit path rows g8, g8+8 of the m-tile; FP8 path the
+          // ldmatrix on byte pairs interleaves them: rows g8, g8+8 are dims 2*g8, 2*g8+1
+          const int d_lo = FP8 ? m2 * 16 + 2 * g8 : m2 * 16 + g8;
+          const int d_hi = FP8 ? d_lo + 1 : d_lo + 8;
+          so0[d_lo] = oacc[mt][0]; so1[d_lo] = oacc[mt][1];
+          so0[d_hi] = oacc[mt][2]; so1[d_hi] = oacc[mt][3];
+        }
+        if (!math_sync()) break;
+        for (int idx = tid; idx < n_heads * C::kHalf; idx += kThreads) {
+          const int hn = idx / C::kHalf, dl = idx - hn * C::kHalf;
+          const int dd = half * C::kHalf + dl;
+          float mw[kWarps], M = kNegFloor;
+#pragma unroll
+          for (int w = 0; w < kWarps; ++w) {
+            mw[w] = s_ml[(w * 8 + hn) * 2];
+            M = fmaxf(M, mw[w]);
+          }
+          float acc = 0.f, L = 0.f;
+#pragma unroll
+          for (int w = 0; w < kWarps; ++w) {
+            const float e = fast_exp2(mw[w] - M);
+            acc += e * s_o[(w * 8 + hn) * C::kMergeStride + dl];
+            L += e * s_ml[(w * 8 + hn) * 2 + 1];
+          }
+          if (single) {
+            const size_t orow = size_t(b) * p.heads + head0 + hn;
+            emit_out<TO>(p, parity, orow, dd, D, L > 0.f ? acc / L : 0.f);
+            if (dd == 0) emit_lse(p, parity, orow, D, L > 0.f ? M + log2f(L) : -INFINITY);
+          } else {
+            po[hn * D + dd] = acc;
+            if (dd == 0) { pml[hn * 2] = M; pml[hn * 2 + 1] = L; }
+          }
+        }
+        if (!math_sync()) break;   // the area is rewritten by the next pass / item
+      }
+      if (!alive) break;
+      if (!single) {
+        // the ticket for this (sequence, KV head, head block) is taken at the start of the next item
+        pend.valid = true;
+        pend.ticket = p.counters + kCounterWords + (size_t(b) * p.heads_kv + hk) * p.n_hb + d.hbi;
+        pend.n_runs = d.n_runs;
+        pend.first_item = d.first_run * lanes_per_run + d.rem;
+        pend.b = b; pend.head0 = head0; pend.n_heads = n_heads;
+      }
+    }
+    if (alive) resolve_pending();
+
+    // ---- the last CTA to leave resets the scheduler counters ------------------------------
+    if (p.world > 1) __threadfence_system();   // stores to the other GPUs, out to system scope
+    if (alive) math_sync();
+    if (tid == 0) {
+      __threadfence();
+      const int done = atomicAdd(&p.counters[1], 1);
+      if (done == int(gridDim.x) - 1) {
+        p.counters[0] = 0;
+        p.counters[1] = 0;
+        __threadfence();
+        if (p.world > 1) {
+          *p.step_counter = step;
+          __threadfence_system();
+          for (int r = 0; r < p.world; ++r)
+            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer_flag[r]), "r"(step) : "memory");
+        }
+      }
+    }
+  }
+  if (*s_abort) {
+    // give copies still in flight time to land before the shared memory is released
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+// [batches, tokens, heads_kv, D] (strides in elements) -> 4-D map (d, head, token, batch) with a box of
+// one 128-byte panel x 64 tokens, 128B swizzle.  16-bit elements are described as UINT16, e4m3 as UINT8:
+// the copy never interprets them.
+struct MapKey {
+  const void* base;
+  int esize, heads_kv, dim;
+  long long tokens, batches, tok_stride, head_stride, batch_stride;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && esize == o.esize && heads_kv == o.heads_kv && dim == o.dim && tokens == o.tokens &&
+           batches == o.batches && tok_stride == o.tok_stride && head_stride == o.head_stride &&
+           batch_stride == o.batch_stride;
+  }
+};
+
+int encode_kv_map(CUtensorMap* map, const MapKey& k) {
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (!enc) return kTmaNotApplicable;
+  cuuint64_t dims[4] = {cuuint64_t(k.dim), cuuint64_t(k.heads_kv), cuuint64_t(k.tokens), cuuint64_t(k.batches)};
+  cuuint64_t strides[3] = {cuuint64_t(k.head_stride) * k.esize, cuuint64_t(k.tok_stride) * k.esize,
+                           cuuint64_t(k.batch_stride) * k.esize};
+  cuuint32_t box[4] = {cuuint32_t(128 / k.esize), 1, cuuint32_t(kTile), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, k.esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 4,
+                   const_cast<void*>(k.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return kTmaNotApplicable;   // a layout the copy engine cannot describe: the other kernel serves it
+  return TB200_OK;
+}
+
+// Encoding a map costs a driver call; decode steps reuse the same pools, so the last few are kept.
+int cached_kv_map(CUtensorMap* out, const MapKey& key) {
+  constexpr int kSlots = 8;
+  struct Slot { MapKey key; CUtensorMap map; bool used; };
+  static thread_local Slot cache[kSlots] = {};
+  static thread_local int next = 0;
+  for (int i = 0; i < kSlots; ++i)
+    if (cache[i].used && cache[i].key == key) { *out = cache[i].map; return TB200_OK; }
+  CUtensorMap m;
+  const int st = encode_kv_map(&m, key);
+  if (st != TB200_OK) return st;
+  cache[next] = Slot{key, m, true};
+  next = (next + 1) % kSlots;
+  *out = m;
+  return TB200_OK;
+}
+
+template <int D, bool FP8, typename T, typename TO>
+int launch_tma(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, cudaStream_t stream) {
+  auto kern = gqa_decode_tma_kernel<D, FP8, T, TO>;
+  const size_t smem = tma_smem_bytes<D, FP8>(p.batch);
+  static thread_local size_t configured[64] = {0};
+  static thread_local size_t sized_for[64] = {0};
+  static thread_local int resident[64] = {0};
+  int dev = 0;
+  TB200_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return kTmaNotApplicable;
+  if (smem > 227 * 1024) return kTmaNotApplicable;
+  if (configured[dev] < smem) {
+    TB200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev] = smem;
+  }
+  if (sized_for[dev] != smem) {
+    int n = 0;
+    TB200_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kTmaThreads, smem));
+    sized_for[dev] = smem;
+    resident[dev] = n < TmaCfg<D, FP8>::kBlocks ? n : TmaCfg<D, FP8>::kBlocks;
+  }
+  // with fewer resident CTAs than the kernel is tuned for (a very large batch: the plan's tables
+  // grow with it) the cp.async kernel is the better choice
+  if (resident[dev] < TmaCfg<D, FP8>::kBlocks) return kTmaNotApplicable;
+  kern<<<sm_count() * resident[dev], kTmaThreads, smem, stream>>>(mk, mv, p);
+  TB200_CUDA_CHECK(cudaGetLastError());
+  return TB200_OK;
+}
+
+template <int D, bool FP8, typename T>
+int launch_tma_o(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, int o_dtype, cudaStream_t s) {
+  switch (o_dtype) {
+    case TB200_F32: return launch_tma<D, FP8, T, float>(mk, mv, p, s);
+    case TB200_BF16: return launch_tma<D, FP8, T, __nv_bfloat16>(mk, mv, p, s);
+    case TB200_F16: return launch_tma<D, FP8, T, __half>(mk, mv, p, s);
+  }
+  return kTmaNotApplicable;
+}
+
+}  // namespace
+
+int launch_decode_tma(const DecodeParams& p, int q_dtype, int kv_dtype, int o_dtype, int dim, int nt,
+                      long long pool_tokens, cudaStream_t stream) {
+  const bool fp8 = kv_dtype == TB200_E4M3;
+  const int esize = fp8 ? 1 : 2;
+  const int row_bytes = dim * esize;
+  if (nt != 1 || (row_bytes != 128 && row_bytes != 256)) return kTmaNotApplicable;
+  if (p.bt && !p.tile_in_page) return kTmaNotApplicable;
+  if (fp8 && !p.bt) return kTmaNotApplicable;              // scales are indexed by page: needs the table
+  if (reinterpret_cast<uintptr_t>(p.q) & 15) return kTmaNotApplicable;
+  if (p.tok_stride <= 0 || p.head_stride <= 0) return kTmaNotApplicable;
+
+  MapKey key{};
+  key.esize = esize; key.heads_kv = p.heads_kv; key.dim = dim;
+  key.tok_stride = p.tok_stride; key.head_stride = p.head_stride;
+  if (p.bt) {
+    key.tokens = pool_tokens > 0 ? pool_tokens : 0x7fffffffLL;   // unknown pool size: only the table bounds the reads
+    key.batches = 1;
+    key.batch_stride = p.tok_stride;                              // unused (one batch); any multiple of 16 bytes
+  } else {
+    if (p.batch_stride <= 0 || p.batch_stride % p.tok_stride != 0) return kTmaNotApplicable;
+    key.tokens = p.batch_stride / p.tok_stride;
+    key.batches = p.batch;
+    key.batch_stride = p.batch_stride;
+  }
+  if (key.tokens > 0xffffffffLL || (unsigned long long)key.tok_stride * esize >= (1ull << 40) ||
+      (unsigned long long)key.batch_stride * esize >= (1ull << 40))
+    return kTmaNotApplicable;
+  CUtensorMap mk, mv;
+  key.base = p.k;
+  int st = cached_kv_map(&mk, key);
+  if (st != TB200_OK) return st;
+  key.base = p.v;
+  st = cached_kv_map(&mv, key);
+  if (st != TB200_OK) return st;
+
+  if (fp8) {
+    return dim == 128 ? launch_tma_o<128, true, __half>(mk, mv, p, o_dtype, stream) : kTmaNotApplicable;
+  }
+  if (q_dtype == TB200_BF16)
+    return dim == 128 ? launch_tma_o<128, false, __nv_bfloat16>(mk, mv, p, o_dtype, stream)
+                      : launch_tma_o<64, false, __nv_bfloat16>(mk, mv, p, o_dtype, stream);
+  return dim == 128 ? launch_tma_o<128, false, __half>(mk, mv, p, o_dtype, stream)
+                    : launch_tma_o<64, false, __half>(mk, mv, p, o_dtype, stream);
+}
+
+}  // namespace tb200

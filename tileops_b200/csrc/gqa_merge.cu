@@ -12,16 +12,20 @@ namespace {
 // Arrival flags of a KV-sequence sharded step (flags != null): the parts are written into this GPU's
 // memory by the other ranks' decode kernels over NVLink; rank r then stores the step number to
 // flags[r] (release, system scope).  Every block waits until all flags have reached the step this
-// GPU's own decode kernel just finished (*step_counter), at most ~0.5 s; on a timeout it records
-// code 501 in *status and leaves its output untouched.  With flags the parts of a step live in the
-// half of the buffers chosen by the step's parity (parity_stride floats apart).
+// GPU's own decode kernel just finished (*step_counter), at most wait_cycles clock ticks; on a timeout
+// it records code 501 in *status and fills its row with NaN (o) and -inf (lse), so that a step whose
+// exchange failed cannot pass for a result.  A block that finds *status already set gives up at once:
+// a launch with more rows than resident blocks waits about one limit in total, not one per wave.
+// With flags the parts of a step live in the half of the buffers chosen by the step's parity
+// (parity_stride floats apart).
 template <typename TO>
 __global__ void __launch_bounds__(128) lse_merge_kernel(const float* o_parts, const float* lse_parts,
                                                         TO* __restrict__ o, float* __restrict__ lse,
                                                         int parts, int64_t rows, int dim,
                                                         int64_t o_stride, int64_t lse_stride,
                                                         const int* flags, const int* step_counter,
-                                                        int64_t parity_stride, int* status) {
+                                                        int64_t parity_stride, int* status,
+                                                        long long wait_cycles) {
   const int64_t row = blockIdx.x;
   if (row >= rows) return;
   if (flags) {
@@ -30,20 +34,24 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const float* o_parts, co
     if (threadIdx.x == 0) {
       step = *reinterpret_cast<const volatile int*>(step_counter);
       const long long t0 = clock64();
-      int ok = 1;
+      int ok = (status && *reinterpret_cast<const volatile int*>(status) != 0) ? 0 : 1;
       for (int r = 0; r < parts && ok; ++r) {
         int seen;
         do {
           asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flags + r) : "memory");
           if (seen - step >= 0) break;
-          if (clock64() - t0 > 1000000000LL) { ok = 0; break; }
+          if (clock64() - t0 > wait_cycles) { ok = 0; break; }
         } while (true);
       }
       if (!ok && status) atomicCAS(status, 0, 501);
       s_ok = ok ? step + 1 : 0;          // step >= 1, so 0 is free to mean "gave up"
     }
     __syncthreads();
-    if (s_ok == 0) return;
+    if (s_ok == 0) {
+      for (int d = threadIdx.x; d < dim; d += blockDim.x) store_out<TO>(o + row * dim + d, __int_as_float(0x7fc00000));
+      if (lse && threadIdx.x == 0) lse[row] = -INFINITY;
+      return;
+    }
     const int64_t shift = int64_t((s_ok - 1) & 1) * parity_stride;
     o_parts += shift;
     lse_parts += shift;
@@ -78,7 +86,7 @@ using namespace tb200;
 namespace {
 int merge_impl(const float* o_parts, const float* lse_parts, void* o, float* lse, int parts, int64_t rows, int dim,
                int64_t o_part_stride, int64_t lse_part_stride, int o_dtype, const int* flags,
-               const int* step_counter, int64_t parity_stride, int* status, void* stream) {
+               const int* step_counter, int64_t parity_stride, int* status, long long wait_cycles, void* stream) {
   if (!o_parts || !lse_parts || !o) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "o_parts, lse_parts and o must be non-null");
   if (parts <= 0 || rows <= 0 || dim <= 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "parts, rows and dim must be positive");
   if (o_part_stride == 0) o_part_stride = rows * dim;
@@ -90,13 +98,13 @@ int merge_impl(const float* o_parts, const float* lse_parts, void* o, float* lse
   const unsigned grid = static_cast<unsigned>(rows);
   switch (o_dtype) {
     case TB200_F32:
-      lse_merge_kernel<float><<<grid, 128, 0, s>>>(o_parts, lse_parts, static_cast<float*>(o), lse, parts, rows, dim, o_part_stride, lse_part_stride, flags, step_counter, parity_stride, status);
+      lse_merge_kernel<float><<<grid, 128, 0, s>>>(o_parts, lse_parts, static_cast<float*>(o), lse, parts, rows, dim, o_part_stride, lse_part_stride, flags, step_counter, parity_stride, status, wait_cycles);
       break;
     case TB200_BF16:
-      lse_merge_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(o_parts, lse_parts, static_cast<__nv_bfloat16*>(o), lse, parts, rows, dim, o_part_stride, lse_part_stride, flags, step_counter, parity_stride, status);
+      lse_merge_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(o_parts, lse_parts, static_cast<__nv_bfloat16*>(o), lse, parts, rows, dim, o_part_stride, lse_part_stride, flags, step_counter, parity_stride, status, wait_cycles);
       break;
     case TB200_F16:
-      lse_merge_kernel<__half><<<grid, 128, 0, s>>>(o_parts, lse_parts, static_cast<__half*>(o), lse, parts, rows, dim, o_part_stride, lse_part_stride, flags, step_counter, parity_stride, status);
+      lse_merge_kernel<__half><<<grid, 128, 0, s>>>(o_parts, lse_parts, static_cast<__half*>(o), lse, parts, rows, dim, o_part_stride, lse_part_stride, flags, step_counter, parity_stride, status, wait_cycles);
       break;
     default:
       TB200_FAIL(TB200_ERR_UNSUPPORTED, "o_dtype %d is not F16, BF16 or F32", o_dtype);
@@ -110,14 +118,15 @@ extern "C" int tb200_gqa_lse_merge(const float* o_parts, const float* lse_parts,
                                    int parts, int64_t rows, int dim, int64_t o_part_stride,
                                    int64_t lse_part_stride, int o_dtype, void* stream) {
   return merge_impl(o_parts, lse_parts, o, lse, parts, rows, dim, o_part_stride, lse_part_stride, o_dtype, nullptr,
-                    nullptr, 0, nullptr, stream);
+                    nullptr, 0, nullptr, 0, stream);
 }
 
 extern "C" int tb200_gqa_lse_merge_wait(const float* o_parts, const float* lse_parts, void* o, float* lse,
                                         int parts, int64_t rows, int dim, int64_t o_part_stride,
                                         int64_t lse_part_stride, int64_t parity_stride, int o_dtype,
-                                        const int* flags, const int* step_counter, int* status, void* stream) {
+                                        const int* flags, const int* step_counter, int* status,
+                                        int64_t wait_cycles, void* stream) {
   if (!flags || !step_counter) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "flags and step_counter must be non-null");
   return merge_impl(o_parts, lse_parts, o, lse, parts, rows, dim, o_part_stride, lse_part_stride, o_dtype, flags,
-                    step_counter, parity_stride, status, stream);
+                    step_counter, parity_stride, status, wait_cycles > 0 ? wait_cycles : 1000000000LL, stream);
 }

@@ -60,6 +60,7 @@ def gqa_decode(
     return_lse: bool = False,
     out: Optional[torch.Tensor] = None,
     lse_out: Optional[torch.Tensor] = None,
+    config: Optional[dict] = None,
 ) -> "torch.Tensor | Tuple[torch.Tensor, torch.Tensor]":
     """Single-token GQA decode.
 
@@ -68,7 +69,7 @@ def gqa_decode(
     all sequences.  An e4m3 cache needs ``k_scale``/``v_scale`` ``[N/page,Hkv]`` fp32.
     Returns o ``[B,H,D]`` (and the log2-domain LSE ``[B,H]`` fp32 when asked).  ``out`` /
     ``lse_out`` are optional preallocated contiguous destinations (e.g. slices of a
-    communication buffer).
+    communication buffer).  ``config`` selects a kernel variant (see ``_native.decode_flags``).
     """
     _require_cuda(q=q, k=k, v=v, block_table=block_table, k_scale=k_scale, v_scale=v_scale)
     if q.dim() != 3:
@@ -141,7 +142,7 @@ def gqa_decode(
             N.dtype_code(q.dtype), N.dtype_code(k.dtype), N.dtype_code(out_dtype),
             B, H, Hkv, D, int(page_size),
             tok_stride, head_stride, batch_stride,
-            scale, float(softcap or 0.0),
+            scale, float(softcap or 0.0), k.shape[0] if paged else 0, N.decode_flags(config),
             ws.data_ptr(), ws.numel(), N.current_stream(q.device))
     N.check(st, "tb200_gqa_decode")
     return (o, lse) if return_lse else o

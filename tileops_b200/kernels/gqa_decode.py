@@ -69,7 +69,15 @@ class _DecodeBase(Kernel):
 
     @property
     def default_config(self) -> dict:
-        return {"block_N": _TILE, "threads": 128, "num_stages": 3, "num_split": "device-balanced"}
+        """``block_N`` / ``threads`` / ``num_stages`` / ``num_split`` describe the compiled kernel (the
+        reference's tunables, ``gqa_decode.py:520-553``; fixed here).  The entries a caller may set through
+        ``config=`` select a compiled variant and travel to the library as flags, never as environment
+        variables: ``wide`` (True / False / None = the library's choice: 3 CTAs per SM with a 2-stage ring
+        for long 16-bit contexts), ``tma`` (False keeps the cp.async kernel where the TMA-producer kernel
+        would apply), ``fp8_mma`` (e4m3 tensor-core path of an FP8 cache), ``chunk_tiles`` (fixed split-KV
+        run length in 64-token tiles; 0 = the device-side cost model)."""
+        return {"block_N": _TILE, "threads": 128, "num_stages": 3, "num_split": "device-balanced",
+                "wide": None, "tma": True, "fp8_mma": False, "chunk_tiles": 0}
 
 
 class GQADecodeSm100Kernel(_DecodeBase):
@@ -85,7 +93,7 @@ class GQADecodeSm100Kernel(_DecodeBase):
                 return_lse: bool = False):
         self._require_cuda(Q=Q, K=K, V=V)
         return F.gqa_decode(Q, K, V, real_seqlen_kv=int(real_seqlen_kv), sm_scale=self.sm_scale,
-                            softcap=self.softcap, return_lse=return_lse)
+                            softcap=self.softcap, return_lse=return_lse, config=self.config)
 
 
 class GQADecodePagedSm100Kernel(_DecodeBase):
@@ -108,7 +116,7 @@ class GQADecodePagedSm100Kernel(_DecodeBase):
         self._require_cuda(Q=Q, K=K, V=V, real_seqlen_kv=real_seqlen_kv, block_table=block_table)
         return F.gqa_decode(Q, K, V, real_seqlen_kv=real_seqlen_kv, block_table=block_table,
                             page_size=self.page_size, sm_scale=self.sm_scale, softcap=self.softcap,
-                            return_lse=return_lse, out_dtype=out_dtype)
+                            return_lse=return_lse, out_dtype=out_dtype, config=self.config)
 
 
 class GQADecodePagedFp8Sm100Kernel(GQADecodePagedSm100Kernel):
@@ -126,4 +134,4 @@ class GQADecodePagedFp8Sm100Kernel(GQADecodePagedSm100Kernel):
         return F.gqa_decode(Q, K, V, real_seqlen_kv=real_seqlen_kv, block_table=block_table,
                             page_size=self.page_size, k_scale=k_scale, v_scale=v_scale,
                             sm_scale=self.sm_scale, softcap=self.softcap, return_lse=return_lse,
-                            out_dtype=out_dtype)
+                            out_dtype=out_dtype, config=self.config)

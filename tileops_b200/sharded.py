@@ -59,6 +59,8 @@ class KVSequenceShardedPagedDecode:
         self._merge = merge_fn or self._cuda_merge
         self._buffers: dict = {}
         self._peer = None
+        #: limit of the merge kernel's wait for the other ranks' flags, in GPU clock ticks (0: about 0.5 s)
+        self.peer_wait_cycles = 0
 
     # default compute: the CUDA kernels
     def _cuda_decode(self, q, k, v, lens, bt, out, lse_out):
@@ -134,9 +136,16 @@ class KVSequenceShardedPagedDecode:
         torch.cuda.synchronize(device)
         dist.barrier(group=group)      # every buffer is zeroed before any rank stores into it
 
-    def peer_status(self) -> int:
-        """0, or 501 if a merge gave up waiting for another rank's flag (synchronises)."""
-        return int(self._peer["status"].item()) if getattr(self, "_peer", None) else 0
+    def peer_status(self, reset: bool = False) -> int:
+        """0, or 501 if a merge gave up waiting for another rank's flag (synchronises).  The rows such a
+        merge could not produce are NaN.  The word is sticky: every later merge gives up at once until it
+        is cleared (``reset=True``), so a failed exchange cannot pass unnoticed."""
+        if not getattr(self, "_peer", None):
+            return 0
+        code = int(self._peer["status"].item())
+        if reset and code:
+            self._peer["status"].zero_()
+        return code
 
     def _forward_peer(self, q, k, v, lens, bt) -> torch.Tensor:
         import ctypes
@@ -155,14 +164,15 @@ class KVSequenceShardedPagedDecode:
             st = lib.tb200_gqa_decode_sharded(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), lens.data_ptr(), 0, bt.data_ptr(), bt.shape[1], None, None,
                 N.dtype_code(q.dtype), N.dtype_code(k.dtype), B, H, Hkv, D, self.page_size, k.stride(0), k.stride(1), 0,
-                float(self.sm_scale), float(self.softcap), ctypes.addressof(P["buffers"]), ctypes.addressof(P["flags"]),
+                float(self.sm_scale), float(self.softcap), k.shape[0], 0, ctypes.addressof(P["buffers"]),
+                ctypes.addressof(P["flags"]),
                 P["step"].data_ptr(), self.world, self.rank, ws.data_ptr(), ws.numel(), stream)
             N.check(st, "tb200_gqa_decode_sharded")
             base = P["buf"].data_ptr()
             st = lib.tb200_gqa_lse_merge_wait(
                 base, base + B * H * D * 4, out.data_ptr(), None, self.world, B * H, D, P["slot"], P["slot"],
                 self.world * P["slot"], N.dtype_code(q.dtype), P["own_flags"], P["step"].data_ptr(),
-                P["status"].data_ptr(), stream)
+                P["status"].data_ptr(), int(self.peer_wait_cycles), stream)
             N.check(st, "tb200_gqa_lse_merge_wait")
         return out
 
