@@ -1,23 +1,25 @@
 #!/usr/bin/env python
 """Benchmark of the GQA attention-forward hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-others] [--no-manifest]
 
 One "step" is one pass of the hot path over one batch of seeded synthetic input.  The headline
-workload is BASELINE config 3 (paged bf16 decode, batch 64, 32/8 heads, D=128, context uniform
-in [512, 8192], page 64, random-permutation block table); the metric is achieved HBM GB/s over
-the algorithmic bytes (live K/V + q + o + block-table entries + lengths, each once).  The other
-BASELINE configurations are timed too and reported under ``"others"`` in the same JSON line.
+workload is the paged bf16 decode of a Llama-3-8B attention layer (batch 64, 32 q heads / 8 KV heads,
+head dim 128, context uniform in [512, 8192], 64-token pages, random-permutation block table); the
+metric is achieved HBM GB/s over the algorithmic bytes (live K/V + q + o + block-table entries +
+lengths, each once).  The FP8-cache decode, the long-context KV-sharded decode, the causal prefill and
+a paged-prefill chunk are timed with the same protocol and reported under ``"others"``, each with its
+own clock record, per-launch medians, roofline block and a one-shot comparison with the CPU oracle.
 
 For N > 1 (launched by ``python -m torch.distributed.run``, one rank per GPU) every rank decodes
-its own batch of the same shape (weak scaling; the path partitions by sequence with no
-data-path collective); ``value`` is all ranks' bytes over the slowest rank's time.  The
-KV-sequence-sharded long-context decode (config 5), which does have one exchange step, is
-reported under ``"others"``.
+its own batch of the same shape (weak scaling; the path partitions by sequence with no data-path
+collective); ``value`` is all ranks' bytes over the slowest rank's time.  The KV-sequence-sharded
+long-context decode, which does have one exchange step, is reported under ``"others"`` together with a
+bit-identity check of its fused exchange against the NCCL all-gather path.
 
 ``--impl reference`` times the reference's CPU implementation of the same workload (its torch
-reference program, restated in ``oracle/`` because the reference tree is not on the GPU box)
-on the host cores, on a bounded sample.
+reference program, restated in ``oracle/`` because the reference tree does not travel with this
+repository) on the host cores, on a bounded sample.
 """
 
 from __future__ import annotations
@@ -41,11 +43,12 @@ METRIC = "paged_decode_hbm_gbs"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
+PER_LAUNCH_SAMPLES = 100
 
-# DRAM traffic per launch relative to the algorithmic bytes, from the ncu capture summarised in
-# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum of gqa_decode_kernel on a scaled-down
-# config-3 case; traffic grows in proportion to the live tokens).
-NCU_TRAFFIC_RATIO = {"cfg3": 1.026}
+# DRAM traffic per launch relative to the algorithmic bytes (dram__bytes_read.sum + dram__bytes_write.sum
+# of one ncu capture of the decode kernel on a quarter-size case; traffic grows in proportion to the live
+# tokens, so the ratio carries over to the full launch).
+NCU_TRAFFIC_RATIO = {"paged_decode_bf16": 1.026}
 
 
 def measured_peaks():
@@ -117,18 +120,18 @@ def dist_env():
     return rank, world, local
 
 
-def time_steps(fn, steps: int, warmup: int, world: int, sampler=None):
+def time_steps(fn, steps: int, warmup: int, world: int, sampler=None, soak_s: float = 1.5):
     """W untimed steps, then exactly K steps between a barrier+synchronize on both sides, timed
     with CUDA events on the launching (current) stream.  Returns this rank's elapsed ms.
 
-    With a clock sampler the untimed part is stretched to about 1.5 s of the same step, the
+    With a clock sampler the untimed part is stretched to ``soak_s`` seconds of the same step, the
     sampler running from its start to the end of the timed region: the timed region itself
     lasts only milliseconds, far less than one nvidia-smi sampling period, so the samples
     describe the clocks the GPU holds under this load when the timed steps run."""
     import torch.distributed as dist
     if sampler:
         sampler.start()
-        t_end = time.perf_counter() + 1.5
+        t_end = time.perf_counter() + soak_s
         while time.perf_counter() < t_end:
             for _ in range(20):
                 fn()
@@ -151,6 +154,35 @@ def time_steps(fn, steps: int, warmup: int, world: int, sampler=None):
     return e0.elapsed_time(e1)
 
 
+def per_launch_us(fn, samples: int = PER_LAUNCH_SAMPLES):
+    """``samples`` steps, each between its own pair of CUDA events on the launching stream (all queued,
+    one synchronize at the end): (median, min) microseconds of one step."""
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(samples)]
+    for a, b in evs:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    us = [a.elapsed_time(b) * 1e3 for a, b in evs]
+    return statistics.median(us), min(us)
+
+
+def measure(fn, steps, warmup, world, device, local_index, sample_clocks=True):
+    """The timing protocol of every entry: clock sampler over a soak and the timed region, K steps timed as
+    one region (max over ranks), then per-launch medians over 100 more steps."""
+    sampler = ClockSampler(local_index) if sample_clocks else None
+    ms_local = time_steps(fn, steps, warmup, world, sampler, soak_s=1.5 if sample_clocks else 0.0)
+    med, mn = per_launch_us(fn)
+    clocks = sampler.stop() if sampler else None
+    ms = max_over_ranks(ms_local, world, device) / steps
+    out = {"ms_per_step": ms, "ms_per_step_local": ms_local / steps, "per_launch_us_median": med,
+           "per_launch_us_min": mn, "per_launch_samples": PER_LAUNCH_SAMPLES, "clocks": clocks}
+    if clocks and clocks.get("sm_mhz"):
+        # time x clock: comparable between boxes that settle at different SM clocks under the power cap
+        out["us_x_sm_mhz"] = med * clocks["sm_mhz"]
+    return out
+
+
 def max_over_ranks(ms: float, world: int, device) -> float:
     if world == 1:
         return ms
@@ -169,71 +201,99 @@ def sum_over_ranks(x: float, world: int, device) -> float:
     return float(t.item())
 
 
+def hbm_roofline(kernel, bytes_per_launch, us_per_launch, peaks, traffic_ratio=None):
+    achieved = bytes_per_launch / (us_per_launch * 1e-6) / 1e9
+    return {"bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": achieved / peaks["hbm_gbs"], "peak_source": f"of {peaks['source']}",
+            "frac_of_nominal_8000": achieved / 8000.0, "algorithmic_bytes_per_launch": bytes_per_launch,
+            "traffic": None if traffic_ratio is None else traffic_ratio * bytes_per_launch}
+
+
+def tensor_roofline(kernel, flops_per_launch, us_per_launch, peaks):
+    achieved = flops_per_launch / (us_per_launch * 1e-6) / 1e12
+    return {"bound": "tensor", "kernel": kernel, "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+            "frac": achieved / peaks["bf16_tflops"], "peak_source": f"of {peaks['source']} (cuBLAS bf16 burst)",
+            "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"], "frac_of_nominal_2250": achieved / 2250.0,
+            "algorithmic_flops_per_launch": flops_per_launch, "traffic": None}
+
+
 # ------------------------------------------------------------------------------------------
 # workloads
 # ------------------------------------------------------------------------------------------
 
-def build_paged(cfg: int, rank: int, device):
+def build_paged(kind: str, rank: int, device):
     from tileops_b200 import workloads as W
     from tileops_b200.ops import (GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp,
                                   GroupedQueryAttentionDecodePagedWithKVCacheFwdOp)
     # every rank has its own batch (own data and block table from its own seed stream) with the SAME
     # context lengths, so that the work per GPU is identical at every N (weak scaling)
-    if cfg == 3:
+    if kind == "bf16":
         inp = W.make_paged_decode(3 + 10 * rank, 64, 32, 8, 128, 64, lens=W.draw_lengths(3, 64, (512, 8192)),
                                   device=device)
-    elif cfg == 4:
+    elif kind == "fp8":
         inp = W.make_paged_decode(4 + 10 * rank, 128, 64, 8, 128, 64, lens=[4096] * 128, fp8_cache=True,
                                   device=device)
     else:
-        raise ValueError(cfg)
+        raise ValueError(kind)
     B, H, D = inp.q.shape
-    cls = GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp if cfg == 4 else GroupedQueryAttentionDecodePagedWithKVCacheFwdOp
+    cls = GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp if kind == "fp8" else GroupedQueryAttentionDecodePagedWithKVCacheFwdOp
     op = cls(B, H, inp.k.shape[1], inp.k.shape[0], D, inp.page_size)
-    if cfg == 4:
+    if kind == "fp8":
         args = (inp.q, inp.k, inp.v, inp.k_scale, inp.v_scale, inp.real_seqlen_kv, inp.block_table)
     else:
         args = (inp.q, inp.k, inp.v, inp.real_seqlen_kv, inp.block_table)
     return inp, op, args
 
 
-def run_paged_device(cfg, rank, world, device, steps, warmup, sampler=None):
-    inp, op, args = build_paged(cfg, rank, device)
-    ms = time_steps(lambda: op(*args), steps, warmup, world, sampler)
-    return inp, op, args, ms
+def paged_parity_spot(inp, out, b: int = 0) -> float:
+    """Max abs error of sequence ``b`` of a paged decode result against the CPU oracle."""
+    from oracle import gqa_oracle as O
+    sl = slice(b, b + 1)
+    if inp.k_scale is not None:
+        ref = O.paged_decode_fp8_ref(inp.q[sl].cpu(), inp.k.cpu(), inp.v.cpu(), inp.k_scale.cpu(), inp.v_scale.cpu(),
+                                     inp.real_seqlen_kv[sl].cpu(), inp.block_table[sl].cpu(), inp.page_size)
+    else:
+        ref = O.paged_decode_ref(inp.q[sl].cpu(), inp.k.cpu(), inp.v.cpu(), inp.real_seqlen_kv[sl].cpu(),
+                                 inp.block_table[sl].cpu(), inp.page_size)
+    return float((out[sl].float().cpu() - ref.float()).abs().max())
 
 
-def run_e2e_paged(op, args, steps, warmup, world, device):
-    """Same op, inputs in pinned HOST memory: every step copies them to the device, runs the op
-    and reads the result back."""
-    host = [a.cpu().pin_memory() for a in args]
-    dev = [torch.empty_like(a) for a in args]
+def run_e2e_paged(op, args, steps, warmup, world, device, resident: bool):
+    """Same op through the operator call with HOST buffers: every step copies its inputs from pinned host
+    memory to the device, runs the op and reads the result back.  ``resident=False`` copies everything
+    (the KV pool included: what a caller holding its cache in host memory pays); ``resident=True`` is the
+    serving step, cache resident on the device, only q, lengths and block table copied in."""
+    moved = [i for i, a in enumerate(args) if not resident or a.numel() * a.element_size() < (64 << 20)]
+    host = {i: args[i].cpu().pin_memory() for i in moved}
+    dev = list(args)
+    for i in moved:
+        dev[i] = torch.empty_like(args[i])
     out_host = torch.empty(args[0].shape, dtype=args[0].dtype).pin_memory()
-    h2d = sum(a.numel() * a.element_size() for a in host)
+    h2d = sum(h.numel() * h.element_size() for h in host.values())
     d2h = out_host.numel() * out_host.element_size()
 
     def step():
-        for h, d in zip(host, dev):
-            d.copy_(h, non_blocking=True)
+        for i in moved:
+            dev[i].copy_(host[i], non_blocking=True)
         out_host.copy_(op(*dev), non_blocking=True)
 
     ms = time_steps(step, steps, warmup, world)
     return ms, h2d, d2h
 
 
-def cpu_baseline_paged(cfg: int, budget_s: float = 15.0):
+def cpu_baseline_paged(kind: str, budget_s: float = 15.0):
     """Reference CPU path (oracle port of the reference's torch ref_program) on a bounded sample
-    of the workload: whole sequences of the config, as many as fit the time budget."""
+    of the workload: whole sequences of the workload, as many repetitions as fit the time budget."""
     from oracle import gqa_oracle as O
     from tileops_b200 import workloads as W
     n_seq = 4
-    if cfg == 3:
+    if kind == "bf16":
         inp = W.make_paged_decode(3, n_seq, 32, 8, 128, 64, len_range=(512, 8192), device="cpu")
     else:
         inp = W.make_paged_decode(4, n_seq, 64, 8, 128, 64, lens=[4096] * n_seq, fp8_cache=True, device="cpu")
 
     def run():
-        if cfg == 4:
+        if kind == "fp8":
             return O.paged_decode_fp8_ref(inp.q, inp.k, inp.v, inp.k_scale, inp.v_scale, inp.real_seqlen_kv,
                                           inp.block_table, inp.page_size)
         return O.paged_decode_ref(inp.q, inp.k, inp.v, inp.real_seqlen_kv, inp.block_table, inp.page_size)
@@ -249,7 +309,7 @@ def cpu_baseline_paged(cfg: int, budget_s: float = 15.0):
     sec = (time.perf_counter() - t0) / reps
     by = inp.algorithmic_bytes()
     return {"value": by / sec / 1e9, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{n_seq} sequences of the config-{cfg} workload (sum of lengths {sum(inp.lens)} tokens), "
+            "sample": f"{n_seq} sequences of the paged {kind} decode workload (sum of lengths {sum(inp.lens)} tokens), "
                       f"{reps} repetitions, {sec * 1e3:.1f} ms each",
             "ms_per_step_sample": sec * 1e3}
 
@@ -261,9 +321,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-others", action="store_true", help="time only the headline workload")
+    ap.add_argument("--no-manifest", action="store_true", help="skip the decode workloads of the operator manifest")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="long-context sharded step: eager launches instead of a CUDA graph")
+    ap.add_argument("--nccl-exchange", action="store_true", help="long-context sharded step: NCCL all-gather instead of the fused exchange")
     ap.add_argument("--case", default=None,
-                    choices=["decode_small", "decode_fp8_small", "prefill_small", "prefill_paged"],
+                    choices=["decode_small", "decode_fp8_small", "prefill_small", "prefill_paged", "rope_small",
+                             "fp8_cache_small", "merge_small"],
                     help="run only a reduced case of one kernel (a few hundred MB on the device: the "
                          "size an ncu capture of all sections can handle) and print its timing")
     a = ap.parse_args()
@@ -271,7 +335,7 @@ def main():
         return run_small_case(a.case, a.steps, max(a.warmup, 1))
     rank, world, local = dist_env()
     warmup = max(a.warmup, 3)
-    workload = ("BASELINE config 3: GQA paged decode bf16, batch 64, 32 q heads / 8 KV heads, head_dim 128, "
+    workload = ("GQA paged decode bf16 (Llama-3-8B attention): batch 64, 32 q heads / 8 KV heads, head_dim 128, "
                 "context ~U[512,8192], page 64, random-permutation block table")
     config = {"workload": workload, "per_gpu_batch": 64, "l2_policy": "inputs (1.3 GB per step) exceed the 126 MB L2",
               "partition": "by sequence, one batch per GPU" if a.gpus > 1 else "single GPU"}
@@ -280,7 +344,7 @@ def main():
         if rank != 0:
             return
         torch.set_num_threads(os.cpu_count() or 1)
-        base = cpu_baseline_paged(3, budget_s=max(5.0, min(60.0, 2.0 * a.steps)))
+        base = cpu_baseline_paged("bf16", budget_s=max(5.0, min(60.0, 2.0 * a.steps)))
         line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": a.gpus,
                 "steps": a.steps, "warmup": warmup, "ms_per_step": base["ms_per_step_sample"],
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
@@ -298,44 +362,53 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     peaks = measured_peaks()
 
-    sampler = ClockSampler(local) if rank == 0 else None
-    inp, op, args, ms_local = run_paged_device(3, rank, world, device, a.steps, warmup, sampler)
-    clocks = sampler.stop() if sampler else None
-    ms = max_over_ranks(ms_local, world, device)
+    inp, op, args = build_paged("bf16", rank, device)
+    m = measure(lambda: op(*args), a.steps, warmup, world, device, local, sample_clocks=True)
     bytes_all = sum_over_ranks(float(inp.algorithmic_bytes()), world, device)
     tokens_all = sum_over_ranks(float(inp.q.shape[0]), world, device)
-    ms_step = ms / a.steps
+    ms_step = m["ms_per_step"]
     value = bytes_all / (ms_step * 1e-3) / 1e9
-    # roofline of the dominant kernel on this rank (one launch per step)
-    achieved = inp.algorithmic_bytes() / (ms_local / a.steps * 1e-3) / 1e9
-    ratio = NCU_TRAFFIC_RATIO.get("cfg3")
-    roofline = {"bound": "hbm", "kernel": "gqa_decode_kernel<128,bf16>", "achieved": achieved,
-                "peak": peaks["hbm_gbs"], "unit": UNIT, "frac": achieved / peaks["hbm_gbs"],
-                "peak_source": f"of {peaks['source']}", "frac_of_nominal_8000": achieved / 8000.0,
-                "algorithmic_bytes_per_launch": inp.algorithmic_bytes(),
-                "traffic": None if ratio is None else ratio * inp.algorithmic_bytes()}
+    # roofline of the dominant kernel on this rank (one launch per step), from the timed region
+    roofline = hbm_roofline("gqa_decode_tma_kernel<128, bf16>", inp.algorithmic_bytes(), m["ms_per_step_local"] * 1e3,
+                            peaks, NCU_TRAFFIC_RATIO.get("paged_decode_bf16"))
+    roofline["achieved_per_launch_median"] = inp.algorithmic_bytes() / (m["per_launch_us_median"] * 1e-6) / 1e9
+    parity_spot = paged_parity_spot(inp, op(*args)) if rank == 0 else None
 
-    e2e_ms, h2d, d2h = run_e2e_paged(op, args, max(3, min(a.steps, 10)), 3, world, device)
-    e2e_ms = max_over_ranks(e2e_ms, world, device) / max(3, min(a.steps, 10))
+    n_e2e = max(3, min(a.steps, 10))
+    e2e_ms, h2d, d2h = run_e2e_paged(op, args, n_e2e, 3, world, device, resident=False)
+    e2e_ms = max_over_ranks(e2e_ms, world, device) / n_e2e
     e2e = {"value": bytes_all / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms}
+    n_res = max(10, min(a.steps, 50))
+    res_ms, h2d_r, d2h_r = run_e2e_paged(op, args, n_res, 3, world, device, resident=True)
+    res_ms = max_over_ranks(res_ms, world, device) / n_res
+    e2e_resident = {"value": bytes_all / (res_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d_r,
+                    "d2h_bytes_per_step": d2h_r, "ms_per_step": res_ms,
+                    "what": "KV pool resident on the device; q, lengths and block table copied in, o copied out"}
 
     others = {}
     del inp, op, args
     torch.cuda.empty_cache()
     if not a.no_others:
-        others = run_others(rank, world, device, max(5, a.steps // 2), warmup, peaks)
+        others = run_others(rank, world, local, device, max(5, a.steps // 2), warmup, peaks, a)
+    if not a.no_manifest and world == 1:
+        try:
+            others["manifest_decode_workloads"] = run_manifest_decode(device, peaks)
+        except Exception as exc:  # noqa: BLE001 - report, never hide
+            others["manifest_decode_workloads"] = {"error": repr(exc)}
 
     cpu_base = None
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
-        cpu_base = cpu_baseline_paged(3)
+        cpu_base = cpu_baseline_paged("bf16")
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps,
                 "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
                 "tokens_per_s": tokens_all / (ms_step * 1e-3), "roofline": roofline, "e2e": e2e,
-                "gpu_launches": a.steps, "clocks": clocks, "others": others}
+                "e2e_resident": e2e_resident, "gpu_launches": a.steps, "clocks": m["clocks"],
+                "per_launch_us_median": m["per_launch_us_median"], "per_launch_us_min": m["per_launch_us_min"],
+                "us_x_sm_mhz": m.get("us_x_sm_mhz"), "parity_spot": parity_spot, "others": others}
         if cpu_base is not None:
             line["cpu_baseline"] = cpu_base
         print(json.dumps(line))
@@ -346,7 +419,8 @@ def main():
 
 def run_small_case(case: str, steps: int, warmup: int):
     """Reduced single-kernel cases for profiler captures: same kernels and code path as the
-    BASELINE configurations, a quarter of the batch (inputs still exceed the L2)."""
+    benchmarked workloads, a fraction of the batch (inputs still exceed the L2)."""
+    from tileops_b200 import functional as F
     from tileops_b200 import workloads as W
     from tileops_b200.ops import (GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp,
                                   GroupedQueryAttentionDecodePagedWithKVCacheFwdOp,
@@ -366,6 +440,32 @@ def run_small_case(case: str, steps: int, warmup: int):
     elif case == "prefill_paged":
         fn, work = paged_prefill_step(device, 0)
         unit = "TFLOP/s"
+    elif case == "rope_small":
+        # the rotation pass of the fused-RoPE paged prefill: 64k tokens x 32 heads x 128 dims, bf16 (read + write 1 GB)
+        T, H, D = 65536, 32, 128
+        x = torch.randn(T, H, D, device=device, dtype=torch.bfloat16)
+        pos = torch.arange(8192, device=device, dtype=torch.float32)[:, None]
+        inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device=device, dtype=torch.float32) / D))
+        cos, sin = torch.cos(pos * inv).to(x.dtype), torch.sin(pos * inv).to(x.dtype)
+        cu = torch.arange(0, T + 1, 8192, device=device, dtype=torch.int32)
+        cache = torch.zeros(cu.numel() - 1, device=device, dtype=torch.int32)
+        fn = lambda: F.rope_neox_packed(x, cos, sin, cu, cache)  # noqa: E731
+        work, unit = 2 * x.numel() * 2, "GB/s"
+    elif case == "fp8_cache_small":
+        # gather + packed prefill + append of the paged prefill over an FP8 cache (8 x 512 new over 8 x 4096 cached)
+        B, H, Hkv, D, page, Wp, old, n = 8, 32, 8, 128, 64, 72, 4096, 512
+        args = list(W.make_paged_prefill(6, [n] * B, [old] * B, H, Hkv, D, page, Wp, torch.float16, device))
+        f8 = torch.float8_e4m3fn
+        args[3], args[4] = args[3].to(f8), args[4].to(f8)
+        fn = lambda: F.gqa_prefill_paged_fp8_cache(*args[:10], args[10], page_size=page)  # noqa: E731
+        work, unit = 2 * B * old * Hkv * D + 2 * B * n * Hkv * D * 3, "GB/s"
+    elif case == "merge_small":
+        # the cross-rank merge: 8 parts of 256 rows x 128 dims
+        parts, rows, D = 8, 256, 128
+        o_parts = torch.randn(parts, rows, D, device=device)
+        lse_parts = torch.randn(parts, rows, device=device)
+        fn = lambda: F.gqa_lse_merge(o_parts, lse_parts, torch.bfloat16)  # noqa: E731
+        work, unit = parts * rows * (D + 1) * 4 + rows * D * 2, "GB/s"
     else:
         q, k, v = W.make_prefill(2, 1, 4096, 4096, 32, 8, 128, torch.bfloat16, device)
         op = GroupedQueryAttentionFwdOp(1, 32, 8, 4096, 128, is_causal=True)
@@ -378,40 +478,47 @@ def run_small_case(case: str, steps: int, warmup: int):
                       "steps": steps, "warmup": warmup}))
 
 
-def run_others(rank, world, device, steps, warmup, peaks):
-    """The remaining BASELINE configurations, each timed with the same protocol."""
+def run_others(rank, world, local, device, steps, warmup, peaks, a):
+    """The remaining workloads, each timed with the same protocol and its own clock record."""
     out = {}
-    # config 4: FP8-e4m3 KV cache, batch 128 per GPU
+    # FP8-e4m3 KV cache (Llama-3-70B attention), batch 128 per GPU
     try:
-        inp, op, args, ms = run_paged_device(4, rank, world, device, steps, warmup)
-        ms = max_over_ranks(ms, world, device) / steps
+        inp, op, args = build_paged("fp8", rank, device)
+        m = measure(lambda: op(*args), steps, warmup, world, device, local)
         by = sum_over_ranks(float(inp.algorithmic_bytes()), world, device)
-        out["cfg4_paged_decode_fp8kv"] = {
-            "gbs": by / (ms * 1e-3) / 1e9, "frac_of_peak": by / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-            "ms_per_step": ms, "tokens_per_s": 128 * world / (ms * 1e-3), "gpu_launches": steps}
+        out["paged_decode_fp8kv"] = {
+            "workload": "batch 128, 64 q heads / 8 KV heads, head_dim 128, context 4096, page 64, e4m3 cache with "
+                        "fp32 scales per (page, KV head)",
+            "gbs": by / (m["ms_per_step"] * 1e-3) / 1e9, "tokens_per_s": 128 * world / (m["ms_per_step"] * 1e-3),
+            "gpu_launches": steps,
+            "roofline": hbm_roofline("gqa_decode_tma_kernel<128, e4m3>", inp.algorithmic_bytes(),
+                                     m["ms_per_step_local"] * 1e3, peaks),
+            "parity_spot": paged_parity_spot(inp, op(*args)) if rank == 0 else None, **m}
         del inp, op, args
         torch.cuda.empty_cache()
     except Exception as exc:  # noqa: BLE001 - report, never hide
-        out["cfg4_paged_decode_fp8kv"] = {"error": repr(exc)}
-    # config 5: long context, KV-sequence sharded over the ranks, NCCL (O, LSE) exchange
+        out["paged_decode_fp8kv"] = {"error": repr(exc)}
+    # long context, KV-sequence sharded over the ranks, (O, LSE) exchange
     try:
-        out["cfg5_long_context_sharded"] = run_cfg5(rank, world, device, steps, warmup, peaks)
+        out["long_context_sharded"] = run_long_context(rank, world, local, device, steps, warmup, peaks, a)
         torch.cuda.empty_cache()
     except Exception as exc:  # noqa: BLE001
-        out["cfg5_long_context_sharded"] = {"error": repr(exc)}
-    # config 2: causal prefill
+        out["long_context_sharded"] = {"error": repr(exc)}
+    # causal prefill
     try:
-        out["cfg2_causal_prefill"] = run_cfg2(rank, world, device, steps, warmup, peaks)
+        out["causal_prefill"] = run_causal_prefill(rank, world, local, device, steps, warmup, peaks)
     except Exception as exc:  # noqa: BLE001
-        out["cfg2_causal_prefill"] = {"error": repr(exc)}
+        out["causal_prefill"] = {"error": repr(exc)}
     # the step that fills the pages decode reads: one 512-token chunk per request over a 4k prefix
     try:
         fn, flops = paged_prefill_step(device, rank)
-        ms = max_over_ranks(time_steps(fn, steps, warmup, world), world, device) / steps
-        tf = flops * world / (ms * 1e-3) / 1e12
+        m = measure(fn, steps, warmup, world, device, local)
+        tf = flops * world / (m["ms_per_step"] * 1e-3) / 1e12
         out["paged_prefill_llama8b_chunk512"] = {
-            "tflops": tf, "frac_of_peak_burst": tf / world / peaks["bf16_tflops"], "ms_per_step": ms,
-            "tokens_per_s": 8 * 512 * world / (ms * 1e-3), "gpu_launches": steps}
+            "workload": "manifest llama-8b-prefill-paged-b8-prefix4k-chunk512-p64 (fp16)",
+            "tflops": tf, "tokens_per_s": 8 * 512 * world / (m["ms_per_step"] * 1e-3), "gpu_launches": steps,
+            "roofline": tensor_roofline("gqa_prefill_kernel<f16, 128, paged>", flops, m["ms_per_step_local"] * 1e3, peaks),
+            **m}
     except Exception as exc:  # noqa: BLE001
         out["paged_prefill_llama8b_chunk512"] = {"error": repr(exc)}
     return out
@@ -433,21 +540,23 @@ def paged_prefill_step(device, rank):
     return (lambda: kern(*args)), flops
 
 
-def run_cfg5(rank, world, device, steps, warmup, peaks):
+def run_long_context(rank, world, local, device, steps, warmup, peaks, a):
+    from oracle import gqa_oracle as O
     from tileops_b200 import workloads as W
     from tileops_b200.sharded import KVSequenceShardedPagedDecode, shard_page_range
     B, H, Hkv, D, page, ctx = 8, 32, 8, 128, 128, 131072
     p0, p1 = shard_page_range(ctx // page, rank, world)
     inp = W.make_paged_decode(5, B, H, Hkv, D, page, lens=[ctx] * B, device=device, page_begin=p0, page_end=p1)
     op = KVSequenceShardedPagedDecode(B, H, Hkv, D, page)
-    fn = lambda: op(inp.q, inp.k, inp.v, inp.real_seqlen_kv, inp.block_table)  # noqa: E731
-    # one CUDA graph per step (decode launch + NCCL all-gather + merge launch): at 4+ GPUs the GPU work of a
-    # step is shorter than the time Python needs to issue the three calls.  Every rank takes the same branch.
-    graphed = os.environ.get("TB200_BENCH_GRAPH", "1") != "0"
+    call = (inp.q, inp.k, inp.v, inp.real_seqlen_kv, inp.block_table)
+    reference_out = op(*call).clone()            # NCCL all-gather path (or the plain merge on one GPU)
+    # one CUDA graph per step (decode launch [+ exchange] + merge launch): at 4+ GPUs the GPU work of a
+    # step is shorter than the time Python needs to issue the calls.  Every rank takes the same branch.
+    graphed = not a.no_graph
     # exchange: stores over NVLink from the decode kernel into every rank's symmetric buffer (fused compute +
     # exchange); falls back to the NCCL all-gather if symmetric memory cannot be set up.  All ranks agree.
-    exchange = "nccl_all_gather"
-    if world > 1 and os.environ.get("TB200_BENCH_PEER", "1") != "0":
+    exchange, exchange_check = "nccl_all_gather", None
+    if world > 1 and not a.nccl_exchange:
         import torch.distributed as dist
         ok = torch.ones(1, device=device)
         try:
@@ -458,37 +567,131 @@ def run_cfg5(rank, world, device, steps, warmup, peaks):
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if ok.item() > 0:
             exchange = "peer_stores"
+            # the fused exchange against the all-gather path on the same inputs, on every rank
+            diff = (op(*call).float() - reference_out.float()).abs().max().reshape(1)
+            dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+            exchange_check = "bit-identical" if float(diff.item()) == 0.0 else float(diff.item())
         else:
             op._peer = None
-    if graphed:
-        fn = op.graphed(inp.q, inp.k, inp.v, inp.real_seqlen_kv, inp.block_table)
-    ms = max_over_ranks(time_steps(fn, steps, warmup, world), world, device) / steps
+    # one sequence x one KV-head group of the merged result against the CPU oracle over the whole context
+    parity_spot = None
+    if rank == 0:
+        full = W.make_paged_decode(5, 1, H, Hkv, D, page, lens=[ctx], device=device)   # sequence 0: same K/V stream
+        g = H // Hkv
+        ref = O.paged_decode_ref(inp.q[0:1, 0:g].cpu().float(), full.k[:, 0:1].cpu().float(), full.v[:, 0:1].cpu().float(),
+                                 full.real_seqlen_kv.cpu(), full.block_table.cpu(), page)
+        parity_spot = float((reference_out[0:1, 0:g].float().cpu() - ref).abs().max())
+        del full
+    fn = op.graphed(*call) if graphed else (lambda: op(*call))
+    m = measure(fn, steps, warmup, world, device, local)
     peer_status = op.peer_status()
     # drop the graph and the symmetric buffer before the process group is torn down
     del fn
     op._peer = None
     torch.cuda.synchronize(device)
     total = 2 * B * ctx * Hkv * D * 2 + 2 * B * H * D * 2 + 4 * B * (ctx // page) + 4 * B
-    return {"gbs": total / (ms * 1e-3) / 1e9, "frac_of_peak": total / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-            "ms_per_step": ms, "tokens_per_s": B / (ms * 1e-3), "scaling": "strong",
+    ms = m["ms_per_step"]
+    return {"workload": "batch 8, 32 q heads / 8 KV heads, head_dim 128, context 131072 per sequence, page 128, bf16; "
+                        "KV positions sharded over the ranks",
+            "gbs": total / (ms * 1e-3) / 1e9, "tokens_per_s": B / (ms * 1e-3), "scaling": "strong",
             "exchange_bytes_per_rank": B * H * (D + 1) * 4 * world, "cuda_graph": graphed, "exchange": exchange,
-            "peer_wait_status": peer_status,
-            "gpu_launches": steps * (2 if world > 1 else 2)}
+            "exchange_check": exchange_check, "parity_spot": parity_spot, "peer_wait_status": peer_status,
+            "gpu_launches": steps * 2,
+            "roofline": hbm_roofline("gqa_decode_kernel<128, bf16> + lse_merge_kernel", total // world,
+                                     m["ms_per_step_local"] * 1e3, peaks), **m}
 
 
-def run_cfg2(rank, world, device, steps, warmup, peaks):
+def run_causal_prefill(rank, world, local, device, steps, warmup, peaks):
+    from oracle import gqa_oracle as O
     from tileops_b200 import workloads as W
     from tileops_b200.ops import GroupedQueryAttentionFwdOp
     B, S, H, Hkv, D = 4, 4096, 32, 8, 128
     q, k, v = W.make_prefill(2 + 10 * rank, B, S, S, H, Hkv, D, torch.bfloat16, device)
     op = GroupedQueryAttentionFwdOp(B, H, Hkv, S, D, is_causal=True)
-    ms = max_over_ranks(time_steps(lambda: op(q, k, v), steps, warmup, world), world, device) / steps
+    m = measure(lambda: op(q, k, v), steps, warmup, world, device, local)
     flops, _ = op.eval_roofline()
-    tf = flops * world / (ms * 1e-3) / 1e12
-    return {"tflops": tf, "frac_of_peak_burst": tf / world / peaks["bf16_tflops"],
-            "frac_of_peak_sustained": tf / world / peaks["bf16_tflops_sustained"],
-            "frac_of_nominal_2250": tf / world / 2250.0, "ms_per_step": ms,
-            "tokens_per_s": B * S * world / (ms * 1e-3), "gpu_launches": steps}
+    tf = flops * world / (m["ms_per_step"] * 1e-3) / 1e12
+    parity_spot = None
+    if rank == 0:
+        g = H // Hkv
+        ref = O.prefill_ref(q[0:1, :, 0:g].cpu(), k[0:1, :, 0:1].cpu(), v[0:1, :, 0:1].cpu(), True)
+        parity_spot = float((op(q, k, v)[0:1, :, 0:g].float().cpu() - ref.float()).abs().max())
+    return {"workload": "batch 4, seqlen 4096, 32 q heads / 8 KV heads, head_dim 128, causal, bf16",
+            "tflops": tf, "tokens_per_s": B * S * world / (m["ms_per_step"] * 1e-3), "gpu_launches": steps,
+            "roofline": tensor_roofline("gqa_prefill_kernel<bf16, 128>", flops, m["ms_per_step_local"] * 1e3, peaks),
+            "parity_spot": parity_spot, **m}
+
+
+def run_manifest_decode(device, peaks):
+    """The decode and paged-decode workloads of the operator manifest (the reference's benchmark shapes,
+    ``src/tileops/manifest/attention.yaml`` of tile-ai/TileOPs, incl. the batch-1 1k..256k contexts), one
+    launch each between its own events.  These inputs are small (most fit the L2), so two figures are given:
+    launches back to back on resident data, and launches after a write larger than the L2."""
+    from tileops_b200 import workloads as W
+    from tileops_b200.manifest import load_workloads
+    from tileops_b200.ops import (GroupedQueryAttentionDecodePagedWithKVCacheFwdOp,
+                                  GroupedQueryAttentionDecodeWithKVCacheFwdOp)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    rows = {}
+
+    def timed(fn, cold: bool, n: int = 30):
+        """cold: a write larger than the L2 before every launch, each launch between its own events.
+        warm: ``n`` launches back to back behind one such write (the write keeps the queue busy while the
+        host enqueues, so no host launch latency is inside the events); the average of the launches."""
+        for _ in range(3):
+            fn()
+        if not cold:
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e3 / n
+        us = []
+        for _ in range(n):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            us.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(us)
+
+    for wl in load_workloads("GroupedQueryAttentionDecodeWithKVCacheFwdOp"):
+        B, H, D = wl["q_shape"]
+        _, S, Hkv, _ = wl["kv_shape"]
+        dtype = getattr(torch, wl["dtypes"][0])
+        q, k, v = W.make_contiguous_decode(20, B, H, Hkv, S, D, dtype, device)
+        op = GroupedQueryAttentionDecodeWithKVCacheFwdOp(B, H, Hkv, S, D, softcap=wl.get("softcap"))
+        fn = lambda: op(q, k, v)  # noqa: E731
+        by = 2 * B * S * Hkv * D * 2 + 2 * B * H * D * 2
+        warm, cold = timed(fn, False), timed(fn, True)
+        rows["decode/" + wl["label"]] = {"us_warm": warm, "us_cold": cold, "gbs_cold": by / cold / 1e3,
+                                         "frac_of_peak_cold": by / cold / 1e3 / peaks["hbm_gbs"], "bytes": by}
+        del q, k, v, op
+    for wl in load_workloads("GroupedQueryAttentionDecodePagedWithKVCacheFwdOp"):
+        if wl.get("own_pages"):
+            continue            # the headline and long-context workloads: timed above with their own protocol
+        B, H, D = wl["q_shape"]
+        pool, Hkv, _ = wl["kv_shape"]
+        page = wl["page_size"]
+        dtype = getattr(torch, wl["dtypes"][0])
+        # the reference's paged workload: one pool of `pool` tokens, every sequence reads all of it through
+        # the same identity block table (workloads/attention/gqa.py:204-218)
+        q = torch.randn(B, H, D, device=device).to(dtype)
+        k = torch.randn(pool, Hkv, D, device=device).to(dtype)
+        v = torch.randn(pool, Hkv, D, device=device).to(dtype)
+        lens = torch.full((B,), pool, dtype=torch.int32, device=device)
+        bt = torch.arange(pool // page, dtype=torch.int32, device=device).repeat(B, 1).contiguous()
+        op = GroupedQueryAttentionDecodePagedWithKVCacheFwdOp(B, H, Hkv, pool, D, page, softcap=wl.get("softcap"))
+        fn = lambda: op(q, k, v, lens, bt)  # noqa: E731
+        by = 2 * pool * Hkv * D * 2 + 2 * B * H * D * 2          # the pool is shared: each byte once from HBM
+        warm, cold = timed(fn, False), timed(fn, True)
+        rows["paged/" + wl["label"]] = {"us_warm": warm, "us_cold": cold, "bytes_from_hbm": by,
+                                        "gbs_l2_warm": B * 2 * pool * Hkv * D * 2 / warm / 1e3}
+        del q, k, v, op
+    return rows
 
 
 if __name__ == "__main__":

@@ -384,3 +384,11 @@ def test_fp8_cache_golden_vectors():
     torch.testing.assert_close(o[..., :32].cpu().float(), h("p8_o").float(), atol=5e-3, rtol=1e-2)
     assert torch.equal(kp[..., :32].cpu().view(torch.uint8), f8("p8_k_pages_after").view(torch.uint8))
     assert torch.equal(vp[..., :32].cpu().view(torch.uint8), f8("p8_v_pages_after").view(torch.uint8))
+
+
+def test_last_cached_tile_never_reads_behind_the_block_table_row():
+    """5 pages of 16 tokens, 79 cached + 1 new: the last 64-key tile of the cache covers tokens 64..127,
+    past the 80 the table describes.  The lookup for the tile's tail must stay inside the request's row
+    (here the LAST row of the table, which ends its allocation); the result must still match."""
+    for heads_kv in (2, 8):
+        _check([1, 1], [40, 79], 8, heads_kv, 64, 16, torch.float16, pages_per_req=5, pool_fill=float("nan"))

@@ -399,9 +399,11 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                              const CUtensorMap* pool_map, int i) {
           if (kPaged && i < n_old) {
             for (int r = 0; r < kBN; r += p.page_box) {
-              const int tok = i * kBN + r;
+              // the last cached tile may reach past old_len: look up the page of a live token there (the
+              // rows are masked and their V cleared), never an entry behind the request's pages
+              const int tok = min(i * kBN + r, old_len - 1);
               const int page = p.bt[(long long)b * p.bt_stride + (tok >> p.page_shift)];
-              const int row = page * p.page_size + (tok & (p.page_size - 1));
+              const int row = page * p.page_size + ((i * kBN + r) & (p.page_size - 1));
 #pragma unroll
               for (int pn = 0; pn < kHD / 64; ++pn)
                 tma_load_4d(dst + pn * kKvPanel + r * 128, pool_map, full_bar, pn * 64, hk, row, 0);

@@ -188,13 +188,41 @@ def _prefill_status(device: torch.device, need: int) -> torch.Tensor:
     return ws
 
 
-def prefill_status(device: "torch.device | str" = "cuda") -> int:
-    """0 if no prefill launch on ``device`` has timed out on a device-side wait, else the code of
-    the wait that gave up (synchronises with the device)."""
-    ws = _WORKSPACES.get((torch.device(device) if not isinstance(device, torch.device) else device, "prefill_status"))
+def _device_of(device: "torch.device | str | int | None") -> torch.device:
+    """A device with an explicit index (``"cuda"`` means the current device)."""
+    d = torch.device("cuda" if device is None else device)
+    if d.type == "cuda" and d.index is None:
+        d = torch.device("cuda", torch.cuda.current_device())
+    return d
+
+
+def prefill_status(device: "torch.device | str | int | None" = None, reset: bool = False) -> int:
+    """0 if no prefill launch on ``device`` (default: the current CUDA device) has timed out on a
+    device-side wait, else the code of the wait that gave up (synchronises with the device).
+
+    The word is sticky: once set, every later prefill launch on the device returns at once with its
+    outputs unwritten, so after a suspected timeout poll this before using any output.  ``reset=True``
+    clears the word after reading it."""
+    ws = _WORKSPACES.get((_device_of(device), "prefill_status"))
     if ws is None:
         return 0
-    return int(ws[:4].view(torch.int32).item())
+    code = int(ws[:4].view(torch.int32).item())
+    if reset and code:
+        ws[:4].zero_()
+    return code
+
+
+def decode_status(device: "torch.device | str | int | None" = None) -> int:
+    """Largest non-zero status word left by a decode launch in any cached workspace of ``device`` (601-603:
+    a bounded wait of the TMA decode kernel ran out), else 0.  Synchronises.  A workspace whose status is set
+    is dropped from the cache (its counters are no longer trustworthy); the next call allocates a fresh one."""
+    dev, worst = _device_of(device), 0
+    for key in [k for k in _WORKSPACES if len(k) > 2 and k[2] == "decode" and k[0] == dev]:
+        code = int(_WORKSPACES[key][8:12].view(torch.int32).item())
+        if code:
+            worst = max(worst, code)
+            del _WORKSPACES[key]
+    return worst
 
 
 def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal: bool = True,

@@ -11,7 +11,7 @@ import yaml
 _DIR = os.path.dirname(os.path.abspath(__file__))
 
 #: keys of a workload entry that are not op parameters
-WORKLOAD_RESERVED_KEYS = frozenset({"dtypes", "label", "bench_skip_reason"})
+WORKLOAD_RESERVED_KEYS = frozenset({"dtypes", "label", "bench_skip_reason", "own_pages"})
 
 
 @functools.lru_cache(maxsize=1)
