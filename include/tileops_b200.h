@@ -158,7 +158,8 @@ int tb200_gqa_decode_noalloc(const void* q, const void* k, const void* v, void* 
  * Merge R partial attention results over disjoint KV ranges (split-KV across GPUs).
  *   o_parts   [R, rows, dim] fp32, each normalised by its own softmax sum; part r starts at
  *             o_parts + r * o_part_stride floats (0 means packed: rows * dim)
- *   lse_parts [R, rows] fp32 log2-domain (-inf or <= -1e29 marks an empty part); part r starts
+ *   lse_parts [R, rows] fp32 log2-domain (-inf or <= -1e29 marks an empty part; a NaN makes the
+ *             row's o and lse NaN: a part that went wrong must not pass for an empty one); part r starts
  *             at lse_parts + r * lse_part_stride floats (0 means packed: rows)
  *   o         [rows, dim] o_dtype ; lse [rows] fp32 or NULL
  * Same algebra as the reference's combine grid
@@ -224,15 +225,21 @@ int tb200_gqa_lse_merge_wait(const float* o_parts, const float* lse_parts, void*
  * d = seqlen_kv - seqlen_q, key j is visible to row i iff j >= i + d - window_left (when
  * window_left >= 0), j <= i + d + window_right (when window_right >= 0) and j <= i + d (when
  * causal); -1 = unlimited.  Key tiles outside the window of a whole row tile are skipped.
- * workspace: tb200_gqa_prefill_workspace_bytes() bytes (may be 0 -> NULL allowed).
+ * flags: 0, or TB200_PREFILL_ONE_TILE to keep the kernel with one Q tile per CTA where the kernel with two
+ * Q tiles per CTA (head dim 128) would be chosen: the tuning surface of the reference's config=.
+ * workspace: tb200_gqa_prefill_workspace_bytes() bytes, zeroed once.  Its first int is a status word: 0, or
+ * the code of a bounded device-side wait that ran out (1xx-3xx, 7xx); once set, later launches return at
+ * once with their outputs unwritten until the word is cleared.
  * ------------------------------------------------------------------------- */
+#define TB200_PREFILL_ONE_TILE 1
+
 size_t tb200_gqa_prefill_workspace_bytes(int batch, int heads, int heads_kv, int seqlen_q,
                                          int seqlen_kv, int dim);
 
 int tb200_gqa_prefill(const void* q, const void* k, const void* v, void* o, float* lse,
                       int dtype, int batch, int seqlen_q, int seqlen_kv, int heads, int heads_kv,
                       int dim, int is_causal, float sm_scale, float softcap,
-                      int window_left, int window_right,
+                      int window_left, int window_right, int flags,
                       void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------
@@ -273,7 +280,7 @@ int tb200_gqa_prefill_paged(const void* q, const void* k_new, const void* v_new,
                             int dtype, int total_q, int total_kv, int batch, int max_seqlen_q,
                             int heads, int heads_kv, int dim, int page_size, int64_t pool_tokens,
                             int is_causal, float sm_scale, float softcap,
-                            int window_left, int window_right,
+                            int window_left, int window_right, int flags,
                             void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------

@@ -374,8 +374,11 @@ def merge_partials_ref(o_parts: torch.Tensor, lse_parts: torch.Tensor) -> Tuple[
     algebra of the reference's combine grid
     (``src/tileops/kernels/attention/gqa_decode_paged.py:344-374``).  A part whose
     LSE is ``-inf`` (or the finite floor ``<= -1e29``) carries no weight; if every
-    part is empty the result is zero.
+    part is empty the result is zero.  A NaN LSE in any part makes the row NaN (o and lse): a part that
+    went wrong must not be mistaken for an empty one.
     """
+    bad = torch.isnan(lse_parts).any(dim=0)
+    lse_parts = torch.nan_to_num(lse_parts, nan=float("-inf"))
     lse = lse_parts.double()
     m = lse.max(dim=0).values
     m_safe = torch.where(torch.isfinite(m) & (m > -1e29), m, torch.zeros_like(m))
@@ -385,7 +388,10 @@ def merge_partials_ref(o_parts: torch.Tensor, lse_parts: torch.Tensor) -> Tuple[
     o = (w[..., None] * o_parts.double()).sum(dim=0) / torch.where(den > 0, den, torch.ones_like(den))[..., None]
     lse_tot = torch.where(den > 0, torch.log2(torch.where(den > 0, den, torch.ones_like(den))) + m_safe,
                           torch.full_like(den, float("-inf")))
-    return o.float(), lse_tot.float()
+    o, lse_tot = o.float(), lse_tot.float()
+    o[bad] = float("nan")
+    lse_tot[bad] = float("nan")
+    return o, lse_tot
 
 
 # ---------------------------------------------------------------------------

@@ -6,6 +6,8 @@ import ctypes
 import json
 import os
 import re
+import subprocess
+import sys
 
 import pytest
 import torch
@@ -431,3 +433,47 @@ def test_workload_generator_shards_reproduce_the_full_problem():
             parts.append(sh.k[torch.from_numpy(r)])
             assert torch.equal(sh.q, full.q)
         assert torch.equal(torch.cat(parts), logical)
+
+
+REFERENCE_SRC = "/root/reference/src"
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE_SRC, "tileops", "backend")),
+                    reason="needs a TileOPs source tree (present in the build container only)")
+def test_plugin_registers_with_the_real_tileops_backend():
+    """The plugin seam against the reference's own ``tileops.backend`` (``src/tileops/backend/registry.py:42-84``,
+    ``protocol.py:10-32``), in a child process so that the reference tree never enters this process: importing
+    the plugin registers the detector and the five builders in the REAL registry, this package's backend module
+    is then that registry, builders answer ``(*TensorSpec, **params)``, and the real dispatch resolves the target."""
+    code = r'''
+import torch, tileops.backend as tb
+from tileops.backend import registry, dispatch
+import tileops_b200.backend as mine
+assert mine.USES_INSTALLED_TILEOPS and mine.registry is registry and mine.TensorSpec is tb.TensorSpec
+from tileops_b200 import plugin                      # the entry-point import: registers on import
+assert registry.DETECTORS[plugin.TARGET] is plugin.detect
+assert len(plugin.BUILDERS) == 5
+for op_name, builder in plugin.BUILDERS.items():
+    assert registry.BUILDERS[(op_name, plugin.TARGET)] is builder, op_name
+assert plugin.TARGET in tb.registered_targets()
+try:
+    plugin.register(tb)
+    raise SystemExit("a second detector for the same target must be refused")
+except tb.BackendError:
+    pass
+S = tb.TensorSpec
+dev = torch.device("cuda", 0)
+q, kv, meta = S(dev, torch.bfloat16, (4, 32, 128)), S(dev, torch.bfloat16, (4096, 8, 128)), S(dev, torch.int32, (4,))
+run = registry.BUILDERS[("GroupedQueryAttentionDecodePagedWithKVCacheFwdOp", plugin.TARGET)](
+    q, kv, kv, meta, meta, page_size=64, sm_scale=None, softcap=None)
+assert callable(run)
+tb.set_default_target(plugin.TARGET)
+assert tb.default_target() == plugin.TARGET
+# this package's operators dispatch through the same (real) tables
+from tileops_b200.ops import GroupedQueryAttentionDecodePagedWithKVCacheFwdOp
+op = GroupedQueryAttentionDecodePagedWithKVCacheFwdOp(4, 32, 8, 4096, 128, 64)
+print("REAL-BACKEND-OK")
+'''
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([REFERENCE_SRC, ROOT]))
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd="/tmp", timeout=300)
+    assert out.returncode == 0 and "REAL-BACKEND-OK" in out.stdout, out.stdout[-2000:] + out.stderr[-3000:]

@@ -158,3 +158,36 @@ def test_config2_rows_against_oracle_and_causal_prefix_property():
     o1 = F.gqa_prefill(q[:, :1024].contiguous(), k[:, :1024].contiguous(), v[:, :1024].contiguous(), is_causal=True)
     assert torch.equal(o1, o[:, :1024])
     assert F.prefill_status("cuda:0") == 0
+
+
+@pytest.mark.parametrize("B,Sq,Skv,H,Hkv,causal,wl,wr,softcap,dtype", [
+    (1, 1024, 1024, 8, 2, True, -1, -1, 0.0, torch.bfloat16),
+    (2, 640, 640, 4, 4, True, -1, -1, 0.0, torch.float16),        # odd number of row tiles: a pair with one tile
+    (1, 300, 777, 4, 2, True, -1, -1, 0.0, torch.bfloat16),       # Sq < Skv, ragged tiles on both sides
+    (1, 777, 300, 4, 2, True, -1, -1, 0.0, torch.bfloat16),       # Sq > Skv: leading rows see no key
+    (1, 512, 512, 4, 1, False, -1, -1, 0.0, torch.bfloat16),
+    (1, 1024, 1024, 4, 2, True, 200, -1, 0.0, torch.bfloat16),    # causal sliding window: the tiles of a pair start at different keys
+    (1, 900, 900, 4, 2, False, 100, 60, 0.0, torch.float16),
+    (1, 512, 512, 4, 2, True, -1, -1, 30.0, torch.bfloat16),
+])
+def test_two_tile_and_one_tile_kernels_agree_with_the_oracle(B, Sq, Skv, H, Hkv, causal, wl, wr, softcap, dtype):
+    """Head dim 128 is served by two kernels (two Q tiles per CTA in ping-pong with 128-key tiles; one Q
+    tile per CTA with 64-key tiles); both against the oracle, LSE included."""
+    q, k, v = W.make_prefill(44, B, Sq, Skv, H, Hkv, 128, dtype, "cuda")
+    ro, rl = O.prefill_ref(q.cpu(), k.cpu(), v.cpu(), causal, softcap=softcap or None, return_lse=True,
+                           window_left=wl, window_right=wr)
+    outs = []
+    for tiles in (2, 1):
+        o, lse = F.gqa_prefill(q, k, v, is_causal=causal, softcap=softcap, return_lse=True, window_size_left=wl,
+                               window_size_right=wr, config={"tiles_per_cta": tiles})
+        assert F.prefill_status() == 0
+        assert not torch.isnan(o).any()
+        close(o, ro)
+        fin = torch.isfinite(rl)
+        assert torch.equal(fin, torch.isfinite(lse.cpu()))
+        torch.testing.assert_close(lse.cpu()[fin], rl[fin], atol=2e-3, rtol=1e-3)
+        outs.append((o, lse))
+    torch.testing.assert_close(outs[0][0].float(), outs[1][0].float(), atol=1e-2, rtol=1e-2)
+    fin = torch.isfinite(outs[1][1])
+    assert torch.equal(fin, torch.isfinite(outs[0][1]))
+    torch.testing.assert_close(outs[0][1][fin], outs[1][1][fin], atol=2e-3, rtol=1e-3)

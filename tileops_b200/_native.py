@@ -25,6 +25,15 @@ F16, BF16, E4M3, F32 = 0, 1, 2, 3
 # variant flags of tb200_gqa_decode (TB200_DECODE_* in include/tileops_b200.h)
 DECODE_WIDE_ON, DECODE_WIDE_OFF, DECODE_FP8_MMA, DECODE_NO_TMA = 1, 2, 4, 8
 DECODE_CHUNK_TILES_SHIFT = 8
+PREFILL_ONE_TILE = 1
+
+
+def prefill_flags(config: "dict | None") -> int:
+    """Variant flags of the prefill entry points from a kernel ``config`` dict: ``tiles_per_cta`` 1 keeps the
+    kernel with one Q tile per CTA (2, the default, lets the library use the ping-pong kernel)."""
+    if config and int(config.get("tiles_per_cta") or 2) == 1:
+        return PREFILL_ONE_TILE
+    return 0
 
 
 def decode_flags(config: "dict | None") -> int:
@@ -91,12 +100,12 @@ SIGNATURES = {
     "tb200_gqa_prefill": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,      # q k v o lse
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,  # dtype B Sq Skv H Hkv D causal
-        c_float, c_float, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+        c_float, c_float, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),   # sm_scale softcap win_l win_r flags ws bytes stream
     "tb200_gqa_prefill_paged": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # q k_new v_new k_pages v_pages o lse
         c_void_p, c_void_p, c_void_p, c_void_p, c_int64,        # cu_seqlens_q cu_seqlens_kv cache_seqlens block_table stride
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int,  # dtype total_q total_kv B maxq H Hkv D page pool causal
-        c_float, c_float, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+        c_float, c_float, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "tb200_rope_neox_packed": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,      # x y cos sin cu_seqlens_q cache_seqlens
         c_int, c_int, c_int, c_int, c_int, c_int, c_int,              # dtype tokens B H D rotary_dim max_position

@@ -1,4 +1,5 @@
-"""Which target serves a call (``src/tileops/backend/dispatch.py:15-129`` of the reference):
+"""Which target serves a call; condensed from ``src/tileops/backend/dispatch.py:15-129`` of the reference
+(used only when ``tileops.backend`` itself is not importable):
 explicit ``target=`` first, then the process default, then detection on the first tensor's
 device; ``None`` means the in-tree kernels run."""
 

@@ -1,5 +1,5 @@
-"""Errors of the target-plugin layer (mirrors ``tileops.backend.errors``,
-``src/tileops/backend/errors.py:1-23`` in the reference)."""
+"""Errors of the target-plugin layer; condensed from ``src/tileops/backend/errors.py:1-23`` of the
+reference (used only when ``tileops.backend`` itself is not importable)."""
 
 
 class BackendError(Exception):

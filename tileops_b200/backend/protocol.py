@@ -1,4 +1,5 @@
-"""Types that cross the op/target boundary (``src/tileops/backend/protocol.py:10-53``)."""
+"""Types that cross the op/target boundary; condensed from ``src/tileops/backend/protocol.py:10-53`` of the
+reference (used only when ``tileops.backend`` itself is not importable)."""
 
 from __future__ import annotations
 

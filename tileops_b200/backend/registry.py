@@ -1,6 +1,8 @@
 """Process-wide tables of target detectors and kernel builders.
 
-Same contract as ``src/tileops/backend/registry.py:42-194`` of the reference: one detector
+Condensed from ``src/tileops/backend/registry.py:42-194`` of the reference (same globals, functions and
+messages, so that this package runs without a TileOPs installation; when ``tileops.backend`` is
+importable the package uses that one instead, see ``backend/__init__.py``).  The contract: one detector
 per target, one builder per ``(op, target)``, duplicates are an error, plugins are discovered
 from the ``tileops.backends`` entry-point group exactly once, and a plugin that fails to
 import is recorded and skipped rather than fatal.

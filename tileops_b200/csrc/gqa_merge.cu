@@ -57,9 +57,16 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const float* o_parts, co
     lse_parts += shift;
   }
   float M = kNegFloor;
+  bool bad = false;                    // a NaN LSE: that part went wrong, which must not pass for "empty"
   for (int r = 0; r < parts; ++r) {
     float l = __ldcg(lse_parts + int64_t(r) * lse_stride + row);
+    bad |= (l != l);
     if (l > -1e29f) M = fmaxf(M, l);   // -inf and the finite floor both mean "empty"
+  }
+  if (bad) {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) store_out<TO>(o + row * dim + d, __int_as_float(0x7fc00000));
+    if (lse && threadIdx.x == 0) lse[row] = __int_as_float(0x7fc00000);
+    return;
   }
   float den = 0.f;
   for (int r = 0; r < parts; ++r) {

@@ -31,11 +31,9 @@
 //
 // Every mbarrier wait is bounded; on a timeout the CTA records an error code, stops issuing work,
 // lets its copies drain, frees its TMEM and returns.
-#include <cuda.h>
-
 #include <type_traits>
 
-#include "tb200_common.cuh"
+#include "gqa_prefill.cuh"
 
 namespace tb200 {
 namespace {
@@ -57,17 +55,9 @@ constexpr int kThreads = 192;
 __host__ __device__ constexpr uint32_t tmem_cols(int hd) { return hd <= 128 ? 256u : 512u; }
 __host__ __device__ constexpr int ctas_per_sm(int hd) { return hd <= 128 ? 2 : 1; }
 constexpr uint32_t kColS = 0, kColO = 128;    // S buffer s at columns [64 s, 64 s + 64)
-#ifndef TB200_PF_TIE
-#define TB200_PF_TIE 1
-#endif
-#ifndef TB200_PF_WAIT_HINT_NS
-#define TB200_PF_WAIT_HINT_NS 0   // suspend-time hint of a failed mbarrier probe; 0 = none
-#endif
 #ifndef TB200_PF_F32X2
 #define TB200_PF_F32X2 1
 #endif
-constexpr float kRescaleThreshold = 8.f;   // log2 of the growth of the row maximum that forces a rescale
-constexpr long long kWaitCycles = 1000000000LL;  // ~0.5 s at 2 GHz
 
 // Shared-memory plan for head dim HD (64 or 128): HD / 64 panels per operand tile.
 template <int HD>
@@ -99,182 +89,11 @@ constexpr int kTraceIters = 64, kTraceSlots = 10, kTraceCta = 600;
 #define TB200_STAMP(slot, j) do {} while (0)
 #endif
 
-struct PrefillParams {
-  void* o;
-  float* lse;
-  int* status;
-  int batch, heads, heads_kv, seqlen_q, seqlen_kv;
-  int is_causal;
-  int win_left, win_right;     // sliding window around the (bottom-right aligned) diagonal; -1 = unlimited
-  float sm_scale, softcap;
-  // packed (ragged) queries over a paged cache; unused by the dense kernel
-  const int32_t* cu_q;         // [batch + 1] row offsets of the requests in q / o (and k_new / v_new)
-  const int32_t* cu_kv;        // [batch + 1] row offsets in k_new / v_new when they differ from cu_q, or null
-  const int32_t* cache_lens;   // [batch] tokens already in the pages (null: none)
-  const int32_t* bt;           // [batch, bt_stride] logical page -> physical page
-  long long bt_stride;
-  const void* k_new;           // [total_q, heads_kv, HD]
-  const void* v_new;
-  void* k_pages;               // [pool_tokens, heads_kv, HD]; null: nothing is appended
-  void* v_pages;
-  int page_size, page_shift, page_box;   // page_box = min(64, page_size): rows per TMA box of the pool maps
-  int total_q;
-};
-
-// ---- PTX wrappers ------------------------------------------------------------------------
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-#if TB200_PF_WAIT_HINT_NS
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-#else
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(uint32_t(TB200_PF_WAIT_HINT_NS))
-      : "memory");
-  return ok != 0;
-}
+// ---- PTX wrappers: tb200_async.cuh (mbarrier, TMA) and tb200_tcgen05.cuh (MMA, TMEM) ----------------
 // Bounded wait.  Returns false when the CTA is aborting (this wait ran out, or another role's did).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (true) {
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
-      *abort_flag = 1;
-      atomicCAS(status, 0, code);
-      return false;
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
-                                            int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// The same wait, naming the registers a preceding tcgen05.ld fills: the load is asynchronous, and the
-// in/out operands keep the compiler from moving any use of those registers above the wait.
-__device__ __forceinline__ void tc_wait_ld(uint32_t (&r)[32]) {
-#if !TB200_PF_TIE
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-  return;
-#endif
-  asm volatile(
-      "tcgen05.wait::ld.sync.aligned;"
-      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-        "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
-        "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
-        "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-      :
-      : "memory");
-}
-// Packed pairs of fp32 (sm_100 has two-wide fp32 FMA and ADD on 64-bit register pairs).
-__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
-  uint64_t d;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
-  return d;
-}
-__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// 64-bit shared-memory matrix descriptor, 128B swizzle, version 1 (sm_100).
-//   [0,14) start address >> 4 | [16,30) leading byte offset >> 4 | [32,46) stride byte offset >> 4
-//   [46,48) version = 1 | [61,64) layout type (2 = SWIZZLE_128B)
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) |
-         (uint64_t(sbo_bytes >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
-}
-
-// Instruction descriptor of kind::f16: fp32 accumulate, A/B format fmt (0 = f16, 1 = bf16),
-// M = 128, N = n, A K-major; B K-major (b_mn = 0) or MN-major (b_mn = 1).
-__host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t b_mn, uint32_t n) {
-  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn << 16) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+  return mbar_wait_bounded(bar, parity, abort_flag, status, code, kWaitCycles);
 }
 
 template <typename T>
@@ -735,43 +554,6 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 // ---- host side ------------------------------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// [batch, seq, heads, hd] contiguous 16-bit tensor -> 4-D map (d, head, seq, batch), box 64 x 1 x box_rows x 1
-int make_map(CUtensorMap* map, const void* base, int dtype, long long batch, long long seq, int heads, int hd,
-             int box_rows) {
-  EncodeTiledFn enc = encode_fn();
-  if (!enc) TB200_FAIL(TB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t dims[4] = {cuuint64_t(hd), cuuint64_t(heads), cuuint64_t(seq), cuuint64_t(batch)};
-  cuuint64_t strides[3] = {cuuint64_t(hd) * 2, cuuint64_t(heads) * hd * 2, cuuint64_t(seq) * heads * hd * 2};
-  cuuint32_t box[4] = {64, 1, cuuint32_t(box_rows), 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(map, dtype == TB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) TB200_FAIL(TB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
-  return TB200_OK;
-}
-
-struct PrefillMaps {
-  CUtensorMap q, k, v, kp, vp;
-};
-
 template <typename T, bool kSoftcap, int HD, bool kPaged>
 int launch_prefill(const PrefillMaps& m, const PrefillParams& p, cudaStream_t stream) {
   auto kern = gqa_prefill_kernel<T, kSoftcap, HD, kPaged>;
@@ -808,7 +590,8 @@ extern "C" size_t tb200_gqa_prefill_workspace_bytes(int batch, int heads, int he
 extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, void* o, float* lse, int dtype,
                                  int batch, int seqlen_q, int seqlen_kv, int heads, int heads_kv, int dim,
                                  int is_causal, float sm_scale, float softcap, int window_left, int window_right,
-                                 void* workspace, size_t workspace_bytes, void* stream) {
+                                 int flags, void* workspace, size_t workspace_bytes, void* stream) {
+  if (flags < 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "flags must be a combination of TB200_PREFILL_* values");
   if (window_left < -1 || window_right < -1)
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "window sizes must be -1 (unlimited) or >= 0");
   if (!q || !k || !v || !o) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "q, k, v and o must be non-null");
@@ -839,6 +622,11 @@ extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, vo
   p.is_causal = is_causal; p.sm_scale = sm_scale; p.softcap = softcap;
   p.win_left = window_left; p.win_right = window_right;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!(flags & TB200_PREFILL_ONE_TILE)) {
+    // head dim 128: two Q tiles per CTA in ping-pong (gqa_prefill_pp.cu); it declines what it does not serve
+    const int st2 = launch_prefill_pp(m, p, dtype, dim, false, s);
+    if (st2 != kPrefillPpNotApplicable) return st2;
+  }
   if (dim == 256) return dispatch_prefill<256, false>(dtype, m, p, s);
   return dim == 128 ? dispatch_prefill<128, false>(dtype, m, p, s) : dispatch_prefill<64, false>(dtype, m, p, s);
 }
@@ -850,8 +638,9 @@ extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const v
                                        int total_q, int total_kv, int batch, int max_seqlen_q, int heads,
                                        int heads_kv, int dim, int page_size,
                                        int64_t pool_tokens, int is_causal, float sm_scale, float softcap,
-                                       int window_left, int window_right, void* workspace,
+                                       int window_left, int window_right, int flags, void* workspace,
                                        size_t workspace_bytes, void* stream) {
+  if (flags < 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "flags must be a combination of TB200_PREFILL_* values");
   if (window_left < -1 || window_right < -1)
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "window sizes must be -1 (unlimited) or >= 0");
   if (!q || !k_new || !v_new || !o || !cu_seqlens_q)

@@ -227,7 +227,7 @@ def decode_status(device: "torch.device | str | int | None" = None) -> int:
 
 def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal: bool = True,
                 sm_scale: Optional[float] = None, softcap: float = 0.0, return_lse: bool = False,
-                window_size_left: int = -1, window_size_right: int = -1):
+                window_size_left: int = -1, window_size_right: int = -1, config: Optional[dict] = None):
     """Dense BSHD prefill: q ``[B,Sq,H,D]``, k/v ``[B,Skv,Hkv,D]`` -> o ``[B,Sq,H,D]`` (+ LSE
     ``[B,H,Sq]`` fp32, log2 domain)."""
     _require_cuda(q=q, k=k, v=v)
@@ -251,7 +251,8 @@ def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal:
         st = N.lib().tb200_gqa_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), N.ptr(lse),
                                        N.dtype_code(q.dtype), B, Sq, Skv, H, Hkv, D, int(bool(is_causal)),
                                        scale, float(softcap or 0.0), int(window_size_left),
-                                       int(window_size_right), N.ptr(ws), need, N.current_stream(q.device))
+                                       int(window_size_right), N.prefill_flags(config), N.ptr(ws), need,
+                                       N.current_stream(q.device))
     N.check(st, "tb200_gqa_prefill")
     return (o, lse) if return_lse else o
 
@@ -262,7 +263,7 @@ def gqa_prefill_paged(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
                       block_table: Optional[torch.Tensor], max_seqlen_q: int, *, page_size: int = 0,
                       is_causal: bool = True, sm_scale: Optional[float] = None, softcap: float = 0.0,
                       return_lse: bool = False, cu_seqlens_kv: Optional[torch.Tensor] = None,
-                      window_size_left: int = -1, window_size_right: int = -1):
+                      window_size_left: int = -1, window_size_right: int = -1, config: Optional[dict] = None):
     """Packed prefill of one chunk per request over a paged cache, appending the chunk in place.
 
     q ``[total_q,H,D]``, k_new/v_new ``[total_q,Hkv,D]``, k_pages/v_pages ``[pool_tokens,Hkv,D]``
@@ -327,8 +328,8 @@ def gqa_prefill_paged(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
             N.ptr(block_table) if has_cache else None, bt_stride, N.dtype_code(q.dtype), total_q,
             k_new.shape[0], B,
             int(max_seqlen_q), H, Hkv, D, int(page_size), pool_tokens, int(bool(is_causal)), scale,
-            float(softcap or 0.0), int(window_size_left), int(window_size_right), N.ptr(ws), need,
-            N.current_stream(q.device))
+            float(softcap or 0.0), int(window_size_left), int(window_size_right), N.prefill_flags(config),
+            N.ptr(ws), need, N.current_stream(q.device))
     N.check(st, "tb200_gqa_prefill_paged")
     return (o, lse) if return_lse else o
 

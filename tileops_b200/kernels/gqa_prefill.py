@@ -51,7 +51,11 @@ class GQAPrefillSm100Kernel(Kernel):
 
     @property
     def default_config(self) -> dict:
-        return {"block_M": 128, "block_N": 64, "threads": 192}
+        """``tiles_per_cta`` is the one entry a caller may set: 2 (default) lets head dim 128 run the kernel
+        with two Q tiles per CTA in ping-pong (128-key tiles, 320 threads, persistent grid); 1 keeps the
+        kernel with one Q tile per CTA (64-key tiles, 192 threads, two CTAs per SM), which also serves head
+        dims 64 and 256.  The other entries describe the latter."""
+        return {"block_M": 128, "block_N": 64, "threads": 192, "tiles_per_cta": 2}
 
     def forward(self, q, k, v, cu_seqlens_q=None, cu_seqlens_kv=None, q_scale=None, k_scale=None,
                 v_scale=None, return_lse: bool = False):
@@ -64,7 +68,8 @@ class GQAPrefillSm100Kernel(Kernel):
         out = F.gqa_prefill(q.view(B, Sq, self.heads, self.dim), k.view(B, Skv, self.heads_kv, self.dim),
                             v.view(B, Skv, self.heads_kv, self.dim), is_causal=self.is_causal,
                             sm_scale=self.sm_scale, softcap=self.softcap, return_lse=return_lse,
-                            window_size_left=self.window_size_left, window_size_right=self.window_size_right)
+                            window_size_left=self.window_size_left, window_size_right=self.window_size_right,
+                            config=self.config)
         if return_lse:
             return out[0].view(q.shape), out[1]
         return out.view(q.shape)
@@ -163,12 +168,12 @@ class GQASlidingWindowSm100Kernel(Kernel):
 
     @property
     def default_config(self) -> dict:
-        return {"block_M": 128, "block_N": 64, "threads": 192}
+        return {"block_M": 128, "block_N": 64, "threads": 192, "tiles_per_cta": 2}
 
     def forward(self, q, k, v):
         self._require_cuda(q=q, k=k, v=v)
         return F.gqa_prefill(q, k, v, is_causal=self.is_causal, window_size_left=self.window_size_left,
-                             window_size_right=self.window_size_right)
+                             window_size_right=self.window_size_right, config=self.config)
 
 
 class GQAPrefillPagedSm100Kernel(Kernel):

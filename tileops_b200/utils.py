@@ -1,4 +1,4 @@
-"""Cached device facts (role of ``src/tileops/utils/utils.py:19-53`` in the reference)."""
+"""Cached device facts (condensed from ``src/tileops/utils/utils.py:19-53`` of the reference)."""
 
 import functools
 
