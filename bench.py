@@ -327,7 +327,7 @@ def main():
     ap.add_argument("--nccl-exchange", action="store_true", help="long-context sharded step: NCCL all-gather instead of the fused exchange")
     ap.add_argument("--case", default=None,
                     choices=["decode_small", "decode_fp8_small", "prefill_small", "prefill_paged", "rope_small",
-                             "fp8_cache_small", "merge_small"],
+                             "fp8_cache_small", "merge_small", "mma_issue"],
                     help="run only a reduced case of one kernel (a few hundred MB on the device: the "
                          "size an ncu capture of all sections can handle) and print its timing")
     a = ap.parse_args()
@@ -427,6 +427,16 @@ def run_small_case(case: str, steps: int, warmup: int):
                                   GroupedQueryAttentionFwdOp)
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
+    if case == "mma_issue":
+        # what one tcgen05.mma instruction costs on the tensor pipe, by N and by the place of the A operand
+        rows = {}
+        for n in (64, 128, 256):
+            for tmem_a in (False, True):
+                issued, done = F.mma_issue_probe(n, tmem_a, 200, device)
+                rows[f"N={n},A={'tmem' if tmem_a else 'smem'}"] = {"clocks_per_mma": round(done, 1),
+                                                                    "arithmetic_clocks": n // 2}
+        print(json.dumps({"case": case, "M": 128, "K": 16, "kind": "f16", "rows": rows}))
+        return
     if case == "decode_small":
         inp = W.make_paged_decode(3, 16, 32, 8, 128, 64, len_range=(512, 8192), device=device)
         op = GroupedQueryAttentionDecodePagedWithKVCacheFwdOp(16, 32, 8, inp.k.shape[0], 128, 64)

@@ -225,13 +225,14 @@ int tb200_gqa_lse_merge_wait(const float* o_parts, const float* lse_parts, void*
  * d = seqlen_kv - seqlen_q, key j is visible to row i iff j >= i + d - window_left (when
  * window_left >= 0), j <= i + d + window_right (when window_right >= 0) and j <= i + d (when
  * causal); -1 = unlimited.  Key tiles outside the window of a whole row tile are skipped.
- * flags: 0, or TB200_PREFILL_ONE_TILE to keep the kernel with one Q tile per CTA where the kernel with two
- * Q tiles per CTA (head dim 128) would be chosen: the tuning surface of the reference's config=.
+ * flags: 0, or TB200_PREFILL_TWO_TILES to run the kernel with two Q tiles per CTA (head dim 128, dense;
+ * measured slower than the default kernel with one Q tile per CTA on B200, kept as a tuning variant): the
+ * tuning surface of the reference's config=.
  * workspace: tb200_gqa_prefill_workspace_bytes() bytes, zeroed once.  Its first int is a status word: 0, or
  * the code of a bounded device-side wait that ran out (1xx-3xx, 7xx); once set, later launches return at
  * once with their outputs unwritten until the word is cleared.
  * ------------------------------------------------------------------------- */
-#define TB200_PREFILL_ONE_TILE 1
+#define TB200_PREFILL_TWO_TILES 1
 
 size_t tb200_gqa_prefill_workspace_bytes(int batch, int heads, int heads_kv, int seqlen_q,
                                          int seqlen_kv, int dim);
@@ -331,6 +332,17 @@ int tb200_fp8_cache_append(const void* k_new, const void* v_new, void* k_pages, 
                            const int32_t* block_table, int64_t block_table_stride,
                            const float* k_scale, const float* v_scale, int dtype, int total_q,
                            int batch, int heads_kv, int dim, int page_size, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Tensor-pipe probe (no reference counterpart; a measuring aid of this library).  Every SM runs
+ * `repetitions` x 8 tcgen05.mma instructions (cta_group::1, kind::f16, M = 128, K = 16, N = n; A from shared
+ * memory, or from TMEM when a_in_tmem != 0) into one accumulator; SM 0 stores into out_clocks[0] the clocks
+ * until the last instruction was accepted and into out_clocks[1] the clocks until it completed (-1 if a
+ * bounded wait ran out).  Divide by 8 * repetitions for the cost of one instruction.  On B200 it is ~96
+ * clocks for n = 64 and n = 128 and 138-171 for n = 256, against 32 / 64 / 128 clocks of arithmetic: the
+ * number of MMA instructions per key, not their size, bounds the prefill kernels.
+ * ------------------------------------------------------------------------- */
+int tb200_mma_issue_probe(int64_t* out_clocks, int n, int a_in_tmem, int repetitions, void* stream);
 
 #ifdef __cplusplus
 }

@@ -191,3 +191,11 @@ def test_two_tile_and_one_tile_kernels_agree_with_the_oracle(B, Sq, Skv, H, Hkv,
     fin = torch.isfinite(outs[1][1])
     assert torch.equal(fin, torch.isfinite(outs[0][1]))
     torch.testing.assert_close(outs[0][1][fin], outs[1][1][fin], atol=2e-3, rtol=1e-3)
+
+
+def test_mma_issue_probe_reports_the_floor_the_kernels_are_designed_around():
+    """One tcgen05.mma (M = 128, K = 16) never costs less than its arithmetic (N / 2 clocks) and, on B200, not
+    less than ~90 clocks whatever N is."""
+    for n in (64, 128, 256):
+        issued, done = F.mma_issue_probe(n, a_in_tmem=(n == 128))
+        assert n / 2 <= done < 1000 and issued <= done + 1, (n, issued, done)

@@ -25,14 +25,14 @@ F16, BF16, E4M3, F32 = 0, 1, 2, 3
 # variant flags of tb200_gqa_decode (TB200_DECODE_* in include/tileops_b200.h)
 DECODE_WIDE_ON, DECODE_WIDE_OFF, DECODE_FP8_MMA, DECODE_NO_TMA = 1, 2, 4, 8
 DECODE_CHUNK_TILES_SHIFT = 8
-PREFILL_ONE_TILE = 1
+PREFILL_TWO_TILES = 1
 
 
 def prefill_flags(config: "dict | None") -> int:
-    """Variant flags of the prefill entry points from a kernel ``config`` dict: ``tiles_per_cta`` 1 keeps the
-    kernel with one Q tile per CTA (2, the default, lets the library use the ping-pong kernel)."""
-    if config and int(config.get("tiles_per_cta") or 2) == 1:
-        return PREFILL_ONE_TILE
+    """Variant flags of the prefill entry points from a kernel ``config`` dict: ``tiles_per_cta`` 2 asks for
+    the kernel with two Q tiles per CTA (head dim 128, dense); 1, the default, is the kernel with one."""
+    if config and int(config.get("tiles_per_cta") or 1) == 2:
+        return PREFILL_TWO_TILES
     return 0
 
 
@@ -114,6 +114,7 @@ SIGNATURES = {
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,      # k_pages v_pages k_new v_new k_out v_out
         c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,  # cu_q cu_kv cache bt stride k_scale v_scale
         c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),          # dtype total_kv B Hkv D page stream
+    "tb200_mma_issue_probe": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p]),
     "tb200_fp8_cache_append": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p,                         # k_new v_new k_pages v_pages
         c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,      # cu_q cache bt stride k_scale v_scale

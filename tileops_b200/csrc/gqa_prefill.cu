@@ -622,8 +622,8 @@ extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, vo
   p.is_causal = is_causal; p.sm_scale = sm_scale; p.softcap = softcap;
   p.win_left = window_left; p.win_right = window_right;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (!(flags & TB200_PREFILL_ONE_TILE)) {
-    // head dim 128: two Q tiles per CTA in ping-pong (gqa_prefill_pp.cu); it declines what it does not serve
+  if (flags & TB200_PREFILL_TWO_TILES) {
+    // head dim 128, on request: two Q tiles per CTA (gqa_prefill_pp.cu); it declines what it does not serve
     const int st2 = launch_prefill_pp(m, p, dtype, dim, false, s);
     if (st2 != kPrefillPpNotApplicable) return st2;
   }

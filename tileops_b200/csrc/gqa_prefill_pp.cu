@@ -1,26 +1,33 @@
-// Dense GQA prefill, head dim 128, sm_100a: two 128-row Q tiles per CTA in ping-pong on one tensor
-// pipe, 128-key tiles, single-pass softmax in registers, persistent grid.
+// Dense GQA prefill, head dim 128, sm_100a: two 128-row Q tiles per CTA on one tensor pipe, 128-key tiles,
+// single-pass softmax in registers, P handed to the second product through shared memory, persistent grid.
 //
 // Role in the reference: the same as gqa_prefill.cu (GQAPrefillFwdKernel,
 // src/tileops/kernels/attention/gqa_fwd.py:309-468,519-597 in tile-ai/TileOPs); the structure answers the
 // reference's persistent Hopper kernel with paired M tiles (gqa_fwd_ws.py:503-1030, tile pairing at
 // :634-642), rebuilt on tcgen05 / TMEM.
 //
-// One CTA per SM, 10 warps:
+// What shapes the design: on B200 a tcgen05.mma with M = 128, K = 16 occupies the tensor pipe for at least
+// ~96 clocks whatever N is (N = 64: 96, N = 128: 96-107, N = 256: 138-171; tb200_mma_issue_probe measures
+// it), so the number of MMA instructions per key, not their size, bounds the kernel.  The kernel of
+// gqa_prefill.cu (64-key tiles, N = 64 score products) issues 12 per 64 keys and runs at that bound;
+// 128-key tiles need 16 per 128 keys.  With 128-key tiles TMEM holds S and O of two Q tiles exactly once
+// (4 x 128 columns), so S cannot be double buffered; instead S is released early:
+//
+// One CTA per SM, 12 warps (the last two only complete the third warpgroup):
 //   warps 0-3  softmax of Q tile A (thread r owns row r = TMEM lane r)
 //   warps 4-7  softmax of Q tile B (the next 128 rows of the same batch element and q head)
 //   warp  8    MMA issuer (one lane) and TMEM allocator
-//   warp  9    TMA producer (one lane): both Q tiles once per work item, K_j / V_j into 2-stage rings
-// TMEM (all 512 columns): S_A [0,128) | S_B [128,256) | O_A [256,384) | O_B [384,512).  P (16-bit, 64
-// columns) overwrites the first half of its S.  The MMA lane issues, per 128-key tile j,
-//     PV_A(j), QK_A(j+1), PV_B(j), QK_B(j+1)
-// each pair as soon as that tile's P is ready: while the softmax warps of A work on S_A(j+1), the tensor
-// pipe runs B's pair, and vice versa.  One issuer orders all MMAs, and every K/V tile in shared memory
-// feeds both Q tiles.  A thread reads its whole 128-key score row from TMEM once (128 registers), takes
-// the row maximum, exponentiates in place and writes P back; O is rescaled only when a row maximum grew
-// by more than 2^8 (the final 1/l and the LSE use the same stale maximum, so the result is unchanged).
-// S_A(j+1) is committed after PV_A(j) in issue order, so a softmax warp that sees its S also knows that
-// the previous PV into its O has finished: the rescale needs no barrier of its own.
+//   warp  9    TMA producer (one lane): both Q tiles once per work item, K / V tiles into one 3-slot ring
+// TMEM (all 512 columns): S_A [0,128) | S_B [128,256) | O_A [256,384) | O_B [384,512).
+// A softmax thread reads its whole 128-key score row from TMEM once (128 registers) and at once arrives on
+// S_FREE: the MMA lane may then overwrite S with the NEXT tile's scores while this tile's row maximum,
+// exponentials and row sum are computed from registers.  P (16-bit) goes to a swizzled shared-memory tile
+// (the K-major A operand of O += P V), so the second product does not touch S either.  Per 128-key tile j
+// the MMA lane issues QK_A(j+1), QK_B(j+1), PV_A(j), PV_B(j): the score products run under the softmax of
+// the tile before, the PV products under the softmax of the tile after, and a softmax warp that finishes a
+// tile finds its next S ready.  O is rescaled only when a row maximum grew by more than 2^8 (the final 1/l
+// and the LSE use the same stale maximum, so the result is unchanged); the rescale waits for the previous
+// PV through the PV_DONE barrier, which also guards the reuse of the P tile.
 //
 // The grid is persistent (one CTA per SM); CTA c takes work items c, c + grid, ... of a list sorted
 // heaviest first (last row pairs first).  The TMA and MMA lanes run ahead into the next item (its Q and
@@ -36,26 +43,42 @@
 namespace tb200 {
 namespace {
 
-#ifndef TB200_PP_POLY
-#define TB200_PP_POLY 0      // of every 4 exponentials on unmasked tiles, this many run on the FMA pipe
+// Optional timeline for tuning (-DTB200_TRACE): CTA 0 stamps clock64() at the milestones of its MMA lane
+// (slots 10-13: score product and PV product issued, per tile) and of the first thread of each softmax
+// warpgroup (slots 0-4 and 5-9: S seen, S read, maximum done, exponentials done, P handed over) for the first
+// kTraceIters key tiles of its first work item into the workspace behind the status word.
+#ifdef TB200_TRACE
+constexpr int kTraceIters = 40, kTraceSlots = 14;
+#define TB200_PP_STAMP(slot, j)                                                                       \
+  do {                                                                                                \
+    if (blockIdx.x == 0 && item == int(blockIdx.x) && (j) < kTraceIters)                              \
+      reinterpret_cast<long long*>(p.status + 64)[(j) * kTraceSlots + (slot)] = clock64();            \
+  } while (0)
+#else
+#define TB200_PP_STAMP(slot, j) do {} while (0)
 #endif
 
 constexpr int kPM = 128;               // rows per Q tile
 constexpr int kPN = 128;               // keys per KV tile
 constexpr int kPD = 128;               // head dim
-constexpr int kPThreads = 320;
-constexpr int kPanel = 128 * 128;      // 128 rows x 128 B (64 head dims), swizzled
+constexpr int kPThreads = 384;
+constexpr int kLaunchRegs = 168;       // what ptxas grants 384 threads per CTA
+constexpr int kSoftmaxRegs = 224;      // softmax warpgroups after setmaxnreg.inc
+constexpr int kIssueRegs = 56;         // MMA / TMA warpgroup after setmaxnreg.dec
+static_assert(2 * kSoftmaxRegs + kIssueRegs <= 3 * kLaunchRegs, "setmaxnreg.inc would block forever");
+static_assert(kSoftmaxRegs % 8 == 0 && kIssueRegs % 8 == 0 && kIssueRegs >= 24 && kSoftmaxRegs <= 256, "setmaxnreg operand");
+constexpr int kPanel = 128 * 128;      // 128 rows x 128 B (64 head dims or 64 keys), swizzled
 constexpr int kTileBytes = 2 * kPanel; // 128 x 128 16-bit
-constexpr int kKvStages = 2;
+constexpr int kRing = 3;               // K / V tiles in flight: K_j+1, V_j and the next one
 struct PPSmem {
   static constexpr int q = 0;                                  // tile t, panel pn at (t * 2 + pn) * kPanel
-  static constexpr int k = q + 2 * kTileBytes;
-  static constexpr int v = k + kKvStages * kTileBytes;
-  static constexpr int bars = v + kKvStages * kTileBytes;
+  static constexpr int ring = q + 2 * kTileBytes;              // K_lo, K_lo+1, V_lo, K_lo+2, V_lo+1, ... round robin
+  static constexpr int pt = ring + kRing * kTileBytes;         // P of tile t (K-major: rows x 128 keys)
+  static constexpr int bars = pt + 2 * kTileBytes;
   static constexpr int total = bars + 256;
 };
-enum { PB_QFULL = 0, PB_QEMPTY = 1, PB_KFULL = 2, PB_KEMPTY = 4, PB_VFULL = 6, PB_VEMPTY = 8, PB_SFULL = 10,
-       PB_PREADY = 12, PB_OFINAL = 14, PB_COUNT = 16 };
+enum { PB_QFULL = 0, PB_QEMPTY = 1, PB_RFULL = 2, PB_REMPTY = 5, PB_SFULL = 8, PB_SFREE = 10, PB_PREADY = 12,
+       PB_PVDONE = 14, PB_OFINAL = 16, PB_COUNT = 18 };
 constexpr uint32_t kColSA = 0, kColOA = 256;   // tile t: S at 128 t, O at 256 + 128 t
 
 // One work item: a pair of Q tiles of one (batch element, q head), and the key tiles each of them sees.
@@ -97,11 +120,14 @@ __device__ __forceinline__ PPItem pp_item(const PrefillParams& p, int item) {
   return it;
 }
 
-// 10 warps x 192 registers fit the register file of an SM (registers are granted per warp in blocks of 512, so
-// 200 would not launch; a launch bound of 320 threads would be
-// rounded up to 384 and cap the kernel at 168, which spills the 128-register score row).
+// Registers: each of the four SM sub-partitions holds 16384 and hosts a quarter of the warps, so 12 warps
+// launch with 168 registers each.  The third warpgroup (MMA lane, TMA lane, two idle warps) then gives
+// registers back (setmaxnreg.dec) and the two softmax warpgroups take them (setmaxnreg.inc), which makes
+// room for the 128-register score row.  setmaxnreg.inc BLOCKS until the CTA's own pool - what it was
+// launched with, 3 x 168 per lane, not the SM's register file - has the registers, so the new counts must
+// add up to at most that (checked below), or the kernel would wait forever.
 template <typename T, bool kSoftcap>
-__global__ void __maxnreg__(192)
+__global__ void __launch_bounds__(kPThreads, 1)
 gqa_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, PrefillParams p, int total_items) {
   extern __shared__ unsigned char smem_raw[];
@@ -125,13 +151,15 @@ gqa_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   if (tid == 0) {
     mbar_init(bar(PB_QFULL), 1);
     mbar_init(bar(PB_QEMPTY), 1);
+    for (int s = 0; s < kRing; ++s) {
+      mbar_init(bar(PB_RFULL + s), 1);
+      mbar_init(bar(PB_REMPTY + s), 1);
+    }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(bar(PB_KFULL + s), 1);
-      mbar_init(bar(PB_KEMPTY + s), 1);
-      mbar_init(bar(PB_VFULL + s), 1);
-      mbar_init(bar(PB_VEMPTY + s), 1);
       mbar_init(bar(PB_SFULL + s), 1);
+      mbar_init(bar(PB_SFREE + s), 128);
       mbar_init(bar(PB_PREADY + s), 128);
+      mbar_init(bar(PB_PVDONE + s), 1);
       mbar_init(bar(PB_OFINAL + s), 1);
     }
     *s_abort = 0;
@@ -148,15 +176,21 @@ gqa_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   constexpr uint32_t idesc_qk = make_idesc(fmt, 0, kPN);
+  // (An MMA whose A and B element formats differ - f16 P against bf16 V - is an illegal instruction on
+  // sm_100a: P always has the type of V.)
+  constexpr bool kHalfP = std::is_same<T, __half>::value;
   constexpr uint32_t idesc_pv = make_idesc(fmt, 1, kPD);
 
-  if (warp == 9) {
+  if (warp >= 8) {
+    // third warpgroup: TMA lane, MMA lane and two idle warps (a register hand-over needs whole warpgroups)
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kIssueRegs));
+   if (warp == 9) {
     // ================= TMA producer =================
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
-      uint32_t nq = 0, kc = 0, vc = 0;
+      uint32_t nq = 0, rc = 0;                     // work items and ring tiles loaded so far
       bool ok = true;
       for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
         const PPItem it = pp_item(p, item);
@@ -170,99 +204,95 @@ gqa_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             tma_load_4d(sbase + PPSmem::q + (t * 2 + pn) * kPanel, &map_q, bar(PB_QFULL), pn * 64, it.h, it.m0[t], it.b);
         ++nq;
         // a 128-key tile is two 64-row boxes per 64-dim panel (the maps describe 64-row boxes)
-        auto load_tile = [&](uint32_t dst, const CUtensorMap* map, uint32_t full_bar, int j) {
+        auto load_tile = [&](const CUtensorMap* map, int j) -> bool {
+          const int slot = rc % kRing;
+          if (!wait(PB_REMPTY + slot, ((rc / kRing) & 1) ^ 1, 702)) return false;
+          mbar_expect_tx(bar(PB_RFULL + slot), kTileBytes);
+          const uint32_t dst = sbase + PPSmem::ring + slot * kTileBytes;
 #pragma unroll
           for (int pn = 0; pn < 2; ++pn)
 #pragma unroll
             for (int r = 0; r < 2; ++r)
-              tma_load_4d(dst + pn * kPanel + r * 64 * 128, map, full_bar, pn * 64, it.hk, j * kPN + r * 64, it.b);
+              tma_load_4d(dst + pn * kPanel + r * 64 * 128, map, bar(PB_RFULL + slot), pn * 64, it.hk, j * kPN + r * 64, it.b);
+          ++rc;
+          return true;
         };
+        // the order the MMA lane consumes them in: K_lo, then K_j+1 and V_j for every tile j
+        if (!load_tile(&map_k, it.jlo)) break;
         for (int j = it.jlo; j < it.jhi; ++j) {
-          const int ks = kc & 1, vs = vc & 1;
-          if (!wait(PB_KEMPTY + ks, ((kc >> 1) & 1) ^ 1, 702)) { ok = false; break; }
-          mbar_expect_tx(bar(PB_KFULL + ks), kTileBytes);
-          load_tile(sbase + PPSmem::k + ks * kTileBytes, &map_k, bar(PB_KFULL + ks), j);
-          ++kc;
-          if (!wait(PB_VEMPTY + vs, ((vc >> 1) & 1) ^ 1, 703)) { ok = false; break; }
-          mbar_expect_tx(bar(PB_VFULL + vs), kTileBytes);
-          load_tile(sbase + PPSmem::v + vs * kTileBytes, &map_v, bar(PB_VFULL + vs), j);
-          ++vc;
+          if (j + 1 < it.jhi && !load_tile(&map_k, j + 1)) { ok = false; break; }
+          if (!load_tile(&map_v, j)) { ok = false; break; }
         }
       }
     }
   } else if (warp == 8) {
     // ================= MMA issuer =================
     if (lane == 0) {
-      uint32_t nq = 0, kc = 0, vc = 0, pc[2] = {0, 0};
+      uint32_t nq = 0, rc = 0;                     // work items and ring tiles consumed so far
+      uint32_t qk_n[2] = {0, 0}, pv_n[2] = {0, 0}; // score products and PV products issued so far, per Q tile
       const uint64_t dq0 = make_desc(sbase + PPSmem::q, 16, 1024);
-      const uint64_t dk0 = make_desc(sbase + PPSmem::k, 16, 1024);
-      const uint64_t dv0 = make_desc(sbase + PPSmem::v, kPanel, 1024);
-      constexpr uint64_t kTileStep = kTileBytes >> 4;      // next tile / stage, in start-address units
+      const uint64_t dp0 = make_desc(sbase + PPSmem::pt, 16, 1024);
+      constexpr uint64_t kTileStep = kTileBytes >> 4;      // next tile / slot, in start-address units
       bool ok = true;
       for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
         const PPItem it = pp_item(p, item);
         if (it.jhi <= it.jlo) continue;
-        // S_t = Q_t K^T from K stage ks
-        auto issue_qk = [&](int t, int ks) {
+        // S_t(j) = Q_t K_j^T for the tiles that see key tile j; K_j is the ring's next tile
+        auto issue_qk = [&](int j) -> bool {
+          const int slot = rc % kRing;
+          if (!wait(PB_RFULL + slot, (rc / kRing) & 1, 712)) return false;
+          const uint64_t dk = make_desc(sbase + PPSmem::ring + slot * kTileBytes, 16, 1024);
 #pragma unroll
-          for (int kk = 0; kk < kPD / 16; ++kk) {
-            // K-major operands: 16 elements per step = 32 B inside the 128 B swizzled row; after 4
-            // steps the second 64-element panel (16 KB further)
-            const uint32_t o = ((kk >> 2) * kPanel + (kk & 3) * 32) >> 4;
-            tc_mma_ss(tmem + kColSA + t * kPN, dq0 + t * kTileStep + o, dk0 + ks * kTileStep + o, idesc_qk, kk > 0 ? 1u : 0u);
+          for (int t = 0; t < 2; ++t) {
+            if (j < it.lo[t] || j >= it.hi[t]) continue;
+            // the softmax warps must have read the previous scores of this tile out of TMEM
+            if (qk_n[t] > 0 && !wait(PB_SFREE + t, (qk_n[t] - 1) & 1, 713)) return false;
+            ++qk_n[t];
+            tc_fence_after();
+            // K-major operands: 16 elements per step = 32 B inside the 128 B swizzled row; after 4 steps the
+            // second 64-element panel (16 KB further)
+            tc_mma_ss_x8<(kPanel >> 4), (kPanel >> 4)>(tmem + kColSA + t * kPN, dq0 + t * kTileStep, dk, idesc_qk);
+            tc_commit(bar(PB_SFULL + t));
+            TB200_PP_STAMP(10 + 2 * t, j - it.jlo);
           }
-          tc_commit(bar(PB_SFULL + t));
+          tc_commit(bar(PB_REMPTY + slot));
+          ++rc;
+          if (j + 1 == it.jhi) tc_commit(bar(PB_QEMPTY));     // the last score products of the item are issued
+          return true;
         };
         if (!wait(PB_QFULL, nq & 1, 711)) break;
         ++nq;
-        {
-          // first key tile of the item
-          const int ks = kc & 1;
-          if (!wait(PB_KFULL + ks, (kc >> 1) & 1, 712)) break;
-          tc_fence_after();
-#pragma unroll
-          for (int t = 0; t < 2; ++t)
-            if (it.jlo >= it.lo[t] && it.jlo < it.hi[t]) issue_qk(t, ks);
-          tc_commit(bar(PB_KEMPTY + ks));
-          ++kc;
-          if (it.jlo + 1 == it.jhi) tc_commit(bar(PB_QEMPTY));
-        }
+        if (!issue_qk(it.jlo)) break;
         for (int j = it.jlo; ok && j < it.jhi; ++j) {
-          const int vs = vc & 1, ks = kc & 1;
-          const bool more = j + 1 < it.jhi;
-          if (!wait(PB_VFULL + vs, (vc >> 1) & 1, 713)) { ok = false; break; }
-          if (more && !wait(PB_KFULL + ks, (kc >> 1) & 1, 714)) { ok = false; break; }
-          tc_fence_after();
+          if (j + 1 < it.jhi && !issue_qk(j + 1)) { ok = false; break; }
+          // O_t += P_t(j) V_j; V_j is the ring's next tile
+          const int slot = rc % kRing;
+          if (!wait(PB_RFULL + slot, (rc / kRing) & 1, 714)) { ok = false; break; }
+          const uint64_t dv = make_desc(sbase + PPSmem::ring + slot * kTileBytes, kPanel, 1024);
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
-            if (j >= it.lo[t] && j < it.hi[t]) {
-              if (!wait(PB_PREADY + t, pc[t] & 1, 715)) { ok = false; break; }
-              ++pc[t];
-              tc_fence_after();
-#pragma unroll
-              for (int kk = 0; kk < kPN / 16; ++kk) {
-                // B = V: MN-major, 16 keys per step = 16 rows of 128 B; the two 64-wide d panels are
-                // kPanel apart (leading offset), 8-row groups 1024 B apart (stride offset)
-                tc_mma_ts(tmem + kColOA + t * kPD, tmem + kColSA + t * kPN + kk * 8,
-                          dv0 + vs * kTileStep + ((kk * 2048) >> 4), idesc_pv, (j > it.lo[t] || kk > 0) ? 1u : 0u);
-              }
-              if (j == it.hi[t] - 1) tc_commit(bar(PB_OFINAL + t));
-            }
-            if (more && j + 1 >= it.lo[t] && j + 1 < it.hi[t]) issue_qk(t, ks);
+            if (j < it.lo[t] || j >= it.hi[t]) continue;
+            if (!wait(PB_PREADY + t, pv_n[t] & 1, 715)) { ok = false; break; }
+            ++pv_n[t];
+            tc_fence_after();
+            // A = P (K-major, like Q); B = V: MN-major, 16 keys per step = 16 rows of 128 B; the two 64-wide d
+            // panels are kPanel apart (leading offset), 8-row groups 1024 B apart (stride offset)
+            tc_mma_ss_pv_x8<(kPanel >> 4), (2048 >> 4)>(tmem + kColOA + t * kPD, dp0 + t * kTileStep, dv, idesc_pv,
+                                                        j > it.lo[t] ? 1u : 0u);
+            tc_commit(bar(PB_PVDONE + t));
+            if (j == it.hi[t] - 1) tc_commit(bar(PB_OFINAL + t));
+            TB200_PP_STAMP(11 + 2 * t, j - it.jlo);
           }
           if (!ok) break;
-          tc_commit(bar(PB_VEMPTY + vs));
-          ++vc;
-          if (more) {
-            tc_commit(bar(PB_KEMPTY + ks));
-            ++kc;
-            if (j + 2 == it.jhi) tc_commit(bar(PB_QEMPTY));   // the last QKs of the item are issued
-          }
+          tc_commit(bar(PB_REMPTY + slot));
+          ++rc;
         }
       }
     }
+   }
   } else {
     // ================= softmax / rescale / epilogue (thread = row of tile t) =================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
     const int t = warp >> 2;                                // 0: tile A, 1: tile B
     const int row = tid & 127;                              // == TMEM lane
     const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;
@@ -274,7 +304,7 @@ gqa_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int off = p.seqlen_kv - p.seqlen_q;
     const bool has_upper = p.is_causal || p.win_right >= 0;
     const int up_extra = p.is_causal ? 0 : p.win_right;
-    uint32_t cs = 0, co = 0;
+    uint32_t cs = 0, co = 0, pw = 0;                        // S tiles read, outputs written, P tiles written so far
     bool ok = true;
 
     for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
@@ -302,6 +332,7 @@ gqa_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (!__all_sync(0xffffffffu, wait(PB_SFULL + t, cs & 1, 721))) { ok = false; break; }
         ++cs;
         tc_fence_after();
+        if (row == 0) TB200_PP_STAMP(5 * t + 0, j - it.jlo);
         const int k0 = j * kPN;
         const bool need_mask = (has_upper && k0 + kPN - 1 > m0 + off + up_extra) || (k0 + kPN > p.seqlen_kv) ||
                                (p.win_left >= 0 && k0 < m0 + kPM - 1 + off - p.win_left);
@@ -310,6 +341,10 @@ gqa_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         for (int cg = 0; cg < 4; ++cg) tc_ld32(s_addr + cg * 32, s[cg]);
 #pragma unroll
         for (int cg = 0; cg < 4; ++cg) tc_wait_ld(s[cg]);
+        // the scores are in registers: S may be overwritten with the next tile's
+        tc_fence_before();
+        mbar_arrive(bar(PB_SFREE + t));
+        if (row == 0) TB200_PP_STAMP(5 * t + 1, j - it.jlo);
         if (kSoftcap) {
 #pragma unroll
           for (int cg = 0; cg < 4; ++cg)
@@ -338,12 +373,16 @@ gqa_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         // ---- does the running maximum move (and O have to be rescaled)? ----
         const float m_new = fmaxf(m_run, mx);
         const bool grow = (m_new - m_run) * c > kRescaleThreshold || (m_run == -INFINITY && m_new != -INFINITY);
+        bool pv_waited = false;
         if (__any_sync(0xffffffffu, grow)) {
           // 1 for a row that still has seen no key (avoids inf - inf), 0 for a row seeing its first
           const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2((m_run - m_new) * c);
           l_run *= alpha;
           if (j > it.lo[t]) {
-            // PV(j-1) has finished: S(j) was committed behind it
+            // the previous PV of this tile may still be adding into O
+            if (!__all_sync(0xffffffffu, wait(PB_PVDONE + t, (pw - 1) & 1, 723))) { ok = false; break; }
+            pv_waited = true;
+            tc_fence_after();
 #pragma unroll
             for (int cg = 0; cg < kPD / 32; ++cg) {
               uint32_t ov[32];
@@ -353,41 +392,54 @@ gqa_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
               for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
               tc_st32(o_addr + cg * 32, ov);
             }
+            tc_wait_st();
           }
           m_run = m_new;
         }
         const float neg_mc = (m_run == -INFINITY) ? 0.f : -m_run * c;
+        if (row == 0) TB200_PP_STAMP(5 * t + 2, j - it.jlo);
 
-        // ---- p = 2^(s*c - m*c), row sum, P (16-bit) over the first 64 columns of S ----
-        uint64_t lsum_a = 0, lsum_b = 0;                    // two (even key, odd key) pairs of partial sums
-        const uint64_t c2 = f2_pack(c, c), neg_mc2 = f2_pack(neg_mc, neg_mc);
-        const bool poly_ok = TB200_PP_POLY > 0 && !need_mask;   // the polynomial needs finite inputs
+        // ---- p = 2^(s*c - m*c), row sum; P (16-bit) stays in registers until its shared-memory tile is free ----
+        uint32_t pk[4][16];
+        {
+          uint64_t lsum_a = 0, lsum_b = 0;                    // two (even key, odd key) pairs of partial sums
+          const uint64_t c2 = f2_pack(c, c), neg_mc2 = f2_pack(neg_mc, neg_mc);
 #pragma unroll
-        for (int cg = 0; cg < 4; ++cg) {
-          uint32_t pk[16];
+          for (int cg = 0; cg < 4; ++cg)
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            float x0, x1;
-            f2_unpack(f2_fma(f2_pack(__uint_as_float(s[cg][2 * e]), __uint_as_float(s[cg][2 * e + 1])), c2, neg_mc2), x0, x1);
-            float p0, p1;
-            if (TB200_PP_POLY > 0 && (e & 1) == 1 && poly_ok) {
-              p0 = (TB200_PP_POLY >= 2) ? exp2_poly(x0) : fast_exp2(x0);
-              p1 = exp2_poly(x1);
-            } else {
-              p0 = fast_exp2(x0);
-              p1 = fast_exp2(x1);
+            for (int e = 0; e < 16; ++e) {
+              float x0, x1;
+              f2_unpack(f2_fma(f2_pack(__uint_as_float(s[cg][2 * e]), __uint_as_float(s[cg][2 * e + 1])), c2, neg_mc2), x0, x1);
+              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              if (e & 1) lsum_b = f2_add(lsum_b, f2_pack(p0, p1)); else lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
+              pk[cg][e] = pack2<T>(p0, p1);
             }
-            if (e & 1) lsum_b = f2_add(lsum_b, f2_pack(p0, p1)); else lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
-            pk[e] = pack2<T>(p0, p1);
-          }
-          tc_st16(s_addr + cg * 16, pk);
+          float lsum0, lsum1;
+          f2_unpack(f2_add(lsum_a, lsum_b), lsum0, lsum1);
+          l_run += lsum0 + lsum1;
         }
-        float lsum0, lsum1;
-        f2_unpack(f2_add(lsum_a, lsum_b), lsum0, lsum1);
-        l_run += lsum0 + lsum1;
-        tc_wait_st();
-        tc_fence_before();
+        if (row == 0) TB200_PP_STAMP(5 * t + 3, j - it.jlo);
+        // the PV product that read the previous P of this tile must be done before the tile is rewritten
+        if (pw > 0 && !pv_waited) {
+          if (!__all_sync(0xffffffffu, wait(PB_PVDONE + t, (pw - 1) & 1, 724))) { ok = false; break; }
+        }
+        ++pw;
+        {
+          // row r of the K-major P tile: 128 B per 64-key panel, 16-byte chunk c at (c ^ (r & 7)) * 16
+          unsigned char* prow = smem + PPSmem::pt + t * kTileBytes + row * 128;
+          const int x = row & 7;
+#pragma unroll
+          for (int cg = 0; cg < 4; ++cg)
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              const int chunk = cg * 4 + q4;                  // 8 keys per chunk, 16 chunks per row
+              *reinterpret_cast<uint4*>(prow + (chunk >> 3) * kPanel + (((chunk & 7) ^ x) << 4)) =
+                  make_uint4(pk[cg][q4 * 4], pk[cg][q4 * 4 + 1], pk[cg][q4 * 4 + 2], pk[cg][q4 * 4 + 3]);
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores, read by the MMA's async proxy
         mbar_arrive(bar(PB_PREADY + t));
+        if (row == 0) TB200_PP_STAMP(5 * t + 4, j - it.jlo);
       }
       if (!ok) break;
 

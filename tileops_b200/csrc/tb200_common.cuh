@@ -140,6 +140,27 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+// Two exponentials per MUFU instruction: the pair is rounded to f16 (11 significant bits: for |x| < 8
+// an absolute error below 2^-8 in x, i.e. below 0.3 % in 2^x), and 2^x comes back as an f16 pair.
+// -inf and anything below the f16 range give +0.
+__device__ __forceinline__ uint32_t f32x2_to_f16x2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
+  uint32_t y;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t add_f16x2(uint32_t a, uint32_t b) {
+  uint32_t y;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
+  return y;
+}
+__device__ __forceinline__ float2 f16x2_to_f32x2(uint32_t h) {
+  return __half22float2(*reinterpret_cast<__half2*>(&h));
+}
 // 2^x on the FMA and integer pipes (no MUFU): floor by a round-down add of 1.5*2^23, a cubic for
 // 2^frac on [0,1), then the integer part is added to the exponent field.  Relative error about
 // 1e-4 (well under bf16 resolution).  x is clamped at -127, so very negative inputs (and -inf)

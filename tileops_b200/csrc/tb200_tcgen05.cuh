@@ -34,6 +34,73 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Eight MMAs of one 128-deep contraction in a single asm block, so that the issuing lane spends three
+// instructions per MMA (two address adds and the MMA) instead of a compiler-scheduled sequence per call:
+// with two busy softmax warps on the same scheduler every extra instruction of the issuing lane waits for
+// an issue slot, and the tensor pipe idles between MMAs.
+//   tc_mma_ss_x8: D[tmem] = A[smem] B[smem] over 8 k-steps of 16 elements; both operands K-major with 128 B
+//   rows: step kk sits (kk & 3) * 32 B into the row and (kk >> 2) panels further (A_PANEL / B_PANEL are the
+//   panel sizes in descriptor units, bytes >> 4).  The first step overwrites D, the rest accumulate.
+template <uint32_t A_PANEL, uint32_t B_PANEL>
+__device__ __forceinline__ void tc_mma_ss_x8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 a, b;\n\t"
+      "setp.ne.b32 p0, %3, %3;\n\tsetp.eq.b32 p1, %3, %3;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p0;\n\t"
+      "add.s64 a, %1, 2;\n\tadd.s64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+      "add.s64 a, %1, 4;\n\tadd.s64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+      "add.s64 a, %1, 6;\n\tadd.s64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+      "add.s64 a, %1, %4;\n\tadd.s64 b, %2, %5;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+      "add.s64 a, %1, %6;\n\tadd.s64 b, %2, %7;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+      "add.s64 a, %1, %8;\n\tadd.s64 b, %2, %9;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+      "add.s64 a, %1, %10;\n\tadd.s64 b, %2, %11;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(A_PANEL), "n"(B_PANEL), "n"(A_PANEL + 2), "n"(B_PANEL + 2),
+        "n"(A_PANEL + 4), "n"(B_PANEL + 4), "n"(A_PANEL + 6), "n"(B_PANEL + 6)
+      : "memory");
+}
+//   tc_mma_ts_x8: D[tmem] (+)= A[tmem] B[smem] over 8 k-steps of 16 keys: A (16-bit P) advances 8 columns per
+//   step, B (V, MN-major) B_STEP descriptor units (16 rows of 128 B = 128).  `accumulate` applies to the
+//   first step; the rest accumulate.
+template <uint32_t B_STEP>
+__device__ __forceinline__ void tc_mma_ts_x8(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+      "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 p1, %3, %3;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+      "add.u32 a, %1, 8;\n\tadd.s64 b, %2, %5;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, p1;\n\t"
+      "add.u32 a, %1, 16;\n\tadd.s64 b, %2, %6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, p1;\n\t"
+      "add.u32 a, %1, 24;\n\tadd.s64 b, %2, %7;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, p1;\n\t"
+      "add.u32 a, %1, 32;\n\tadd.s64 b, %2, %8;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, p1;\n\t"
+      "add.u32 a, %1, 40;\n\tadd.s64 b, %2, %9;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, p1;\n\t"
+      "add.u32 a, %1, 48;\n\tadd.s64 b, %2, %10;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, p1;\n\t"
+      "add.u32 a, %1, 56;\n\tadd.s64 b, %2, %11;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, p1;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "n"(B_STEP), "n"(2 * B_STEP), "n"(3 * B_STEP),
+        "n"(4 * B_STEP), "n"(5 * B_STEP), "n"(6 * B_STEP), "n"(7 * B_STEP)
+      : "memory");
+}
+//   tc_mma_ss_pv_x8: D[tmem] (+)= A[smem] B[smem] over 8 k-steps of 16 keys, for O += P V with P in shared
+//   memory: A (P, K-major, 128 B rows) advances like the A operand above, B (V, MN-major) B_STEP descriptor
+//   units per step.  `accumulate` applies to the first step; the rest accumulate.
+template <uint32_t A_PANEL, uint32_t B_STEP>
+__device__ __forceinline__ void tc_mma_ss_pv_x8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t.reg .b64 a, b;\n\t"
+      "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 p1, %3, %3;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p0;\n\t"
+      "add.s64 a, %1, 2;\n\tadd.s64 b, %2, %5;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+      "add.s64 a, %1, 4;\n\tadd.s64 b, %2, %6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+      "add.s64 a, %1, 6;\n\tadd.s64 b, %2, %7;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+      "add.s64 a, %1, %12;\n\tadd.s64 b, %2, %8;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+      "add.s64 a, %1, %13;\n\tadd.s64 b, %2, %9;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+      "add.s64 a, %1, %14;\n\tadd.s64 b, %2, %10;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t"
+      "add.s64 a, %1, %15;\n\tadd.s64 b, %2, %11;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, p1;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "n"(B_STEP), "n"(2 * B_STEP), "n"(3 * B_STEP),
+        "n"(4 * B_STEP), "n"(5 * B_STEP), "n"(6 * B_STEP), "n"(7 * B_STEP), "n"(A_PANEL), "n"(A_PANEL + 2),
+        "n"(A_PANEL + 4), "n"(A_PANEL + 6)
+      : "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "

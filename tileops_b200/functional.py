@@ -409,3 +409,18 @@ def gqa_prefill_paged_fp8_cache(q: torch.Tensor, k_new: torch.Tensor, v_new: tor
             v_scale.data_ptr(), N.dtype_code(q.dtype), total_q, B, Hkv, D, int(page_size), stream)
         N.check(st, "tb200_fp8_cache_append")
     return o
+
+
+def mma_issue_probe(n: int = 128, a_in_tmem: bool = False, repetitions: int = 200, device=None) -> "tuple[float, float]":
+    """Clocks one ``tcgen05.mma`` (M = 128, K = 16, N = ``n``) takes to be accepted / to complete on the
+    tensor pipe of ``device`` (``tb200_mma_issue_probe``; synchronises)."""
+    dev = _device_of(device)
+    out = torch.zeros(2, dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev):
+        st = N.lib().tb200_mma_issue_probe(out.data_ptr(), int(n), int(bool(a_in_tmem)), int(repetitions),
+                                           N.current_stream(dev))
+    N.check(st, "tb200_mma_issue_probe")
+    issued, done = (int(x) for x in out.cpu())
+    if done < 0:
+        raise N.NativeLibraryError("tb200_mma_issue_probe: the bounded wait for the last MMA ran out")
+    return issued / (8.0 * repetitions), done / (8.0 * repetitions)

@@ -51,11 +51,11 @@ class GQAPrefillSm100Kernel(Kernel):
 
     @property
     def default_config(self) -> dict:
-        """``tiles_per_cta`` is the one entry a caller may set: 2 (default) lets head dim 128 run the kernel
-        with two Q tiles per CTA in ping-pong (128-key tiles, 320 threads, persistent grid); 1 keeps the
-        kernel with one Q tile per CTA (64-key tiles, 192 threads, two CTAs per SM), which also serves head
-        dims 64 and 256.  The other entries describe the latter."""
-        return {"block_M": 128, "block_N": 64, "threads": 192, "tiles_per_cta": 2}
+        """``tiles_per_cta`` is the one entry a caller may set: 1 (default) is the kernel with one Q tile per
+        CTA (64-key tiles, 192 threads, two CTAs per SM; every head dim); 2 asks for the kernel with two Q
+        tiles per CTA (head dim 128: 128-key tiles, 384 threads, persistent grid), which measured slower on
+        B200 and is kept as a tuning variant.  The other entries describe the default kernel."""
+        return {"block_M": 128, "block_N": 64, "threads": 192, "tiles_per_cta": 1}
 
     def forward(self, q, k, v, cu_seqlens_q=None, cu_seqlens_kv=None, q_scale=None, k_scale=None,
                 v_scale=None, return_lse: bool = False):
@@ -168,7 +168,7 @@ class GQASlidingWindowSm100Kernel(Kernel):
 
     @property
     def default_config(self) -> dict:
-        return {"block_M": 128, "block_N": 64, "threads": 192, "tiles_per_cta": 2}
+        return {"block_M": 128, "block_N": 64, "threads": 192, "tiles_per_cta": 1}
 
     def forward(self, q, k, v):
         self._require_cuda(q=q, k=k, v=v)
