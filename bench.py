@@ -326,8 +326,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="long-context sharded step: eager launches instead of a CUDA graph")
     ap.add_argument("--nccl-exchange", action="store_true", help="long-context sharded step: NCCL all-gather instead of the fused exchange")
     ap.add_argument("--case", default=None,
-                    choices=["decode_small", "decode_fp8_small", "prefill_small", "prefill_paged", "rope_small",
-                             "fp8_cache_small", "merge_small", "mma_issue"],
+                    choices=["decode_small", "decode_fp8_small", "prefill_small", "prefill_two_tile_small", "prefill_paged",
+                             "rope_small", "fp8_cache_small", "merge_small", "mma_issue"],
                     help="run only a reduced case of one kernel (a few hundred MB on the device: the "
                          "size an ncu capture of all sections can handle) and print its timing")
     a = ap.parse_args()
@@ -476,6 +476,11 @@ def run_small_case(case: str, steps: int, warmup: int):
         lse_parts = torch.randn(parts, rows, device=device)
         fn = lambda: F.gqa_lse_merge(o_parts, lse_parts, torch.bfloat16)  # noqa: E731
         work, unit = parts * rows * (D + 1) * 4 + rows * D * 2, "GB/s"
+    elif case == "prefill_two_tile_small":
+        # the opt-in prefill kernel with two Q tiles per CTA, same inputs as prefill_small
+        q, k, v = W.make_prefill(2, 1, 4096, 4096, 32, 8, 128, torch.bfloat16, device)
+        fn = lambda: F.gqa_prefill(q, k, v, is_causal=True, config={"tiles_per_cta": 2})  # noqa: E731
+        work, unit = 4 * 32 * 4096 * 4096 * 128 // 2, "TFLOP/s"
     else:
         q, k, v = W.make_prefill(2, 1, 4096, 4096, 32, 8, 128, torch.bfloat16, device)
         op = GroupedQueryAttentionFwdOp(1, 32, 8, 4096, 128, is_causal=True)

@@ -12,8 +12,8 @@
 //   * warp 4 owns the shared-memory ring: per 64-token tile it issues one TMA box per 128-byte panel
 //     of K and of V (swizzled, no padding), waits only for a free stage, and walks the CTA's items
 //     back to back, so the next item's first tiles are in flight while the math warps finish the
-//     current one; it also pulls the item ids, copies the item's q rows into shared memory and reads
-//     the block-table entries (32 tiles per global read, one lane each);
+//     current one; it also copies each item's q rows into shared memory and reads the block-table
+//     entries (32 tiles per global read, one lane each);
 //   * warps 0-3 are the math warps of gqa_decode.cu (tokens on the MMA M dimension, q heads on N = 8,
 //     mma.sync.m16n8k16, movmatrix for P^T, FP8 expanded with cvt.rn.f16x2.e4m3x2), without a single
 //     load instruction or address computation for K/V; stages are handed over with mbarriers, one
@@ -25,6 +25,10 @@
 // Rows of the last tile behind the sequence end are whatever the pool holds: their scores are
 // replaced by -inf, and their V rows are zeroed in shared memory by the warp that owns them before
 // it reads them (0 x NaN would be NaN).
+//
+// Work is not pulled from a queue: the tiles of all (sequence, KV head) pairs are cut into one equal
+// contiguous range per CTA (stream-K, see segment_at below), which balances ragged batches to one tile,
+// needs no cost model, no atomics and almost no plan code, and makes the result bit-reproducible.
 //
 // Every wait is bounded (the math warps also meet at an mbarrier, not at a hardware barrier); when
 // one runs out the CTA records a code in counters[2] (601 producer, 602 math warps waiting for data,
@@ -49,7 +53,7 @@ namespace {
 #endif
 
 constexpr int kTmaThreads = kThreads + 32;   // 4 math warps + the producer warp
-constexpr int kItemSlots = 2;                // item descriptors (id + q rows) the producer may post ahead
+constexpr int kItemSlots = 2;                // q rows of the segments the producer may post ahead
 constexpr int kMathBarrier = 1;              // named barrier of the 128 math threads (plan only: nothing can give up there)
 
 template <int D, bool FP8>
@@ -86,6 +90,97 @@ size_t tma_smem_bytes(int batch) {
   return size_t(TmaCfg<D, FP8>::plan) + size_t(2 * batch + 1) * 4 + 1024;   // + alignment slack
 }
 
+// ---- work partition (stream-K) ---------------------------------------------------------------
+// A unit is one 64-token tile of one (sequence, KV head, head block) "lane"; units are numbered lane by
+// lane (sequence-major), tile by tile.  The T units are cut into equal contiguous ranges, one per CTA
+// (range k belongs to CTA k % grid; there is more than one per CTA only when a fixed run length is asked
+// for): every CTA gets the same number of tiles to within one, whatever the lengths are, and no CTA ever
+// asks a global counter for work.  A range cuts a lane into "segments": a segment that is a whole lane
+// writes the output directly; the segments of a lane that several ranges share leave partial (O, max, sum)
+// in a slot of their range (2 slots per range: its first segment and its last are the only ones that can
+// be partial) and the last one to finish merges them, as in gqa_decode.cu.  The partition is a pure
+// function of the lengths, so the producer warp and the math warps walk it independently, and the result
+// is bit-reproducible.
+struct Segment {
+  int b, hk, hbi, rem, len;
+  int tile0, tile1;          // tiles of the lane this segment covers
+  int n_runs, first_range;   // ranges that share the lane, and the first of them
+  int slot;                  // partial-result slot of this segment
+  int lane;                  // b * lanes + rem: the lane's ticket
+  unsigned lane_start;       // first unit of the lane
+  unsigned next;             // first unit behind the segment
+};
+__device__ __forceinline__ Segment segment_at(const DecodeParams& p, unsigned u, unsigned range_begin, unsigned range_end,
+                                              int range, unsigned per, const int* s_prefix, const int* s_lens,
+                                              int lanes) {
+  Segment g;
+  int lo = 0, hi = p.batch - 1;  // the sequence that holds unit u: largest b with lanes * prefix[b] <= u
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (unsigned(s_prefix[mid]) * unsigned(lanes) <= u) lo = mid; else hi = mid - 1;
+  }
+  g.b = lo;
+  g.len = max(s_lens[lo], 0);
+  const unsigned tiles_b = unsigned(s_prefix[lo + 1] - s_prefix[lo]);
+  const unsigned local = u - unsigned(s_prefix[lo]) * unsigned(lanes);
+  g.rem = int(local / tiles_b);
+  const unsigned t = local - unsigned(g.rem) * tiles_b;
+  g.hk = g.rem / p.n_hb;
+  g.hbi = g.rem - g.hk * p.n_hb;
+  g.lane = lo * lanes + g.rem;
+  g.lane_start = u - t;
+  const unsigned lane_end = g.lane_start + tiles_b;
+  g.next = min(range_end, lane_end);
+  g.tile0 = int(t);
+  g.tile1 = int(t + (g.next - u));
+  g.first_range = int(g.lane_start / per);
+  g.n_runs = int((lane_end - 1) / per) - g.first_range + 1;
+  g.slot = 2 * range + (u == range_begin ? 0 : 1);
+  return g;
+}
+// Slot of the segment that range k contributes to the lane starting at lane_start: the range's first
+// segment when the lane holds the range's first unit, else its last.
+__device__ __forceinline__ int segment_slot(int k, unsigned per, unsigned lane_start) {
+  return 2 * k + (unsigned(k) * per >= lane_start ? 0 : 1);
+}
+
+// Exclusive scan of the tile counts: s_prefix[0..batch], and the lengths in s_lens.  Called by the 128 math
+// threads; `sync` is a barrier over exactly those.
+template <typename Sync>
+__device__ __forceinline__ void tile_prefix_plan(const DecodeParams& p, int tid, int* s_prefix, int* s_lens,
+                                                 int* s_warp_sums, Sync sync) {
+  const int lane = tid & 31, warp = tid >> 5;
+  const int per = (p.batch + kThreads - 1) / kThreads;
+  const int b0 = tid * per;
+  int sum = 0;
+  for (int i = 0; i < per; ++i) {
+    const int b = b0 + i;
+    if (b < p.batch) {
+      const int len = p.lens ? p.lens[b] : p.uniform_len;
+      s_lens[b] = len;
+      sum += (max(len, 0) + kTile - 1) / kTile;
+    }
+  }
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  if (lane == 31) s_warp_sums[warp] = incl;
+  sync();
+  int run = incl - sum;
+  for (int w = 0; w < warp; ++w) run += s_warp_sums[w];
+  for (int i = 0; i < per; ++i) {
+    const int b = b0 + i;
+    if (b < p.batch) {
+      s_prefix[b] = run;
+      run += (max(s_lens[b], 0) + kTile - 1) / kTile;
+    }
+    if (b == p.batch - 1) s_prefix[p.batch] = run;
+  }
+}
+
 // T : MMA element type (bf16 or f16; f16 for FP8 caches, q is converted).  TO : output type.
 template <int D, bool FP8, typename T, typename TO>
 __global__ void __launch_bounds__(kTmaThreads, TmaCfg<D, FP8>::kBlocks)
@@ -108,17 +203,13 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   auto bar_item_full = [&](int s) { return smem_u32(bars + 2 * C::kStages + s); };
   auto bar_item_empty = [&](int s) { return smem_u32(bars + 2 * C::kStages + kItemSlots + s); };
   const uint32_t bar_math = smem_u32(bars + 2 * C::kStages + 2 * kItemSlots);
-  int* s_misc = reinterpret_cast<int*>(smem + C::misc);    // [0] abort, [1] ticket, [2..5] warp sums, [6],[7] item ids
+  int* s_misc = reinterpret_cast<int*>(smem + C::misc);    // [0] abort, [1] ticket, [2..5] warp sums
   volatile int* s_abort = s_misc;
-  int* s_item = s_misc + 6;
   int* s_prefix = reinterpret_cast<int*>(smem + C::plan);  // [batch + 1]
   int* s_lens = s_prefix + p.batch + 1;                    // [batch]
   float* s_scales = reinterpret_cast<float*>(smem + C::scales);
   int* status = p.counters + 2;
 
-  // id of this CTA's first work item: requested now, its round trip runs under the plan
-  int next_id = 0;
-  if (tid == kThreads) next_id = atomicAdd(&p.counters[0], 1);
   if (tid == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_full(s), 1);
@@ -137,14 +228,19 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   const int lanes_per_run = p.heads_kv * p.n_hb;
 
   if (warp < kWarps)
-    decode_plan<FP8>(p, tid, reinterpret_cast<int*>(smem + C::merge), s_prefix, s_lens, s_misc + 2,
-                     [] { named_barrier(kMathBarrier, kThreads); });
+    tile_prefix_plan(p, tid, s_prefix, s_lens, s_misc + 2, [] { named_barrier(kMathBarrier, kThreads); });
   __syncthreads();
-  const int total_items = s_prefix[p.batch] * lanes_per_run;
+  const unsigned total_units = unsigned(s_prefix[p.batch]) * unsigned(lanes_per_run);
+  // units per range: an equal share per CTA, or the run length asked for; never so small that the ranges
+  // outnumber the partial-result slots of the workspace (2 per range)
+  unsigned per = (total_units + gridDim.x - 1) / gridDim.x;
+  if (p.force_chunk > 0) per = unsigned(p.force_chunk);
+  per = max(max(per, 1u), (2u * total_units + unsigned(p.max_items) - 1) / unsigned(p.max_items));
+  const int n_ranges = int((total_units + per - 1) / per);
   const long long limit = p.wait_cycles;
 
   if (warp == kWarps) {
-    // ================= producer: item ids, q rows, K/V tiles =================
+    // ================= producer: q rows and K/V tiles of this CTA's segments =================
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
@@ -152,26 +248,20 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     int stage = 0;
     uint32_t stage_par = 0;
     bool alive = true;
-    for (int round = 0; alive; ++round) {
+    int round = 0;
+    for (int range = blockIdx.x; alive && range < n_ranges; range += gridDim.x) {
+     const unsigned range_begin = unsigned(range) * per, range_end = min(range_begin + per, total_units);
+     for (unsigned u = range_begin; alive && u < range_end; ++round) {
       const int slot = round & 1;
       const uint32_t slot_par = (round >> 1) & 1;
-      const int item = __shfl_sync(0xffffffffu, next_id, 0);
       int ok = 1;
       if (lane == 0) ok = mbar_wait_bounded(bar_item_empty(slot), slot_par ^ 1, s_abort, status, 601, limit) ? 1 : 0;
-      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-      if (item >= total_items) {
-        if (lane == 0) {
-          s_item[slot] = -1;
-          mbar_arrive(bar_item_full(slot));
-        }
-        break;
-      }
-      if (lane == 0) next_id = atomicAdd(&p.counters[0], 1);   // id of the following item, in flight from now
-      const ItemDesc d = decode_item(p, item, s_prefix, s_lens);
+      if (!__shfl_sync(0xffffffffu, ok, 0)) { alive = false; break; }
+      const Segment d = segment_at(p, u, range_begin, range_end, range, per, s_prefix, s_lens, lanes_per_run);
+      u = d.next;
       const int head0 = d.hk * p.group + d.hbi * p.hb;
       const int n_heads = min(p.hb, p.group - d.hbi * p.hb);
       if (lane == 0) {
-        s_item[slot] = item;
         const uint32_t q_bytes = uint32_t(n_heads) * D * 2;
         mbar_expect_tx(bar_item_full(slot), q_bytes);
         bulk_load(sbase + C::qslots + slot * C::kQSlotBytes,
@@ -224,6 +314,7 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
           if (++stage == C::kStages) { stage = 0; stage_par ^= 1; }
         }
       }
+     }
     }
   } else {
     // ================= math warps =================
@@ -270,8 +361,9 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     struct Pending {
       bool valid;
       int* ticket;
-      int n_runs, first_item, b, head0, n_heads;
-    } pend{false, nullptr, 0, 0, 0, 0, 0};
+      int n_runs, first_range, b, head0, n_heads;
+      unsigned lane_start;
+    } pend{false, nullptr, 0, 0, 0, 0, 0, 0u};
     auto resolve_pending = [&]() {
       if (!pend.valid) return;           // uniform across the math warps
       pend.valid = false;
@@ -291,7 +383,7 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       const int n_out = pend.n_heads * D;
 #pragma unroll 2
       for (int r = 0; r < pend.n_runs; ++r) {
-        const size_t it2 = size_t(pend.first_item) + size_t(r) * lanes_per_run;
+        const size_t it2 = size_t(segment_slot(pend.first_range + r, per, pend.lane_start));
         const float* ml = p.part_ml + it2 * p.hb * 2;
         const float* po2 = p.part_o + it2 * p.hb * D;
         float mt[kOut], lt[kOut], ot[kOut];
@@ -328,12 +420,14 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 
     int stage = 0;
     uint32_t stage_par = 0;
-    for (int round = 0; alive; ++round) {
+    int round = 0;
+    for (int range = blockIdx.x; alive && range < n_ranges; range += gridDim.x) {
+     const unsigned range_begin = unsigned(range) * per, range_end = min(range_begin + per, total_units);
+     for (unsigned u = range_begin; alive && u < range_end; ++round) {
       const int slot = round & 1;
-      if (!mbar_wait_bounded(bar_item_full(slot), (round >> 1) & 1, s_abort, status, 602, limit)) break;
-      const int item = s_item[slot];
-      if (item < 0) break;
-      const ItemDesc d = decode_item(p, item, s_prefix, s_lens);
+      if (!mbar_wait_bounded(bar_item_full(slot), (round >> 1) & 1, s_abort, status, 602, limit)) { alive = false; break; }
+      const Segment d = segment_at(p, u, range_begin, range_end, range, per, s_prefix, s_lens, lanes_per_run);
+      u = d.next;
       const int b = d.b, hk = d.hk, len = d.len;
       const int n_tiles = d.tile1 - d.tile0;
       const int head0 = hk * p.group + d.hbi * p.hb;
@@ -510,8 +604,8 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         }
       }
       const bool single = (d.n_runs == 1);
-      float* po = p.part_o + size_t(item) * p.hb * D;
-      float* pml = p.part_ml + size_t(item) * p.hb * 2;
+      float* po = p.part_o + size_t(d.slot) * p.hb * D;
+      float* pml = p.part_ml + size_t(d.slot) * p.hb * 2;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         float* so0 = s_o + (warp * 8 + t4 * 2) * C::kMergeStride;
@@ -558,13 +652,27 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       if (!single) {
         // the ticket for this (sequence, KV head, head block) is taken at the start of the next item
         pend.valid = true;
-        pend.ticket = p.counters + kCounterWords + (size_t(b) * p.heads_kv + hk) * p.n_hb + d.hbi;
+        pend.ticket = p.counters + kCounterWords + d.lane;
         pend.n_runs = d.n_runs;
-        pend.first_item = d.first_run * lanes_per_run + d.rem;
+        pend.first_range = d.first_range;
+        pend.lane_start = d.lane_start;
         pend.b = b; pend.head0 = head0; pend.n_heads = n_heads;
       }
+     }
     }
     if (alive) resolve_pending();
+    // sequences without a single token own no unit: their rows are zero, their LSE -inf
+    if (alive) {
+      for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
+        if (s_prefix[b + 1] != s_prefix[b]) continue;
+        for (int idx = tid; idx < p.heads * D; idx += kThreads) {
+          const int h = idx / D, dd = idx - h * D;
+          const size_t orow = size_t(b) * p.heads + h;
+          emit_out<TO>(p, parity, orow, dd, D, 0.f);
+          if (dd == 0) emit_lse(p, parity, orow, D, -INFINITY);
+        }
+      }
+    }
 
     // ---- the last CTA to leave resets the scheduler counters ------------------------------
     if (p.world > 1) __threadfence_system();   // stores to the other GPUs, out to system scope
@@ -690,6 +798,13 @@ int launch_decode_tma(const DecodeParams& p, int q_dtype, int kv_dtype, int o_dt
   if (fp8 && !p.bt) return kTmaNotApplicable;              // scales are indexed by page: needs the table
   if (reinterpret_cast<uintptr_t>(p.q) & 15) return kTmaNotApplicable;
   if (p.tok_stride <= 0 || p.head_stride <= 0) return kTmaNotApplicable;
+  {
+    // the partition counts tiles in 32 bits: bound them by what the cache can hold
+    const long long cap = p.bt ? (long long)p.bt_stride * p.page_size
+                               : (p.lens ? (p.tok_stride > 0 ? p.batch_stride / p.tok_stride : 0) : (long long)p.uniform_len);
+    const long long units = (long long)p.batch * ((cap + kTile - 1) / kTile) * p.heads_kv * p.n_hb;
+    if (units >= (1LL << 30)) return kTmaNotApplicable;
+  }
 
   MapKey key{};
   key.esize = esize; key.heads_kv = p.heads_kv; key.dim = dim;

@@ -5,6 +5,10 @@
 
 #include "tb200_common.cuh"
 
+#ifndef TB200_WAIT_SLEEP_NS
+#define TB200_WAIT_SLEEP_NS 0
+#endif
+
 namespace tb200 {
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -37,8 +41,12 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
+#if TB200_WAIT_SLEEP_NS
+      __nanosleep(TB200_WAIT_SLEEP_NS);   // a polling warp takes issue slots from the warps it waits for
+#endif
+    }
     if (*abort_flag) return false;
     if (clock64() - t0 > limit) {
       *abort_flag = 1;
