@@ -313,7 +313,9 @@ int tb200_rope_neox_packed(const void* x, void* y, const void* cos_table, const 
  * cu_seqlens_kv[b] .. +cache_seqlens[b] are its cached tokens dequantised (float(x8) * scale, rounded to
  * dtype), followed by its chunk's own rows of k_new / v_new (copied).
  *   k_pages / v_pages [pool_tokens, heads_kv, dim] e4m3 ; k_new / v_new [total_q, heads_kv, dim] dtype
- *   k_out / v_out [total_kv, heads_kv, dim] dtype, total_kv = sum_b (cache_seqlens[b] + q_len[b])
+ *   k_out / v_out [total_kv, heads_kv, dim] dtype, total_kv >= sum_b (cache_seqlens[b] + q_len[b]) (an upper
+ *   bound is enough: rows at or behind cu_seqlens_kv[batch] are not touched, so a host that knows only the
+ *   capacity of the block table need not read the lengths back)
  *   cu_seqlens_kv [batch + 1] int32 = exclusive sums of cache_seqlens[b] + q_len[b]
  *   k_scale / v_scale: device pointers to one fp32 each
  *

@@ -477,3 +477,21 @@ print("REAL-BACKEND-OK")
     env = dict(os.environ, PYTHONPATH=os.pathsep.join([REFERENCE_SRC, ROOT]))
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd="/tmp", timeout=300)
     assert out.returncode == 0 and "REAL-BACKEND-OK" in out.stdout, out.stdout[-2000:] + out.stderr[-3000:]
+
+
+def test_paged_decode_op_can_range_check_its_block_table(clean_registry):
+    """Opt-in host-side check of lengths and page ids (the kernel trusts them): a bad table is a ValueError
+    before anything is launched."""
+    op = GroupedQueryAttentionDecodePagedWithKVCacheFwdOp(2, 8, 2, 256, 64, 64, kernel_map={"gqa_decode_paged_kernel": _Recorder})
+    op.validate_inputs = True
+    q = torch.zeros(2, 8, 64, dtype=torch.float16)
+    k = torch.zeros(256, 2, 64, dtype=torch.float16)
+    lens = torch.tensor([100, 64], dtype=torch.int32)
+    good = torch.tensor([[0, 1], [3, 9]], dtype=torch.int32)      # entry [1, 1] is behind sequence 1's length: not read
+    op(q, k, k, lens, good)
+    with pytest.raises(ValueError, match=r"block_table\[0, 1\]=7 is outside the pool of 4 pages"):
+        op(q, k, k, lens, torch.tensor([[0, 7], [3, 0]], dtype=torch.int32))
+    with pytest.raises(ValueError, match="needs 3 pages"):
+        op(q, k, k, torch.tensor([129, 1], dtype=torch.int32), good)
+    with pytest.raises(ValueError, match="non-negative"):
+        op(q, k, k, torch.tensor([-1, 1], dtype=torch.int32), good)

@@ -199,3 +199,22 @@ def test_mma_issue_probe_reports_the_floor_the_kernels_are_designed_around():
     for n in (64, 128, 256):
         issued, done = F.mma_issue_probe(n, a_in_tmem=(n == 128))
         assert n / 2 <= done < 1000 and issued <= done + 1, (n, issued, done)
+
+
+def test_a_timed_out_prefill_surfaces_at_the_next_call():
+    """The status word of the prefill kernels is sticky (launches after a wait that ran out return with their
+    outputs unwritten).  The host keeps a pinned mirror of it: the call after the failure raises and clears it.
+    The failure is made on the host here - the word is set by hand, no device-side wait runs out."""
+    from tileops_b200._native import NativeLibraryError
+    q, k, v = W.make_prefill(45, 1, 128, 128, 2, 1, 128, torch.bfloat16, "cuda")
+    F.gqa_prefill(q, k, v)                                    # creates the status word and its mirror
+    torch.cuda.synchronize()
+    ws = F._WORKSPACES[(q.device, "prefill_status")]
+    ws[:4].view(torch.int32).fill_(302)                       # what a kernel leaves when a wait gives up
+    F.gqa_prefill(q, k, v)                                    # returns at once on the device; mirrors the word
+    torch.cuda.synchronize()
+    with pytest.raises(NativeLibraryError, match="code 302"):
+        F.gqa_prefill(q, k, v)
+    torch.cuda.synchronize()
+    assert F.prefill_status() == 0                            # cleared: the next call works again
+    close(F.gqa_prefill(q, k, v), O.prefill_ref(q.cpu(), k.cpu(), v.cpu(), True))

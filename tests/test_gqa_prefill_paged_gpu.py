@@ -376,11 +376,16 @@ def test_fp8_cache_golden_vectors():
     def pad(x):   # D = 32 fixtures, the kernel serves 64: zero columns (zero is exact in e4m3 too)
         return torch.cat([x, torch.zeros_like(x)], dim=-1).cuda()
     kp, vp = pad(f8("p8_k_pages")), pad(f8("p8_v_pages"))
-    o = _F().gqa_prefill_paged_fp8_cache(
-        pad(h("p8_q")), pad(h("p8_k_new")), pad(h("p8_v_new")), kp, vp, torch.from_numpy(G["p8_k_scale"]).cuda(),
-        torch.from_numpy(G["p8_v_scale"]).cuda(), torch.from_numpy(G["p8_cu"]).cuda(),
-        torch.from_numpy(G["p8_cache"]).cuda(), torch.from_numpy(G["p8_bt"]).cuda(), 48, page_size=int(G["p8_page"]),
-        sm_scale=32 ** -0.5)
+    args = (pad(h("p8_q")), pad(h("p8_k_new")), pad(h("p8_v_new")), kp, vp, torch.from_numpy(G["p8_k_scale"]).cuda(),
+            torch.from_numpy(G["p8_v_scale"]).cuda(), torch.from_numpy(G["p8_cu"]).cuda(),
+            torch.from_numpy(G["p8_cache"]).cuda(), torch.from_numpy(G["p8_bt"]).cuda())
+    page = int(G["p8_page"])
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")          # the call must not read anything back from the device
+    try:
+        o = _F().gqa_prefill_paged_fp8_cache(*args, 48, page_size=page, sm_scale=32 ** -0.5)
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
     torch.testing.assert_close(o[..., :32].cpu().float(), h("p8_o").float(), atol=5e-3, rtol=1e-2)
     assert torch.equal(kp[..., :32].cpu().view(torch.uint8), f8("p8_k_pages_after").view(torch.uint8))
     assert torch.equal(vp[..., :32].cpu().view(torch.uint8), f8("p8_v_pages_after").view(torch.uint8))

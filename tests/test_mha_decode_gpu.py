@@ -61,11 +61,30 @@ def test_mha_decode_op(batch, heads, seqlen_q, seqlen_kv, live, dim, dtype):
     torch.testing.assert_close(o.cpu().float(), _ref(q, k, v).float(), atol=ATOL[dtype], rtol=1e-2)
 
 
-def test_causal_multi_row_q_is_refused():
+def test_causal_multi_row_paged_decode_matches_the_reference_mask():
+    """The reference's paged MHA decode masks top-left aligned (row i sees keys 0..i,
+    src/tileops/kernels/attention/mha_decode_paged.py:72-95); rows are clamped to the live length."""
     from tileops_b200.ops import MultiHeadAttentionDecodePagedWithKVCacheFwdOp
-    op = MultiHeadAttentionDecodePagedWithKVCacheFwdOp(1, 8, 4, 512, 128, 64, is_causal=True)
-    q = torch.zeros(1, 4, 8, 128, device="cuda", dtype=torch.float16)
-    k = torch.zeros(512, 8, 128, device="cuda", dtype=torch.float16)
-    with pytest.raises(ValueError, match="no implementation serves this call"):
-        op(q, k, k, torch.full((1,), 64, dtype=torch.int32, device="cuda"),
-           torch.zeros(1, 8, dtype=torch.int32, device="cuda"))
+    B, H, Sq, D, page, pool = 2, 8, 4, 128, 64, 512
+    g = torch.Generator().manual_seed(8)
+    q = torch.randn(B, Sq, H, D, generator=g).to(torch.float16)
+    k = torch.randn(pool, H, D, generator=g).to(torch.float16)
+    v = torch.randn(pool, H, D, generator=g).to(torch.float16)
+    lens = torch.tensor([200, 3], dtype=torch.int32)                  # the second sequence is shorter than Sq
+    bt = torch.randperm(pool // page, generator=g).to(torch.int32).reshape(B, -1)
+    op = MultiHeadAttentionDecodePagedWithKVCacheFwdOp(B, H, Sq, pool, D, page, is_causal=True)
+    o = op(q.cuda(), k.cuda(), v.cuda(), lens.cuda(), bt.cuda()).cpu().float()
+    for b in range(B):
+        rows = torch.from_numpy(O.physical_rows(bt[b].numpy(), int(lens[b]), page))
+        kb, vb = k[rows].float(), v[rows].float()
+        for i in range(Sq):
+            n = min(i + 1, int(lens[b]))
+            sc = torch.einsum("hd,nhd->hn", q[b, i].float(), kb[:n]) * D ** -0.5
+            ref = torch.einsum("hn,nhd->hd", torch.softmax(sc, -1), vb[:n])
+            torch.testing.assert_close(o[b, i], ref, atol=5e-3, rtol=1e-2)
+
+
+def test_causal_multi_row_contiguous_decode_is_refused():
+    from tileops_b200.kernels.mha_decode import MHADecodeSm100Kernel
+    with pytest.raises(ValueError, match="causal mask between the q rows"):
+        MHADecodeSm100Kernel(1, 8, 4, 512, 128, True, torch.float16)

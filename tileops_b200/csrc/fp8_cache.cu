@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(kThreads) fp8_cache_gather_kernel(
     const int32_t* __restrict__ bt, long long bt_stride, const float* __restrict__ k_scale,
     const float* __restrict__ v_scale, int batch, int row_elems, int page_size) {
   const int g = blockIdx.x;
+  if (g >= cu_kv[batch]) return;        // total_kv may be an upper bound (the host never reads the lengths)
   const int b = find_request(cu_kv, batch, g);
   const int t = g - cu_kv[b];
   const int old = cache_lens[b];

@@ -178,14 +178,35 @@ def gqa_lse_merge(o_parts: torch.Tensor, lse_parts: torch.Tensor, out_dtype: tor
 
 
 def _prefill_status(device: torch.device, need: int) -> torch.Tensor:
-    """Zeroed status buffer of the prefill kernel, one per device (the kernel writes it only when
-    a bounded device-side wait runs out)."""
+    """Zeroed status buffer of the prefill kernels, one per device (a kernel writes it only when a bounded
+    device-side wait runs out).  A wait that ran out makes the launch - and, the word being sticky, every
+    later launch on the device - return with its outputs unwritten.  So that this cannot pass unnoticed, the
+    word has a mirror in pinned host memory: every prefill call first looks at the mirror (a plain host
+    read, no synchronisation; it shows what launches that have completed by now left there), raises
+    ``NativeLibraryError`` and clears the word if it is set, and after its launch queues a 4-byte copy of the
+    word into the mirror on the same stream."""
     key = (device, "prefill_status")
     ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < need:
         ws = torch.zeros(max(need, 256), dtype=torch.uint8, device=device)
         _WORKSPACES[key] = ws
+        _WORKSPACES[(device, "prefill_status_mirror")] = torch.zeros(1, dtype=torch.int32).pin_memory()
+    mirror = _WORKSPACES[(device, "prefill_status_mirror")]
+    code = int(mirror[0])
+    if code:
+        mirror.zero_()
+        ws[:4].zero_()
+        raise N.NativeLibraryError(
+            f"an earlier prefill launch on {device} gave up on a device-side wait (code {code}); its outputs and "
+            "those of the launches after it are not valid.  The status word has been cleared.")
     return ws
+
+
+def _mirror_prefill_status(device: torch.device) -> None:
+    ws = _WORKSPACES.get((device, "prefill_status"))
+    mirror = _WORKSPACES.get((device, "prefill_status_mirror"))
+    if ws is not None and mirror is not None:
+        mirror.copy_(ws[:4].view(torch.int32), non_blocking=True)
 
 
 def _device_of(device: "torch.device | str | int | None") -> torch.device:
@@ -209,6 +230,7 @@ def prefill_status(device: "torch.device | str | int | None" = None, reset: bool
     code = int(ws[:4].view(torch.int32).item())
     if reset and code:
         ws[:4].zero_()
+        _WORKSPACES[(_device_of(device), "prefill_status_mirror")].zero_()
     return code
 
 
@@ -254,6 +276,7 @@ def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal:
                                        int(window_size_right), N.prefill_flags(config), N.ptr(ws), need,
                                        N.current_stream(q.device))
     N.check(st, "tb200_gqa_prefill")
+    _mirror_prefill_status(q.device)
     return (o, lse) if return_lse else o
 
 
@@ -331,6 +354,7 @@ def gqa_prefill_paged(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
             float(softcap or 0.0), int(window_size_left), int(window_size_right), N.prefill_flags(config),
             N.ptr(ws), need, N.current_stream(q.device))
     N.check(st, "tb200_gqa_prefill_paged")
+    _mirror_prefill_status(q.device)
     return (o, lse) if return_lse else o
 
 
@@ -370,7 +394,8 @@ def gqa_prefill_paged_fp8_cache(q: torch.Tensor, k_new: torch.Tensor, v_new: tor
     """Packed prefill of one chunk per request over an FP8-e4m3 paged cache with scalar scales
     (``k_scale`` / ``v_scale``: fp32 tensors of shape (1,)): the cached tokens are dequantised into a packed
     16-bit K/V next to the chunk's own rows, the packed prefill runs on it, and the chunk is quantised into
-    the pages in place.  One host read of the total KV length per call (it sizes the packed buffer)."""
+    the pages in place.  Nothing is read back from the device: the packed buffer is sized by the capacity of
+    the block table."""
     _require_cuda(q=q, k_new=k_new, v_new=v_new, k_pages=k_pages, v_pages=v_pages, k_scale=k_scale, v_scale=v_scale,
                   cu_seqlens_q=cu_seqlens_q, cache_seqlens=cache_seqlens, block_table=block_table)
     f8 = getattr(torch, "float8_e4m3fn")
@@ -390,9 +415,17 @@ def gqa_prefill_paged_fp8_cache(q: torch.Tensor, k_new: torch.Tensor, v_new: tor
     kv_lens = cache_seqlens + (cu_seqlens_q[1:] - cu_seqlens_q[:-1])
     cu_kv = torch.zeros(B + 1, dtype=torch.int32, device=q.device)
     cu_kv[1:] = torch.cumsum(kv_lens, 0)
-    total_kv = int(cu_kv[-1].item())          # host read: sizes the packed K/V
-    k_all = torch.empty((total_kv, Hkv, D), dtype=q.dtype, device=q.device)
-    v_all = torch.empty_like(k_all)
+    # The packed K/V is sized by what the block table can describe (its width x the page size per request)
+    # plus the chunk: an upper bound known on the host, so that no length is read back from the device.
+    # The buffers are kept per shape (a chunked prefill calls this with the same shapes over and over).
+    total_kv = B * block_table.shape[1] * int(page_size) + total_q
+    key = (q.device, torch.cuda.current_stream(q.device).cuda_stream, "fp8_cache_packed", total_kv, Hkv, D, q.dtype)
+    bufs = _WORKSPACES.get(key)
+    if bufs is None:
+        bufs = (torch.empty((total_kv, Hkv, D), dtype=q.dtype, device=q.device),
+                torch.empty((total_kv, Hkv, D), dtype=q.dtype, device=q.device))
+        _WORKSPACES[key] = bufs
+    k_all, v_all = bufs
     lib, stream = N.lib(), N.current_stream(q.device)
     with torch.cuda.device(q.device):
         st = lib.tb200_fp8_cache_gather(

@@ -6,7 +6,10 @@ Slots and constructors of the reference's ``MHADecodeKernel`` / ``MHADecodePaged
 ``seqlen_q == 1`` the call is GQA decode with one q head per KV head.  With ``seqlen_q > 1`` and no causal
 mask the ``seqlen_q`` rows of a head share that head's K/V exactly like the q heads of a GQA group, so
 they are laid out as a group of ``seqlen_q`` heads (a small host-side permute of q and o) and the same
-CUDA kernel runs; a causal mask between those rows is not served.
+CUDA kernel runs.  The paged kernel's causal mask between the rows of a call is the reference's top-left
+aligned one (``src/tileops/kernels/attention/mha_decode_paged.py:72-95``: row ``i`` sees keys ``0..i``): every
+(sequence, row) then becomes a sequence of its own with length ``min(i + 1, real_seqlen_kv)`` over the same
+pages, again one launch of the same kernel.
 """
 
 from __future__ import annotations
@@ -39,16 +42,18 @@ def _from_groups(o: torch.Tensor, B: int, Sq: int, H: int, D: int) -> torch.Tens
 class _MHADecodeBase(Kernel):
     supported_archs = [100]
     general = True
+    #: whether a causal mask between several q rows of one call is served (the paged kernel only)
+    serves_causal_rows = False
 
     @classmethod
     def applies(cls, call) -> bool:
         return (call.dim in (64, 128) and call.dtype in ATTENTION_DTYPES
-                and not (call.is_causal and call.max_seqlen_q > 1))
+                and (cls.serves_causal_rows or not (call.is_causal and call.max_seqlen_q > 1)))
 
     def _common(self, batch, heads, seqlen_q, seqlen_kv, dim, is_causal, dtype, tune):
         if dim not in (64, 128):
             raise ValueError(f"{type(self).__name__} supports head dim 64 and 128, got {dim}")
-        if is_causal and seqlen_q > 1:
+        if is_causal and seqlen_q > 1 and not self.serves_causal_rows:
             raise ValueError(f"{type(self).__name__} does not serve a causal mask between the q rows")
         self.batch, self.heads, self.seqlen_q, self.seqlen_kv, self.dim = batch, heads, seqlen_q, seqlen_kv, dim
         self.is_causal, self.dtype, self.tune = is_causal, dtype, tune
@@ -74,6 +79,8 @@ class MHADecodeSm100Kernel(_MHADecodeBase):
 class MHADecodePagedSm100Kernel(_MHADecodeBase):
     """Paged cache: ``forward(Q[B,Sq,H,D], K[N,H,D], V, real_seqlen_kv[B] i32, block_table[B,W] i32)``."""
 
+    serves_causal_rows = True
+
     def __init__(self, batch, heads, seqlen_q, seqlen_kv, dim, page_size, is_causal, dtype,
                  config: Optional[dict] = None, tune: bool = False, device_index=None) -> None:
         super().__init__(device_index=device_index)
@@ -86,6 +93,13 @@ class MHADecodePagedSm100Kernel(_MHADecodeBase):
     def forward(self, Q, K, V, real_seqlen_kv, block_table):
         self._require_cuda(Q=Q, K=K, V=V, real_seqlen_kv=real_seqlen_kv, block_table=block_table)
         B, Sq, H, D = Q.shape
+        if self.is_causal and Sq > 1:
+            # row i of sequence b: a sequence of its own that sees keys 0..i of b's pages (no host sync)
+            rows = torch.arange(1, Sq + 1, device=Q.device, dtype=torch.int32).repeat(B)
+            lens = torch.minimum(real_seqlen_kv.repeat_interleave(Sq), rows)
+            o = F.gqa_decode(Q.reshape(B * Sq, H, D), K, V, real_seqlen_kv=lens,
+                             block_table=block_table.repeat_interleave(Sq, dim=0), page_size=self.page_size)
+            return o.view(B, Sq, H, D)
         o = F.gqa_decode(_as_groups(Q), K, V, real_seqlen_kv=real_seqlen_kv, block_table=block_table,
                          page_size=self.page_size)
         return _from_groups(o, B, Sq, H, D)

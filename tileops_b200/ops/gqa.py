@@ -840,9 +840,34 @@ class GroupedQueryAttentionDecodeWithKVCacheFwdOp(Op):
 
 class GroupedQueryAttentionDecodePagedWithKVCacheFwdOp(Op):
     """Single-token decode over a paged cache. q ``[B,H,D]``; k, v physical pool
-    ``[seqlen_kv, heads_kv, dim]``; real_seqlen_kv ``[B]`` int32; block_table ``[B, num_pages]`` int32."""
+    ``[seqlen_kv, heads_kv, dim]``; real_seqlen_kv ``[B]`` int32; block_table ``[B, num_pages]`` int32.
+
+    The kernel trusts the block table (a wrong page id is an out-of-bounds read).  Setting the attribute
+    ``validate_inputs = True`` on an instance makes every ``forward`` check lengths and page ids on the host
+    first, the check the reference's paged prefill does on every call
+    (``src/tileops/ops/attention/gqa.py:1038-1046``); it reads both tensors back, so it is off by default
+    and stays off on a timed path."""
 
     _KEYS = PAGED_DECODE_KEYS
+    validate_inputs = False
+
+    def _check_table(self, k: torch.Tensor, real_seqlen_kv: torch.Tensor, block_table: torch.Tensor) -> None:
+        """Host-side range check of lengths and the page ids they reach (synchronises)."""
+        lens = real_seqlen_kv.detach().cpu().to(torch.int64)
+        table = block_table.detach().cpu().to(torch.int64)
+        width = table.shape[1]
+        pool_pages = k.shape[0] // self.page_size
+        if bool((lens < 0).any()):
+            raise ValueError("real_seqlen_kv must be non-negative")
+        need = (lens + self.page_size - 1) // self.page_size
+        if bool((need > width).any()):
+            b = int((need > width).nonzero()[0])
+            raise ValueError(f"real_seqlen_kv[{b}]={int(lens[b])} needs {int(need[b])} pages, block_table has {width}")
+        live = torch.arange(width)[None, :] < need[:, None]
+        bad = live & ((table < 0) | (table >= pool_pages))
+        if bool(bad.any()):
+            b, i = (int(x) for x in bad.nonzero()[0])
+            raise ValueError(f"block_table[{b}, {i}]={int(table[b, i])} is outside the pool of {pool_pages} pages")
 
     def __init__(self, batch: int, heads: int, heads_kv: int, seqlen_kv: int, dim: int, page_size: int,
                  sm_scale: Optional[float] = None, softcap: Optional[float] = None,
@@ -879,6 +904,8 @@ class GroupedQueryAttentionDecodePagedWithKVCacheFwdOp(Op):
 
     def forward(self, q, k, v, real_seqlen_kv, block_table) -> torch.Tensor:
         self.dtype = q.dtype
+        if self.validate_inputs:
+            self._check_table(k, real_seqlen_kv, block_table)
         return self._get_kernel((q, k, v, real_seqlen_kv, block_table), q.dtype)(
             q, k, v, real_seqlen_kv, block_table)
 
@@ -905,6 +932,8 @@ class GroupedQueryAttentionDecodePagedFp8KVCacheFwdOp(GroupedQueryAttentionDecod
                 raise ValueError(f"{name} must have shape {expected}, got {tuple(t.shape)}")
         self.dtype = q.dtype
         self.cache_dtype = k.dtype
+        if self.validate_inputs:
+            self._check_table(k, real_seqlen_kv, block_table)
         return self._get_kernel((q, k, v, k_scale, v_scale, real_seqlen_kv, block_table), q.dtype)(
             q, k, v, k_scale, v_scale, real_seqlen_kv, block_table)
 
