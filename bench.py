@@ -120,7 +120,7 @@ def dist_env():
     return rank, world, local
 
 
-def time_steps(fn, steps: int, warmup: int, world: int, sampler=None, soak_s: float = 1.5):
+def time_steps(fn, steps: int, warmup: int, world: int, sampler=None, soak_s: float = 0.0):
     """W untimed steps, then exactly K steps between a barrier+synchronize on both sides, timed
     with CUDA events on the launching (current) stream.  Returns this rank's elapsed ms.
 
@@ -131,8 +131,19 @@ def time_steps(fn, steps: int, warmup: int, world: int, sampler=None, soak_s: fl
     import torch.distributed as dist
     if sampler:
         sampler.start()
-        t_end = time.perf_counter() + soak_s
-        while time.perf_counter() < t_end:
+    if soak_s > 0:
+        # the same number of soak steps on every rank (a step may hold an exchange that all ranks must run in
+        # lockstep): the slowest rank's time for 10 steps sizes the soak
+        t0 = time.perf_counter()
+        for _ in range(10):
+            fn()
+        torch.cuda.synchronize()
+        per_step = max((time.perf_counter() - t0) / 10, 1e-6)
+        if world > 1:
+            t = torch.tensor([per_step], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            per_step = float(t.item())
+        for _ in range(min(int(soak_s / per_step), 100000) // 20):
             for _ in range(20):
                 fn()
             torch.cuda.synchronize()
@@ -172,6 +183,9 @@ def measure(fn, steps, warmup, world, device, local_index, sample_clocks=True):
     one region (max over ranks), then per-launch medians over 100 more steps."""
     sampler = ClockSampler(local_index) if sample_clocks else None
     ms_local = time_steps(fn, steps, warmup, world, sampler, soak_s=1.5 if sample_clocks else 0.0)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
     med, mn = per_launch_us(fn)
     clocks = sampler.stop() if sampler else None
     ms = max_over_ranks(ms_local, world, device) / steps
@@ -350,7 +364,7 @@ def main():
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic", "config": config, "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
         return
 
     if not torch.cuda.is_available():
@@ -411,7 +425,7 @@ def main():
                 "us_x_sm_mhz": m.get("us_x_sm_mhz"), "parity_spot": parity_spot, "others": others}
         if cpu_base is not None:
             line["cpu_baseline"] = cpu_base
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()

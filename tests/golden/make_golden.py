@@ -83,7 +83,7 @@ def main():
     g = torch.Generator().manual_seed(SEED)
     out = {}
 
-    # ---- contiguous decode, BASELINE config 1 (fp32 on CPU) + variants
+    # ---- contiguous decode, the reference's CPU-runnable case (fp32 on CPU) + variants
     B, H, Hkv, S, D = 2, 8, 2, 256, 64
     q = torch.randn(B, H, D, generator=g)
     k = torch.randn(B, S, Hkv, D, generator=g)
@@ -157,7 +157,7 @@ def main():
     # ---- FP8 quantiser: the reference function with pages playing the batch role
     P, page, Hkv, D = 6, 16, 2, 64
     xk = torch.randn(P, page, Hkv, D, generator=g).bfloat16()
-    # fed as fp32 so that the scale is the fp32 ``amax / 448`` BASELINE config 4 asks for
+    # fed as fp32 so that the scale is the fp32 ``amax / 448`` the FP8-cache decode workload asks for
     # (on a bf16 tensor the reference function would round the scale itself to bf16)
     xq, desc = fp8u.quantize_kv_fa3_descale(xk.float())
     out["fp8_x"] = bits(xk); out["fp8_q"] = bits(xq); out["fp8_scale"] = desc.numpy()

@@ -37,7 +37,7 @@ def cpu(inp):
 
 # ---------------------------------------------------------------- contiguous decode
 @pytest.mark.parametrize("B,H,Hkv,S,D,dtype", [
-    (2, 8, 2, 256, 64, torch.bfloat16),          # BASELINE config 1 shape
+    (2, 8, 2, 256, 64, torch.bfloat16),          # the reference's CPU-runnable decode case
     (1, 32, 8, 8192, 128, torch.float16),
     (1, 32, 8, 8192, 128, torch.bfloat16),
     (1, 16, 2, 8192, 128, torch.float16),
@@ -222,7 +222,7 @@ def test_fp8_expansion_is_exact_for_every_byte():
 
 # ---------------------------------------------------------------- full-size properties
 def test_split_merge_property_at_config3_size():
-    """BASELINE config 3 at full size: (a) three sequences against the oracle; (b) attention
+    """The paged bf16 decode workload (64 ragged sequences) at full size: (a) three sequences against the oracle; (b) attention
     over a sequence equals the LSE-merge of attention over its two halves, for every row."""
     inp = W.baseline_config(3, "cuda")
     B = 64

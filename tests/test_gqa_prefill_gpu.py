@@ -144,7 +144,7 @@ def test_golden_prefill_fixture_head_dim_128_embedding():
 
 
 def test_config2_rows_against_oracle_and_causal_prefix_property():
-    """BASELINE config 2 at full size.  (a) one (batch, KV head) slice against the oracle;
+    """The causal prefill workload (4 x 4096, 32/8 heads) at full size.  (a) one (batch, KV head) slice against the oracle;
     (b) causality: the first 1024 rows of the 4096-token result equal a 1024-token prefill."""
     B, S, H, Hkv, D = 4, 4096, 32, 8, 128
     q, k, v = W.make_prefill(2, B, S, S, H, Hkv, D, torch.bfloat16, "cuda")

@@ -163,7 +163,7 @@ def make_paged_decode(
 
 
 def make_contiguous_decode(cfg, batch, heads, heads_kv, seqlen_kv, dim, dtype=torch.float32, device="cpu"):
-    """q ``[B,H,D]``, k/v ``[B,S,Hkv,D]`` ~ N(0,1) (BASELINE config 1 draws these on the CPU)."""
+    """q ``[B,H,D]``, k/v ``[B,S,Hkv,D]`` ~ N(0,1) (the reference's CPU-runnable decode case draws these on the CPU)."""
     device = torch.device(device)
     q = torch.randn(batch, heads, dim, generator=_gen(device, BASE_SEED + 100 * cfg), device=device).to(dtype)
     ks, vs = [], []
@@ -211,7 +211,9 @@ def make_paged_prefill(cfg, q_lens, cache_lens, heads, heads_kv, dim, page_size,
             bt.reshape(batch, max_pages_per_req).contiguous(), int(max(q_lens)))
 
 
-# The BASELINE configurations, by number (1-based as in BASELINE.json's ``configs`` list).
+# The five benchmark workloads, by number: 1 contiguous fp32 decode (2 x 256 tokens), 2 causal prefill bf16
+# (4 x 4096), 3 paged bf16 decode (64 ragged sequences), 4 paged decode over an e4m3 cache (128 x 4096),
+# 5 long-context paged decode (8 x 131072, page 128).
 def baseline_config(cfg: int, device="cuda", **overrides):
     if cfg == 1:
         return make_contiguous_decode(1, 2, 8, 2, 256, 64, torch.float32, overrides.get("device", "cpu"))
@@ -224,4 +226,4 @@ def baseline_config(cfg: int, device="cuda", **overrides):
                                  **overrides)
     if cfg == 5:
         return make_paged_decode(5, 8, 32, 8, 128, 128, lens=[131072] * 8, device=device, **overrides)
-    raise ValueError(f"unknown BASELINE config {cfg}")
+    raise ValueError(f"unknown workload number {cfg}")
