@@ -213,19 +213,36 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int pn = 0; pn < kHD / 64; ++pn)
           tma_load_4d(sbase + SmemLayout::q + pn * kQPanel, &map_q, bar(B_QFULL), pn * 64, h, q_row0, q_batch);
         // one 64-key tile of K or V: HD / 64 panels; a cached tile is gathered page by page
-        // (page_box rows per copy) through the block table
-        auto load_tile = [&](uint32_t dst, uint32_t full_bar, const CUtensorMap* dense_map,
-                             const CUtensorMap* pool_map, int i) {
-          if (kPaged && i < n_old) {
-            for (int r = 0; r < kBN; r += p.page_box) {
+        // (page_box rows per copy) through the block table.  The pool rows of a tile's copies are
+        // looked up once for K and V together, one tile ahead, so that the block-table read never
+        // sits between a freed stage and its refill.
+        constexpr int kMaxBoxes = kBN / 16;                  // the smallest page holds 16 tokens
+        int rows_cur[kMaxBoxes], rows_next[kMaxBoxes];
+        auto lookup = [&](int i, int (&rows)[kMaxBoxes]) {
+          if (!(kPaged && i < n_old)) return;
+#pragma unroll
+          for (int x = 0; x < kMaxBoxes; ++x) {
+            const int r = x * p.page_box;
+            if (r < kBN) {
               // the last cached tile may reach past old_len: look up the page of a live token there (the
               // rows are masked and their V cleared), never an entry behind the request's pages
               const int tok = min(i * kBN + r, old_len - 1);
               const int page = p.bt[(long long)b * p.bt_stride + (tok >> p.page_shift)];
-              const int row = page * p.page_size + ((i * kBN + r) & (p.page_size - 1));
+              rows[x] = page * p.page_size + ((i * kBN + r) & (p.page_size - 1));
+            }
+          }
+        };
+        auto load_tile = [&](uint32_t dst, uint32_t full_bar, const CUtensorMap* dense_map,
+                             const CUtensorMap* pool_map, int i, const int (&rows)[kMaxBoxes]) {
+          if (kPaged && i < n_old) {
 #pragma unroll
-              for (int pn = 0; pn < kHD / 64; ++pn)
-                tma_load_4d(dst + pn * kKvPanel + r * 128, pool_map, full_bar, pn * 64, hk, row, 0);
+            for (int x = 0; x < kMaxBoxes; ++x) {
+              const int r = x * p.page_box;
+              if (r < kBN) {
+#pragma unroll
+                for (int pn = 0; pn < kHD / 64; ++pn)
+                  tma_load_4d(dst + pn * kKvPanel + r * 128, pool_map, full_bar, pn * 64, hk, rows[x], 0);
+              }
             }
           } else {
             const int row = kv_row0 + (tile0 + i - n_old) * kBN;
@@ -234,15 +251,19 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
               tma_load_4d(dst + pn * kKvPanel, dense_map, full_bar, pn * 64, hk, row, q_batch);
           }
         };
+        lookup(0, rows_cur);
         for (int i = 0; i < n_kv; ++i) {
           const int s = i & 1;
           const uint32_t par = (i >> 1) & 1;
+          if (i + 1 < n_kv) lookup(i + 1, rows_next);         // in flight during the waits below
           if (!mbar_wait(bar(B_KEMPTY + s), par ^ 1, s_abort, p.status, 101)) break;
           mbar_expect_tx(bar(B_KFULL + s), kKvBytes);
-          load_tile(sbase + SmemLayout::k + s * kKvBytes, bar(B_KFULL + s), &map_k, &map_kp, i);
+          load_tile(sbase + SmemLayout::k + s * kKvBytes, bar(B_KFULL + s), &map_k, &map_kp, i, rows_cur);
           if (!mbar_wait(bar(B_VEMPTY + s), par ^ 1, s_abort, p.status, 102)) break;
           mbar_expect_tx(bar(B_VFULL + s), kKvBytes);
-          load_tile(sbase + SmemLayout::v + s * kKvBytes, bar(B_VFULL + s), &map_v, &map_vp, i);
+          load_tile(sbase + SmemLayout::v + s * kKvBytes, bar(B_VFULL + s), &map_v, &map_vp, i, rows_cur);
+#pragma unroll
+          for (int x = 0; x < kMaxBoxes; ++x) rows_cur[x] = rows_next[x];
         }
       }
     } else if (warp == 5) {
