@@ -154,11 +154,13 @@ def time_steps(fn, steps: int, warmup: int, world: int, sampler=None, soak_s: fl
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()          # a profiler started with --profile-from-start off lists the timed launches only
     e0.record()
     for _ in range(steps):
         fn()
     e1.record()
     torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
