@@ -43,7 +43,8 @@ inline int make_map(CUtensorMap* map, const void* base, int dtype, long long bat
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, dtype == TB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_SWIZZLE_128B,
+                   hd * 2 >= 256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,   // a head's row
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) TB200_FAIL(TB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
   return TB200_OK;
