@@ -45,10 +45,10 @@ FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 PER_LAUNCH_SAMPLES = 100
 
-# DRAM traffic per launch relative to the algorithmic bytes (dram__bytes_read.sum + dram__bytes_write.sum
-# of one ncu capture of the decode kernel on a quarter-size case; traffic grows in proportion to the live
-# tokens, so the ratio carries over to the full launch).
-NCU_TRAFFIC_RATIO = {"paged_decode_bf16": 1.026}
+# DRAM traffic per launch relative to the algorithmic bytes (dram__bytes.sum of one ncu capture of
+# gqa_decode_tma_kernel on the quarter-batch case ``--case decode_small``: 374.8 MB against 368.07 MB; traffic
+# grows in proportion to the live tokens, so the ratio carries over to the full launch).
+NCU_TRAFFIC_RATIO = {"paged_decode_bf16": 1.018}
 
 
 def measured_peaks():
@@ -657,7 +657,7 @@ def run_manifest_decode(device, peaks):
     """The decode and paged-decode workloads of the operator manifest (the reference's benchmark shapes,
     ``src/tileops/manifest/attention.yaml`` of tile-ai/TileOPs, incl. the batch-1 1k..256k contexts), one
     launch each between its own events.  These inputs are small (most fit the L2), so two figures are given:
-    launches back to back on resident data, and launches after a write larger than the L2."""
+    launches back to back on resident data (graph replay), and launches after a write larger than the L2."""
     from tileops_b200 import workloads as W
     from tileops_b200.manifest import load_workloads
     from tileops_b200.ops import (GroupedQueryAttentionDecodePagedWithKVCacheFwdOp,
@@ -667,16 +667,26 @@ def run_manifest_decode(device, peaks):
 
     def timed(fn, cold: bool, n: int = 30):
         """cold: a write larger than the L2 before every launch, each launch between its own events.
-        warm: ``n`` launches back to back behind one such write (the write keeps the queue busy while the
-        host enqueues, so no host launch latency is inside the events); the average of the launches."""
+        warm: ``n`` launches replayed from one CUDA graph (what a decode loop does; no host launch latency
+        inside the events, which for the small shapes is several times the kernel); the average of the launches."""
         for _ in range(3):
             fn()
         if not cold:
-            flush.zero_()
+            side = torch.cuda.Stream(device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                fn()                                 # workspaces of this stream exist before the capture
+            torch.cuda.current_stream(device).wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(n):
+                    fn()
+            graph.replay()
+            torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for _ in range(n):
-                fn()
+            graph.replay()
             e1.record()
             torch.cuda.synchronize()
             return e0.elapsed_time(e1) * 1e3 / n

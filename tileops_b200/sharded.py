@@ -195,7 +195,9 @@ class KVSequenceShardedPagedDecode:
         torch.cuda.current_stream(q.device).wait_stream(side)
         torch.cuda.synchronize(q.device)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        # captured on the stream of the warm-up: the decode workspace is kept per stream, and one that were
+        # first asked for during the capture would put its zero fill into the graph (4 us at every replay)
+        with torch.cuda.graph(graph, stream=side):
             out = self.forward(*args)
 
         def replay() -> torch.Tensor:
