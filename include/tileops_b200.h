@@ -346,6 +346,16 @@ int tb200_fp8_cache_append(const void* k_new, const void* v_new, void* k_pages, 
  * ------------------------------------------------------------------------- */
 int tb200_mma_issue_probe(int64_t* out_clocks, int n, int a_in_tmem, int repetitions, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * Which kernel served the calling thread's last successful tb200_gqa_decode / tb200_gqa_decode_sharded /
+ * tb200_gqa_decode_noalloc call (0 before the first).  No reference counterpart: the reference's dispatch
+ * reports its choice through `Kernel` objects; here the choice is made inside the library, and tests and
+ * benchmarks ask for it to name what they measured.
+ * ------------------------------------------------------------------------- */
+#define TB200_DECODE_KERNEL_TMA 1       /* gqa_decode_tma_kernel: TMA producer warp + 4 math warps */
+#define TB200_DECODE_KERNEL_CP_ASYNC 2  /* gqa_decode_kernel: every thread loads with cp.async */
+int tb200_gqa_decode_last_kernel(void);
+
 #ifdef __cplusplus
 }
 #endif

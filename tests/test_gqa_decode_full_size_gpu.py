@@ -96,13 +96,42 @@ def test_tma_kernel_and_cp_async_kernel_agree(fp8):
     inp = W.make_paged_decode(71, 24, 32, 8, 128, 64, len_range=(1, 6000), fp8_cache=fp8, device="cuda", spare_pages=2,
                               tail_fill=float("nan"))
     a, la = decode(inp, return_lse=True, out_dtype=torch.float32, config={"tma": True})
+    assert F.decode_last_kernel() == "tma"
     b, lb = decode(inp, return_lse=True, out_dtype=torch.float32, config={"tma": False})
+    assert F.decode_last_kernel() == "cp_async"
     assert not torch.isnan(a).any() and not torch.isnan(b).any()
     torch.testing.assert_close(a, b, atol=2e-3, rtol=1e-2)
     torch.testing.assert_close(la, lb, atol=1e-4, rtol=1e-5)
     if not fp8:
         close(a, O.paged_decode_ref(inp.q.cpu(), inp.k.cpu(), inp.v.cpu(), inp.real_seqlen_kv.cpu(),
                                     inp.block_table.cpu(), 64))
+
+
+@pytest.mark.parametrize("page,D,dtype", [(16, 128, torch.bfloat16), (32, 128, torch.float16), (16, 64, torch.bfloat16),
+                                          (32, 64, torch.bfloat16)])
+def test_small_pages_through_the_tma_kernel(page, D, dtype):
+    """Pages of 16 and 32 tokens: a 64-token tile is four or two copies of one page each.  Ragged lengths
+    whose last tile reaches past the sequence's own pages, NaN behind every sequence end, and a block table
+    that is exactly as wide as the longest sequence needs (a lookup behind a sequence's pages would leave the
+    row, or the tensor)."""
+    lens = [1, 15, 16, 17, 63, 64, 65, 100, 1000, 2049, 4096 + 33, 0]
+    inp = W.make_paged_decode(73, len(lens), 32, 8, D, page, lens=lens, dtype=dtype, device="cuda",
+                              tail_fill=float("nan"))
+    assert inp.block_table.shape[1] == -(-max(lens) // page)
+    a, la = decode(inp, return_lse=True, out_dtype=torch.float32, config={"tma": True})
+    assert F.decode_last_kernel() == "tma"
+    b, lb = decode(inp, return_lse=True, out_dtype=torch.float32, config={"tma": False})
+    assert F.decode_last_kernel() == "cp_async"
+    live = [i for i, n in enumerate(lens) if n > 0]
+    assert not torch.isnan(a[live]).any() and not torch.isnan(b[live]).any()
+    torch.testing.assert_close(a[live], b[live], atol=2e-3, rtol=1e-2)
+    torch.testing.assert_close(la[live], lb[live], atol=1e-4, rtol=1e-5)
+    close(a[live], O.paged_decode_ref(inp.q.cpu(), inp.k.cpu(), inp.v.cpu(), inp.real_seqlen_kv.cpu(),
+                                      inp.block_table.cpu(), page)[live])
+    # an e4m3 cache with small pages has several scales per tile: the other kernel serves it
+    inp8 = W.make_paged_decode(74, 3, 32, 8, 128, page, lens=[100, 700, 64], fp8_cache=True, device="cuda")
+    decode(inp8)
+    assert F.decode_last_kernel() == "cp_async"
 
 
 @pytest.mark.parametrize("tma", [True, False])

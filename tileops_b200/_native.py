@@ -115,6 +115,7 @@ SIGNATURES = {
         c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,  # cu_q cu_kv cache bt stride k_scale v_scale
         c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),          # dtype total_kv B Hkv D page stream
     "tb200_mma_issue_probe": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p]),
+    "tb200_gqa_decode_last_kernel": (c_int, []),
     "tb200_fp8_cache_append": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p,                         # k_new v_new k_pages v_pages
         c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,      # cu_q cache bt stride k_scale v_scale

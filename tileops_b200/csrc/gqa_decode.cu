@@ -814,6 +814,8 @@ extern "C" size_t tb200_gqa_decode_workspace_bytes(int batch, int heads, int hea
 }
 
 namespace {
+// which kernel served this thread's last decode call (tb200_gqa_decode_last_kernel)
+thread_local int t_last_kernel = 0;
 struct PeerTargets {
   int world, rank;
   void* const* buffers;   // [world] base of every rank's exchange buffer, as mapped into this process
@@ -908,8 +910,12 @@ int decode_impl(const void* q, const void* k, const void* v, void* o, float* lse
   // declines everything else, and the cp.async kernel below serves every layout.
   if (!var.no_tma && !var.fp8_mma && var.wide != 1) {
     const int st = launch_decode_tma(p, q_dtype, kv_dtype, o_dtype, dim, L.nt, kv_pool_tokens, s);
-    if (st != kTmaNotApplicable) return st;
+    if (st != kTmaNotApplicable) {
+      if (st == TB200_OK) t_last_kernel = TB200_DECODE_KERNEL_TMA;
+      return st;
+    }
   }
+  t_last_kernel = TB200_DECODE_KERNEL_CP_ASYNC;
   if (dim == 128)
     return L.nt == 1 ? launch_t<128, 1>(p, q_dtype, kv_dtype, o_dtype, wide, var.fp8_mma, s)
                      : launch_t<128, 2>(p, q_dtype, kv_dtype, o_dtype, wide, var.fp8_mma, s);
@@ -917,6 +923,8 @@ int decode_impl(const void* q, const void* k, const void* v, void* o, float* lse
                    : launch_t<64, 2>(p, q_dtype, kv_dtype, o_dtype, wide, var.fp8_mma, s);
 }
 }  // namespace
+
+extern "C" int tb200_gqa_decode_last_kernel(void) { return t_last_kernel; }
 
 extern "C" int tb200_gqa_decode(const void* q, const void* k, const void* v, void* o, float* lse,
                                 const int32_t* real_seqlen_kv, int32_t uniform_seqlen,

@@ -49,6 +49,7 @@ struct DecodeParams {
   int n_hb;     // head blocks per KV head
   int page_size;
   int tile_in_page;  // 1 when page_size % 64 == 0: a tile never straddles two pages
+  int box_rows;      // TMA kernel: token rows per copy (64, or the page size when a tile spans 2 or 4 pages)
   int64_t tok_stride, head_stride, batch_stride;  // elements
   float sm_scale, softcap;
   int q_is_bf16;

@@ -19,8 +19,9 @@
 //     load instruction or address computation for K/V; stages are handed over with mbarriers, one
 //     arrival per warp; the four warps meet once per item in an 8.7 KB area of its own, half of the
 //     head dims at a time.
-// Served layouts: 64-token tiles contiguous in memory (no block table, or page_size % 64 == 0), token
-// rows of 128 or 256 bytes, up to 8 q heads per KV head.  Everything else goes to gqa_decode.cu.
+// Served layouts: 64-token tiles that are one copy (no block table, or page_size % 64 == 0) or, for a 16-bit
+// cache, two or four copies of one whole page each (page_size 32 or 16); token rows of 128 or 256 bytes, up
+// to 8 q heads per KV head.  Everything else goes to gqa_decode.cu.
 //
 // Rows of the last tile behind the sequence end are whatever the pool holds: their scores are
 // replaced by -inf, and their V rows are zeroed in shared memory by the warp that owns them before
@@ -296,25 +297,38 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       }
       const int32_t* bt_row = p.bt ? p.bt + size_t(d.b) * p.bt_stride : nullptr;
       const int coord_b = p.bt ? 0 : d.b;
+      const int nb = kTile / p.box_rows;    // copies per tile and panel: 1, or 2 / 4 when a tile spans pages of 32 / 16 tokens
       for (int t0 = d.tile0; t0 < d.tile1 && alive; t0 += 32) {
-        // 32 tiles per round: lane l reads the table entry (and the scales) of tile t0 + l
+        // 32 tiles per round: lane l reads the table entries (and the scales) of tile t0 + l
         const int t = t0 + lane;
-        int tok = 0;
+        int tok[4] = {0, 0, 0, 0};            // pool row of each copy of the tile
         float ks = 0.f, vs = 0.f;
         if (t < d.tile1) {
-          tok = t * kTile;
+          tok[0] = t * kTile;
           if (bt_row) {
-            const int pg = bt_row[tok / p.page_size];
-            tok = pg * p.page_size + tok % p.page_size;
-            if constexpr (FP8) {
-              ks = p.k_scale[size_t(pg) * p.heads_kv + d.hk];
-              vs = p.v_scale[size_t(pg) * p.heads_kv + d.hk];
+            if (nb == 1) {
+              const int pg = bt_row[tok[0] / p.page_size];
+              tok[0] = pg * p.page_size + tok[0] % p.page_size;
+              if constexpr (FP8) {
+                ks = p.k_scale[size_t(pg) * p.heads_kv + d.hk];
+                vs = p.v_scale[size_t(pg) * p.heads_kv + d.hk];
+              }
+            } else {
+              // one whole page per copy.  The last tile may reach past the sequence's pages: a copy that
+              // starts behind the last token re-reads the page of that token (its rows are masked and
+              // their V cleared), never a table entry behind the sequence's own.
+#pragma unroll
+              for (int x = 3; x >= 0; --x)
+                if (x < nb) tok[x] = bt_row[min(t * kTile + x * p.box_rows, d.len - 1) / p.page_size] * p.page_size;
             }
           }
         }
         const int n = min(32, d.tile1 - t0);
         for (int i = 0; i < n; ++i) {
-          const int tok_i = __shfl_sync(0xffffffffu, tok, i);
+          int tok_i[4];
+          tok_i[0] = __shfl_sync(0xffffffffu, tok[0], i);
+#pragma unroll
+          for (int x = 1; x < 4; ++x) tok_i[x] = nb > 1 ? __shfl_sync(0xffffffffu, tok[x], i) : 0;
           const float ks_i = FP8 ? __shfl_sync(0xffffffffu, ks, i) : 0.f;
           const float vs_i = FP8 ? __shfl_sync(0xffffffffu, vs, i) : 0.f;
           if (lane == 0) {
@@ -326,12 +340,18 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
               mbar_expect_tx(bar_full(stage), C::kStageBytes);
               const uint32_t dst = sbase + C::ring + stage * C::kStageBytes;
 #pragma unroll
-              for (int pn = 0; pn < C::kPanels; ++pn)
-                tma_load_4d(dst + pn * C::kPanelBytes, &map_k, bar_full(stage), pn * C::kPanelElems, d.hk, tok_i, coord_b);
+              for (int x = 0; x < 4; ++x) {
+                if (x < nb) {
+                  const uint32_t dx = dst + x * p.box_rows * 128;
 #pragma unroll
-              for (int pn = 0; pn < C::kPanels; ++pn)
-                tma_load_4d(dst + C::kTensorBytes + pn * C::kPanelBytes, &map_v, bar_full(stage), pn * C::kPanelElems,
-                            d.hk, tok_i, coord_b);
+                  for (int pn = 0; pn < C::kPanels; ++pn)
+                    tma_load_4d(dx + pn * C::kPanelBytes, &map_k, bar_full(stage), pn * C::kPanelElems, d.hk, tok_i[x], coord_b);
+#pragma unroll
+                  for (int pn = 0; pn < C::kPanels; ++pn)
+                    tma_load_4d(dx + C::kTensorBytes + pn * C::kPanelBytes, &map_v, bar_full(stage), pn * C::kPanelElems,
+                                d.hk, tok_i[x], coord_b);
+                }
+              }
             } else {
               ok = 0;
             }
@@ -728,14 +748,15 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 // ---- host side ------------------------------------------------------------------------------
 
 // [batches, tokens, heads_kv, D] (strides in elements) -> 4-D map (d, head, token, batch) with a box of
-// one 128-byte panel x 64 tokens, 128B swizzle.  16-bit elements are described as UINT16, e4m3 as UINT8:
+// one 128-byte panel x box_rows tokens (64, or one page of 16 or 32), 128B swizzle.  16-bit elements are described as UINT16, e4m3 as UINT8:
 // the copy never interprets them.
 struct MapKey {
   const void* base;
-  int esize, heads_kv, dim;
+  int esize, heads_kv, dim, box_rows;
   long long tokens, batches, tok_stride, head_stride, batch_stride;
   bool operator==(const MapKey& o) const {
-    return base == o.base && esize == o.esize && heads_kv == o.heads_kv && dim == o.dim && tokens == o.tokens &&
+    return base == o.base && esize == o.esize && heads_kv == o.heads_kv && dim == o.dim && box_rows == o.box_rows &&
+           tokens == o.tokens &&
            batches == o.batches && tok_stride == o.tok_stride && head_stride == o.head_stride &&
            batch_stride == o.batch_stride;
   }
@@ -747,7 +768,7 @@ int encode_kv_map(CUtensorMap* map, const MapKey& k) {
   cuuint64_t dims[4] = {cuuint64_t(k.dim), cuuint64_t(k.heads_kv), cuuint64_t(k.tokens), cuuint64_t(k.batches)};
   cuuint64_t strides[3] = {cuuint64_t(k.head_stride) * k.esize, cuuint64_t(k.tok_stride) * k.esize,
                            cuuint64_t(k.batch_stride) * k.esize};
-  cuuint32_t box[4] = {cuuint32_t(128 / k.esize), 1, cuuint32_t(kTile), 1};
+  cuuint32_t box[4] = {cuuint32_t(128 / k.esize), 1, cuuint32_t(k.box_rows), 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   // a 256-byte fetch per 128-byte request pays when the neighbouring 128 bytes are the same head's second
   // panel; when a head's row is 128 bytes (e4m3, or 16-bit at head dim 64) they belong to another head,
@@ -820,13 +841,20 @@ int launch_tma_o(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParam
 
 }  // namespace
 
-int launch_decode_tma(const DecodeParams& p, int q_dtype, int kv_dtype, int o_dtype, int dim, int nt,
+int launch_decode_tma(const DecodeParams& params, int q_dtype, int kv_dtype, int o_dtype, int dim, int nt,
                       long long pool_tokens, cudaStream_t stream) {
   const bool fp8 = kv_dtype == TB200_E4M3;
   const int esize = fp8 ? 1 : 2;
   const int row_bytes = dim * esize;
   if (nt != 1 || (row_bytes != 128 && row_bytes != 256)) return kTmaNotApplicable;
-  if (p.bt && !p.tile_in_page) return kTmaNotApplicable;
+  DecodeParams p = params;
+  p.box_rows = kTile;
+  if (p.bt && !p.tile_in_page) {
+    // pages of 16 or 32 tokens (16-bit cache): a tile is 4 or 2 copies of one page each.  An e4m3 cache has
+    // one scale per page, i.e. several per tile, which the math warps do not apply: the other kernel serves it.
+    if (fp8 || (p.page_size != 16 && p.page_size != 32)) return kTmaNotApplicable;
+    p.box_rows = p.page_size;
+  }
   if (fp8 && !p.bt) return kTmaNotApplicable;              // scales are indexed by page: needs the table
   if (reinterpret_cast<uintptr_t>(p.q) & 15) return kTmaNotApplicable;
   if (p.tok_stride <= 0 || p.head_stride <= 0) return kTmaNotApplicable;
@@ -839,7 +867,7 @@ int launch_decode_tma(const DecodeParams& p, int q_dtype, int kv_dtype, int o_dt
   }
 
   MapKey key{};
-  key.esize = esize; key.heads_kv = p.heads_kv; key.dim = dim;
+  key.esize = esize; key.heads_kv = p.heads_kv; key.dim = dim; key.box_rows = p.box_rows;
   key.tok_stride = p.tok_stride; key.head_stride = p.head_stride;
   if (p.bt) {
     key.tokens = pool_tokens > 0 ? pool_tokens : 0x7fffffffLL;   // unknown pool size: only the table bounds the reads

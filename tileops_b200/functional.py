@@ -247,6 +247,12 @@ def decode_status(device: "torch.device | str | int | None" = None) -> int:
     return worst
 
 
+def decode_last_kernel() -> str:
+    """Name of the kernel that served this thread's last decode call: ``"tma"`` (TMA producer warp + math
+    warps), ``"cp_async"``, or ``""`` before the first call."""
+    return {1: "tma", 2: "cp_async"}.get(int(N.lib().tb200_gqa_decode_last_kernel()), "")
+
+
 def gqa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal: bool = True,
                 sm_scale: Optional[float] = None, softcap: float = 0.0, return_lse: bool = False,
                 window_size_left: int = -1, window_size_right: int = -1, config: Optional[dict] = None):
