@@ -128,10 +128,31 @@ def test_small_pages_through_the_tma_kernel(page, D, dtype):
     torch.testing.assert_close(la[live], lb[live], atol=1e-4, rtol=1e-5)
     close(a[live], O.paged_decode_ref(inp.q.cpu(), inp.k.cpu(), inp.v.cpu(), inp.real_seqlen_kv.cpu(),
                                       inp.block_table.cpu(), page)[live])
-    # an e4m3 cache with small pages has several scales per tile: the other kernel serves it
-    inp8 = W.make_paged_decode(74, 3, 32, 8, 128, page, lens=[100, 700, 64], fp8_cache=True, device="cuda")
-    decode(inp8)
+
+
+@pytest.mark.parametrize("page", [16, 32])
+def test_small_pages_of_an_fp8_cache_through_the_tma_kernel(page):
+    """An e4m3 cache with pages of 16 / 32 tokens has four / two scale pairs per 64-token tile; every page gets
+    a scale of its own magnitude here, so a warp that took a neighbouring page's scale would be far off."""
+    lens = [1, 17, 64, 100, 1000, 2049, 0]
+    inp = W.make_paged_decode(74, len(lens), 64, 8, 128, page, lens=lens, fp8_cache=True, device="cuda")
+    # spread the scales over a factor of 8 (downwards, so that the outputs stay O(1)): the oracle and both
+    # kernels dequantise with the same (page, head) scales
+    g = torch.Generator(device="cuda").manual_seed(5)
+    factor = torch.exp2(torch.randint(-3, 1, inp.k_scale.shape, generator=g, device="cuda").float())
+    inp.k_scale = (inp.k_scale * factor).contiguous()
+    inp.v_scale = (inp.v_scale * factor.flip(0)).contiguous()
+    a, la = decode(inp, return_lse=True, out_dtype=torch.float32, config={"tma": True})
+    assert F.decode_last_kernel() == "tma"
+    b, lb = decode(inp, return_lse=True, out_dtype=torch.float32, config={"tma": False})
     assert F.decode_last_kernel() == "cp_async"
+    live = [i for i, n in enumerate(lens) if n > 0]
+    assert not torch.isnan(a[live]).any()
+    torch.testing.assert_close(a[live], b[live], atol=5e-3, rtol=1e-2)
+    torch.testing.assert_close(la[live], lb[live], atol=1e-3, rtol=1e-4)
+    ref = O.paged_decode_fp8_ref(inp.q.cpu(), inp.k.cpu(), inp.v.cpu(), inp.k_scale.cpu(), inp.v_scale.cpu(),
+                                 inp.real_seqlen_kv.cpu(), inp.block_table.cpu(), page)
+    close(a[live], ref[live], atol=FP8_ATOL)
 
 
 @pytest.mark.parametrize("tma", [True, False])

@@ -19,9 +19,9 @@
 //     load instruction or address computation for K/V; stages are handed over with mbarriers, one
 //     arrival per warp; the four warps meet once per item in an 8.7 KB area of its own, half of the
 //     head dims at a time.
-// Served layouts: 64-token tiles that are one copy (no block table, or page_size % 64 == 0) or, for a 16-bit
-// cache, two or four copies of one whole page each (page_size 32 or 16); token rows of 128 or 256 bytes, up
-// to 8 q heads per KV head.  Everything else goes to gqa_decode.cu.
+// Served layouts: 64-token tiles that are one copy (no block table, or page_size % 64 == 0) or two or four
+// copies of one whole page each (page_size 32 or 16); token rows of 128 or 256 bytes, up to 8 q heads per
+// KV head.  Everything else goes to gqa_decode.cu.
 //
 // Rows of the last tile behind the sequence end are whatever the pool holds: their scores are
 // replaced by -inf, and their V rows are zeroed in shared memory by the warp that owns them before
@@ -78,12 +78,12 @@ struct TmaCfg {
   static constexpr int qslots = ring + kStages * kStageBytes;
   static constexpr int merge = qslots + kItemSlots * kQSlotBytes;
   static constexpr int ml = merge + kMergeBytes;
-  static constexpr int scales = ml + kMlBytes;               // [kStages][2] fp32 (FP8 only)
-  static constexpr int bars = scales + 64;                   // full[kStages], empty[kStages], item_full[2], item_empty[2], math
+  static constexpr int scales = ml + kMlBytes;               // [kStages][4 copies][K, V] fp32 (FP8 only)
+  static constexpr int bars = scales + 128;                   // full[kStages], empty[kStages], item_full[2], item_empty[2], math
   static constexpr int misc = bars + 8 * (2 * kStages + 2 * kItemSlots + 1);  // 16 ints
   static constexpr int plan = misc + 64;                     // s_prefix [batch + 1], s_lens [batch]
   static_assert(kRowBytes == 128 || kRowBytes == 256, "token rows must be one or two 128-byte panels");
-  static_assert(kStages * 2 * 4 <= 64, "scale slots");
+  static_assert(kStages * 8 * 4 <= 128, "scale slots");
 };
 
 template <int D, bool FP8>
@@ -302,7 +302,7 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         // 32 tiles per round: lane l reads the table entries (and the scales) of tile t0 + l
         const int t = t0 + lane;
         int tok[4] = {0, 0, 0, 0};            // pool row of each copy of the tile
-        float ks = 0.f, vs = 0.f;
+        float ks[4] = {0.f, 0.f, 0.f, 0.f}, vs[4] = {0.f, 0.f, 0.f, 0.f};   // and, for an e4m3 cache, its page's scales
         if (t < d.tile1) {
           tok[0] = t * kTile;
           if (bt_row) {
@@ -310,32 +310,50 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
               const int pg = bt_row[tok[0] / p.page_size];
               tok[0] = pg * p.page_size + tok[0] % p.page_size;
               if constexpr (FP8) {
-                ks = p.k_scale[size_t(pg) * p.heads_kv + d.hk];
-                vs = p.v_scale[size_t(pg) * p.heads_kv + d.hk];
+                ks[0] = p.k_scale[size_t(pg) * p.heads_kv + d.hk];
+                vs[0] = p.v_scale[size_t(pg) * p.heads_kv + d.hk];
               }
             } else {
               // one whole page per copy.  The last tile may reach past the sequence's pages: a copy that
               // starts behind the last token re-reads the page of that token (its rows are masked and
               // their V cleared), never a table entry behind the sequence's own.
 #pragma unroll
-              for (int x = 3; x >= 0; --x)
-                if (x < nb) tok[x] = bt_row[min(t * kTile + x * p.box_rows, d.len - 1) / p.page_size] * p.page_size;
+              for (int x = 3; x >= 0; --x) {
+                if (x < nb) {
+                  const int pg = bt_row[min(t * kTile + x * p.box_rows, d.len - 1) / p.page_size];
+                  tok[x] = pg * p.page_size;
+                  if constexpr (FP8) {
+                    ks[x] = p.k_scale[size_t(pg) * p.heads_kv + d.hk];
+                    vs[x] = p.v_scale[size_t(pg) * p.heads_kv + d.hk];
+                  }
+                }
+              }
             }
           }
         }
         const int n = min(32, d.tile1 - t0);
         for (int i = 0; i < n; ++i) {
           int tok_i[4];
-          tok_i[0] = __shfl_sync(0xffffffffu, tok[0], i);
+          float ks_i[4] = {0.f, 0.f, 0.f, 0.f}, vs_i[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int x = 1; x < 4; ++x) tok_i[x] = nb > 1 ? __shfl_sync(0xffffffffu, tok[x], i) : 0;
-          const float ks_i = FP8 ? __shfl_sync(0xffffffffu, ks, i) : 0.f;
-          const float vs_i = FP8 ? __shfl_sync(0xffffffffu, vs, i) : 0.f;
+          for (int x = 0; x < 4; ++x) {
+            const bool used = x == 0 || nb > 1;            // uniform across the warp
+            tok_i[x] = used ? __shfl_sync(0xffffffffu, tok[x], i) : 0;
+            if constexpr (FP8) {
+              if (used) {
+                ks_i[x] = __shfl_sync(0xffffffffu, ks[x], i);
+                vs_i[x] = __shfl_sync(0xffffffffu, vs[x], i);
+              }
+            }
+          }
           if (lane == 0) {
             if (mbar_wait_bounded(bar_empty(stage), stage_par ^ 1, s_abort, status, 601, limit)) {
               if constexpr (FP8) {
-                s_scales[stage * 2] = ks_i;
-                s_scales[stage * 2 + 1] = vs_i;
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                  s_scales[stage * 8 + x * 2] = ks_i[x];
+                  s_scales[stage * 8 + x * 2 + 1] = vs_i[x];
+                }
               }
               mbar_expect_tx(bar_full(stage), C::kStageBytes);
               const uint32_t dst = sbase + C::ring + stage * C::kStageBytes;
@@ -565,10 +583,13 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         }
 
         // ---- scale, softcap, mask, online softmax ----------------------------------------
-        float sc = qk_scale, vsc = 1.f;    // one K scale and one V scale per tile: the tile lies in one page
+        // one K scale and one V scale per page; this warp's 16 rows lie in one page (the tile's only one, or
+        // with pages of 32 / 16 tokens the tile's copy number warp / 2 or warp)
+        float sc = qk_scale, vsc = 1.f;
         if constexpr (FP8) {
-          sc *= s_scales[stage * 2] * kE4m3Unit;
-          vsc = s_scales[stage * 2 + 1] * kE4m3Unit;
+          const int copy = (warp * 16) / p.box_rows;
+          sc *= s_scales[stage * 8 + copy * 2] * kE4m3Unit;
+          vsc = s_scales[stage * 8 + copy * 2 + 1] * kE4m3Unit;
         }
         const bool ok_lo = tok_a < len, ok_hi = tok_a + 8 < len;
         uint32_t pb[2];
@@ -850,9 +871,9 @@ int launch_decode_tma(const DecodeParams& params, int q_dtype, int kv_dtype, int
   DecodeParams p = params;
   p.box_rows = kTile;
   if (p.bt && !p.tile_in_page) {
-    // pages of 16 or 32 tokens (16-bit cache): a tile is 4 or 2 copies of one page each.  An e4m3 cache has
-    // one scale per page, i.e. several per tile, which the math warps do not apply: the other kernel serves it.
-    if (fp8 || (p.page_size != 16 && p.page_size != 32)) return kTmaNotApplicable;
+    // pages of 16 or 32 tokens: a tile is 4 or 2 copies of one page each (every math warp's 16 rows still lie
+    // in one page, so an e4m3 cache's per-page scales stay one pair per warp and tile)
+    if (p.page_size != 16 && p.page_size != 32) return kTmaNotApplicable;
     p.box_rows = p.page_size;
   }
   if (fp8 && !p.bt) return kTmaNotApplicable;              // scales are indexed by page: needs the table
