@@ -905,8 +905,8 @@ int decode_impl(const void* q, const void* k, const void* v, void* o, float* lse
   p.part_ml = reinterpret_cast<float*>(ws + L.counters_bytes + L.part_o_bytes);
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // The TMA kernel serves caches whose 64-token tiles are contiguous (no table, or pages that are
-  // multiples of 64 tokens) with 128- or 256-byte token rows and up to 8 q heads per KV head; it
+  // The TMA kernel serves caches whose 64-token tiles are contiguous or whole pages (no table, pages that
+  // are multiples of 64 tokens, pages of 16 or 32) with 128- or 256-byte token rows and up to 8 q heads per KV head; it
   // declines everything else, and the cp.async kernel below serves every layout.
   if (!var.no_tma && !var.fp8_mma && var.wide != 1) {
     const int st = launch_decode_tma(p, q_dtype, kv_dtype, o_dtype, dim, L.nt, kv_pool_tokens, s);
