@@ -579,7 +579,13 @@ template <typename T, bool kSoftcap, int HD, bool kPaged>
 int launch_prefill(const PrefillMaps& m, const PrefillParams& p, cudaStream_t stream) {
   auto kern = gqa_prefill_kernel<T, kSoftcap, HD, kPaged>;
   const int smem = SmemLayoutT<HD>::total + 1024;
-  TB200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  static thread_local bool configured[64] = {false};       // per device, for this instantiation
+  int dev = 0;
+  TB200_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    TB200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
   const int n_m = (p.seqlen_q + kBM - 1) / kBM;
   const long long grid = (long long)n_m * p.heads * p.batch;
   if (grid > 0x7fffffffLL) TB200_FAIL(TB200_ERR_UNSUPPORTED, "problem too large for one launch");

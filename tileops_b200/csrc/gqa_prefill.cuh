@@ -33,7 +33,7 @@ struct PrefillParams {
 };
 
 // [batch, seq, heads, hd] contiguous 16-bit tensor -> 4-D map (d, head, seq, batch), box 64 x 1 x box_rows x 1
-inline int make_map(CUtensorMap* map, const void* base, int dtype, long long batch, long long seq, int heads, int hd,
+inline int encode_map(CUtensorMap* map, const void* base, int dtype, long long batch, long long seq, int heads, int hd,
              int box_rows) {
   EncodeTiledFn enc = tensor_map_encoder();
   if (!enc) TB200_FAIL(TB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
@@ -47,6 +47,31 @@ inline int make_map(CUtensorMap* map, const void* base, int dtype, long long bat
                    hd * 2 >= 256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,   // a head's row
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) TB200_FAIL(TB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+  return TB200_OK;
+}
+
+// Encoding a map is a driver call (microseconds on the host); a serving loop presents the same pools, and
+// often the same q / k_new / v_new staging buffers, call after call, so the last few maps are kept per thread.
+inline int make_map(CUtensorMap* map, const void* base, int dtype, long long batch, long long seq, int heads, int hd,
+                    int box_rows) {
+  struct Key {
+    const void* base; int dtype, heads, hd, box_rows; long long batch, seq;
+    bool operator==(const Key& o) const {
+      return base == o.base && dtype == o.dtype && heads == o.heads && hd == o.hd && box_rows == o.box_rows &&
+             batch == o.batch && seq == o.seq;
+    }
+  };
+  constexpr int kSlots = 16;
+  struct Slot { Key key; CUtensorMap map; bool used; };
+  static thread_local Slot cache[kSlots] = {};
+  static thread_local int next = 0;
+  const Key key{base, dtype, heads, hd, box_rows, batch, seq};
+  for (int i = 0; i < kSlots; ++i)
+    if (cache[i].used && cache[i].key == key) { *map = cache[i].map; return TB200_OK; }
+  const int st = encode_map(map, base, dtype, batch, seq, heads, hd, box_rows);
+  if (st != TB200_OK) return st;
+  cache[next] = Slot{key, *map, true};
+  next = (next + 1) % kSlots;
   return TB200_OK;
 }
 
