@@ -285,6 +285,32 @@ int tb200_gqa_prefill_paged(const void* q, const void* k_new, const void* v_new,
                             void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * Packed prefill of one chunk per request over an FP8-e4m3 paged cache, appending the chunk: ONE launch.
+ *
+ * Replaces the forward of GQAPrefillPagedWithFP8KVCacheFwdKernel
+ * (src/tileops/kernels/attention/gqa_fwd.py:1005-1460; dequantisation at :1059-1065): the kernel of
+ * tb200_gqa_prefill_paged reads the e4m3 pages by TMA, four converter warps expand each cached tile in shared
+ * memory to the bare e4m3 values in dtype (exact), the tcgen05 MMAs run on the 16-bit tile, the two scalar
+ * scales are applied in the softmax (K: to the scores of cached tiles, V: in the exponent of their P; the
+ * dequantised values are therefore NOT rounded to dtype first as the reference does - the result is within the
+ * operator's tolerance and slightly more accurate), and the appending CTAs quantise the chunk into the pages
+ * (x8 = e4m3(x / scale), round to nearest even, saturating at +-448).  An e4m3 NaN code in a page reads as +-480.
+ * Measured 20-30 % slower than the three launches below (it converts a tile once per CTA that shares the KV
+ * head); it needs no packed 16-bit copy of the cache.
+ *   k_pages, v_pages [pool_tokens, heads_kv, dim] e4m3 (modified in place: rows cache_seqlens[b] ...)
+ *   k_scale, v_scale  device pointers to ONE fp32 each (the reference keeps one scalar scale per tensor)
+ *   every other argument as for tb200_gqa_prefill_paged with a cache; dim must be 128 (other head dims:
+ *   tb200_fp8_cache_gather + tb200_gqa_prefill_paged + tb200_fp8_cache_append below)
+ * ------------------------------------------------------------------------- */
+int tb200_gqa_prefill_paged_e4m3_cache(const void* q, const void* k_new, const void* v_new, void* k_pages,
+                                       void* v_pages, const float* k_scale, const float* v_scale, void* o,
+                                       float* lse, const int32_t* cu_seqlens_q, const int32_t* cache_seqlens,
+                                       const int32_t* block_table, int64_t block_table_stride, int dtype,
+                                       int total_q, int batch, int max_seqlen_q, int heads, int heads_kv, int dim,
+                                       int page_size, int64_t pool_tokens, int is_causal, float sm_scale,
+                                       float softcap, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
  * GPT-NeoX rotary embedding of a packed tensor at the positions of a prefill chunk.
  *
  * The rotation the reference's fused-RoPE paged prefill applies to q and k_new
@@ -307,7 +333,8 @@ int tb200_rope_neox_packed(const void* x, void* y, const void* cos_table, const 
  * FP8-e4m3 paged cache with one scalar scale per tensor, around a prefill chunk.
  *
  * Together with tb200_gqa_prefill_paged (no cache, cu_seqlens_kv given) these two replace the forward of
- * GQAPrefillPagedWithFP8KVCacheFwdKernel (src/tileops/kernels/attention/gqa_fwd.py:1005-1460):
+ * GQAPrefillPagedWithFP8KVCacheFwdKernel (src/tileops/kernels/attention/gqa_fwd.py:1005-1460) for head dims
+ * other than 128 (head dim 128: tb200_gqa_prefill_paged_e4m3_cache above, one launch):
  *
  * tb200_fp8_cache_gather builds the packed 16-bit K/V the attention reads: for request b, rows
  * cu_seqlens_kv[b] .. +cache_seqlens[b] are its cached tokens dequantised (float(x8) * scale, rounded to

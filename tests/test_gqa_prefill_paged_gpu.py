@@ -364,6 +364,58 @@ def test_paged_op_with_fp8_cache_like_the_reference_test(is_causal, softcap, dty
         op(q.cuda(), kn.cuda(), vn.cuda(), kpd, vpd, ks.cuda() * 0, vs.cuda(), cu.cuda(), cache.cuda(), bt.cuda(), 48)
 
 
+@pytest.mark.parametrize("dtype,page,is_causal,softcap,q_lens,old_lens", [
+    (torch.float16, 64, True, None, [200, 130], [300, 1]),        # two row tiles, ragged last cached tile
+    (torch.bfloat16, 16, True, None, [33, 48, 1], [67, 80, 0]),   # small pages; a request with no cache yet
+    (torch.float16, 32, True, 2.0, [129, 5], [64, 127]),          # softcap; cache length exactly one tile / one short
+    (torch.bfloat16, 128, False, None, [64, 64], [1000, 513]),    # many cached tiles, non-causal chunk
+])
+def test_fused_fp8_cache_prefill_at_head_dim_128(dtype, page, is_causal, softcap, q_lens, old_lens):
+    """The one-launch path (``fused=True``: e4m3 pages read by TMA, expanded in shared memory by the converter
+    warps, scalar scales folded into the softmax, chunk quantised on append) against the dequantise-then-attend
+    oracle, against the three-launch path, and the pages bit for bit."""
+    F = _F()
+    f8 = torch.float8_e4m3fn
+    g = torch.Generator().manual_seed(44)
+    heads, heads_kv, dim = 8, 2, 128
+    B = len(q_lens)
+    W = -(-(max(o + n for o, n in zip(old_lens, q_lens))) // page) + 1
+    cu = torch.zeros(B + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(q_lens).cumsum(0)
+    total = int(cu[-1])
+    cache = torch.tensor(old_lens, dtype=torch.int32)
+    bt = torch.randperm(B * W, generator=g).to(torch.int32).reshape(B, W)
+    ks, vs = torch.tensor([0.02]), torch.tensor([0.025])
+    q = torch.randn(total, heads, dim, generator=g).to(dtype)
+    kn = (torch.randn(total, heads_kv, dim, generator=g) * 0.5).to(dtype)
+    vn = (torch.randn(total, heads_kv, dim, generator=g) * 0.5).to(dtype)
+    # unwritten pool rows hold the e4m3 NaN code: a kernel that let one reach the MMA would show it
+    kp = torch.full((B * W * page, heads_kv, dim), float("nan")).to(f8)
+    vp = kp.clone()
+    for b, n in enumerate(old_lens):
+        if n:
+            rows = torch.from_numpy(O.physical_rows(bt[b].numpy(), n, page))
+            kp[rows] = ((torch.randn(n, heads_kv, dim, generator=g) * 0.5).to(dtype).float() / ks[0]).to(f8)
+            vp[rows] = ((torch.randn(n, heads_kv, dim, generator=g) * 0.5).to(dtype).float() / vs[0]).to(f8)
+    ref_o, ref_kp, ref_vp = O.prefill_paged_fp8_cache_ref(q, kn, vn, kp, vp, ks, vs, cu, cache, bt, page,
+                                                          is_causal=is_causal, softcap=softcap)
+    dev = [x.cuda() for x in (q, kn, vn)]
+    meta = [x.cuda() for x in (ks, vs, cu, cache, bt)]
+    outs = {}
+    for fused in (True, False):
+        kpd, vpd = kp.cuda(), vp.cuda()
+        o = F.gqa_prefill_paged_fp8_cache(*dev, kpd, vpd, *meta, max(q_lens), page_size=page, is_causal=is_causal,
+                                          softcap=softcap or 0.0, fused=fused)
+        assert not torch.isnan(o).any()
+        torch.testing.assert_close(o.cpu().float(), ref_o.float(), **TOL[dtype])
+        live = ~torch.isnan(ref_kp.float())
+        assert torch.equal(kpd.cpu().view(torch.uint8)[live], ref_kp.view(torch.uint8)[live])
+        assert torch.equal(vpd.cpu().view(torch.uint8)[live], ref_vp.view(torch.uint8)[live])
+        assert torch.equal(kpd.cpu().view(torch.uint8)[~live], kp.view(torch.uint8)[~live])      # nothing else moved
+        outs[fused] = o
+    torch.testing.assert_close(outs[True].float(), outs[False].float(), atol=4e-3, rtol=1e-2)
+
+
 def test_fp8_cache_golden_vectors():
     G = np.load(os.path.join(HERE, "golden", "gqa_golden.npz"))
 

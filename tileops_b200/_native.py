@@ -106,6 +106,11 @@ SIGNATURES = {
         c_void_p, c_void_p, c_void_p, c_void_p, c_int64,        # cu_seqlens_q cu_seqlens_kv cache_seqlens block_table stride
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int,  # dtype total_q total_kv B maxq H Hkv D page pool causal
         c_float, c_float, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "tb200_gqa_prefill_paged_e4m3_cache": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # q k_new v_new k_pages v_pages k_scale v_scale o lse
+        c_void_p, c_void_p, c_void_p, c_int64,                  # cu_seqlens_q cache_seqlens block_table stride
+        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int,  # dtype total_q B maxq H Hkv D page pool causal
+        c_float, c_float, c_void_p, c_size_t, c_void_p]),
     "tb200_rope_neox_packed": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,      # x y cos sin cu_seqlens_q cache_seqlens
         c_int, c_int, c_int, c_int, c_int, c_int, c_int,              # dtype tokens B H D rotary_dim max_position

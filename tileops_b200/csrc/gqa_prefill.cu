@@ -31,6 +31,7 @@
 //
 // Every mbarrier wait is bounded; on a timeout the CTA records an error code, stops issuing work,
 // lets its copies drain, frees its TMEM and returns.
+#include <cuda_fp8.h>
 #include <type_traits>
 
 #include "gqa_prefill.cuh"
@@ -50,6 +51,13 @@ constexpr int kStages = 2;                   // K, V and S buffers
 constexpr int kQPanel = kBM * 128;           // 128 rows x 128 B (64 head dims)
 constexpr int kKvPanel = kBN * 128;          // 64 rows x 128 B
 constexpr int kThreads = 192;
+constexpr int kThreadsF8 = 384;              // + warps 6, 7 idle and four converter warps 8-11 (e4m3 pages expanded in shared memory)
+// Registers of the e4m3-page variant: 12 warps x 2 CTAs leave 80 per thread at launch; the softmax warpgroup
+// takes 128 (setmaxnreg.inc) from what the other two warpgroups give back (setmaxnreg.dec to 56).  inc BLOCKS
+// until the CTA's own pool - what it was launched with - holds that many, so the sums must fit the launch
+// allocation; the host refuses the variant when the compiled kernel was given fewer than kF8LaunchRegs.
+constexpr int kF8LaunchRegs = 80, kF8SoftmaxRegs = 128, kF8OtherRegs = 56;
+static_assert(4 * kF8SoftmaxRegs + 8 * kF8OtherRegs <= 12 * kF8LaunchRegs, "setmaxnreg.inc would block forever");
 // TMEM columns a CTA allocates: S0 | S1 | O = 64 + 64 + HD, rounded up to a power of two.  Head dims
 // up to 128 leave room for two CTAs per SM (2 x 256 of 512 columns); 256 takes the whole TMEM.
 __host__ __device__ constexpr uint32_t tmem_cols(int hd) { return hd <= 128 ? 256u : 512u; }
@@ -57,6 +65,9 @@ __host__ __device__ constexpr int ctas_per_sm(int hd) { return hd <= 128 ? 2 : 1
 constexpr uint32_t kColS = 0, kColO = 128;    // S buffer s at columns [64 s, 64 s + 64)
 #ifndef TB200_PF_F32X2
 #define TB200_PF_F32X2 1
+#endif
+#ifndef TB200_PF_F8_CVT_CHUNKS
+#define TB200_PF_F8_CVT_CHUNKS 4   // of a converter thread's four chunks, how many go through the XU pipe (4 measured fastest)
 #endif
 
 // Shared-memory plan for head dim HD (64 or 128): HD / 64 panels per operand tile.
@@ -73,7 +84,7 @@ struct SmemLayoutT {
   static constexpr int total = bars + 256;
 };
 // barrier indices
-enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PREADY = 11, B_ODONE = 13, B_OFINAL = 14, B_COUNT = 15 };
+enum { B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 3, B_VFULL = 5, B_VEMPTY = 7, B_SFULL = 9, B_PREADY = 11, B_ODONE = 13, B_OFINAL = 14, B_KRAW = 15, B_VRAW = 17, B_COUNT = 19 };
 
 // Optional timeline for tuning (-DTB200_TRACE): CTA kTraceCta stamps %globaltimer-free clock64()
 // values of its MMA lane (slots 0-3) and of softmax thread 0 (slots 4-8) for the first
@@ -106,11 +117,21 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) { return pack2
 // visible to every query row) and then the request's own new tokens (read from k_new / v_new with
 // map_k / map_v, causal inside the chunk).  CTAs of the first q head of a KV group also copy their
 // 128 new K/V rows into the pages; attention never reads those copies, so no CTA waits for another.
-template <typename T, bool kSoftcap, int HD, bool kPaged>
-__global__ void __launch_bounds__(kThreads, ctas_per_sm(HD))
+//
+// kF8 (with kPaged, head dim 128): the pages hold e4m3 with one fp32 scale per tensor.  A cached tile arrives as
+// 64 rows of 128 bytes in the SECOND panel's place of its 16 KB buffer; two converter warps (warps 6, 7; thread =
+// row) expand it in place to the 16-bit, 128B-swizzled two-panel tile the MMA descriptors expect (x = float(x8) *
+// scale rounded to T, the reference's dequantisation): a thread reads its whole source row into registers first,
+// then writes panel 0 (nobody's source) and panel 1 (its own source row), so no thread overwrites what another
+// still has to read.  K/V "full" barriers then take two arrivals: the converter warps' for a cached tile, the
+// producer's arrive + arrive.expect_tx for a 16-bit tile of the chunk.  The appended rows are quantised
+// (e4m3(x / scale), saturating) by the appending CTAs.
+template <typename T, bool kSoftcap, int HD, bool kPaged, bool kF8 = false>
+__global__ void __launch_bounds__(kF8 ? kThreadsF8 : kThreads, ctas_per_sm(HD))
 gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_kp,
                    const __grid_constant__ CUtensorMap map_vp, PrefillParams p) {
+  static_assert(!kF8 || (kPaged && HD == 128), "the e4m3-page variant serves the paged kernel at head dim 128");
   using SmemLayout = SmemLayoutT<HD>;
   constexpr int kHD = HD;
   constexpr int kQBytes = SmemLayout::kQBytes, kKvBytes = SmemLayout::kKvBytes;
@@ -172,10 +193,12 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (tid == 0) {
     mbar_init(bar(B_QFULL), 1);
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar(B_KFULL + s), 1);
+      mbar_init(bar(B_KFULL + s), kF8 ? 4 : 1);
       mbar_init(bar(B_KEMPTY + s), 1);
-      mbar_init(bar(B_VFULL + s), 1);
+      mbar_init(bar(B_VFULL + s), kF8 ? 4 : 1);
       mbar_init(bar(B_VEMPTY + s), 1);
+      mbar_init(bar(B_KRAW + s), 1);
+      mbar_init(bar(B_VRAW + s), 1);
       mbar_init(bar(B_SFULL + s), 1);
       mbar_init(bar(B_PREADY + s), 128);
     }
@@ -198,6 +221,10 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   constexpr uint32_t idesc_pv = make_idesc(fmt, 1, kHD);
 
   if (n_kv > 0) {
+   if (warp >= 4) {
+    // (kF8) the warpgroups of the single-lane roles and of the converters give registers back; the role code is
+    // nested under the instruction so that the compiler allocates each side for what it was given
+    if constexpr (kF8) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kF8OtherRegs));
     if (warp == 4) {
       // ================= TMA producer =================
       if (lane == 0) {
@@ -239,9 +266,14 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             for (int x = 0; x < kMaxBoxes; ++x) {
               const int r = x * p.page_box;
               if (r < kBN) {
+                if constexpr (kF8) {
+                  // e4m3 rows (128 bytes each) into the second panel's place; the converter warps expand them
+                  tma_load_4d(dst + kKvPanel + r * 128, pool_map, full_bar, 0, hk, rows[x], 0);
+                } else {
 #pragma unroll
-                for (int pn = 0; pn < kHD / 64; ++pn)
-                  tma_load_4d(dst + pn * kKvPanel + r * 128, pool_map, full_bar, pn * 64, hk, rows[x], 0);
+                  for (int pn = 0; pn < kHD / 64; ++pn)
+                    tma_load_4d(dst + pn * kKvPanel + r * 128, pool_map, full_bar, pn * 64, hk, rows[x], 0);
+                }
               }
             }
           } else {
@@ -256,12 +288,17 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           const int s = i & 1;
           const uint32_t par = (i >> 1) & 1;
           if (i + 1 < n_kv) lookup(i + 1, rows_next);         // in flight during the waits below
+          const bool raw = kF8 && i < n_old;                  // an e4m3 tile: half the bytes, handed to the converter warps
+          const uint32_t k_bar = raw ? bar(B_KRAW + s) : bar(B_KFULL + s);
+          const uint32_t v_bar = raw ? bar(B_VRAW + s) : bar(B_VFULL + s);
           if (!mbar_wait(bar(B_KEMPTY + s), par ^ 1, s_abort, p.status, 101)) break;
-          mbar_expect_tx(bar(B_KFULL + s), kKvBytes);
-          load_tile(sbase + SmemLayout::k + s * kKvBytes, bar(B_KFULL + s), &map_k, &map_kp, i, rows_cur);
+          if (kF8 && !raw) { mbar_arrive(k_bar); mbar_arrive(k_bar); mbar_arrive(k_bar); }   // "full" takes four arrivals here
+          mbar_expect_tx(k_bar, raw ? kKvBytes / 2 : kKvBytes);
+          load_tile(sbase + SmemLayout::k + s * kKvBytes, k_bar, &map_k, &map_kp, i, rows_cur);
           if (!mbar_wait(bar(B_VEMPTY + s), par ^ 1, s_abort, p.status, 102)) break;
-          mbar_expect_tx(bar(B_VFULL + s), kKvBytes);
-          load_tile(sbase + SmemLayout::v + s * kKvBytes, bar(B_VFULL + s), &map_v, &map_vp, i, rows_cur);
+          if (kF8 && !raw) { mbar_arrive(v_bar); mbar_arrive(v_bar); mbar_arrive(v_bar); }
+          mbar_expect_tx(v_bar, raw ? kKvBytes / 2 : kKvBytes);
+          load_tile(sbase + SmemLayout::v + s * kKvBytes, v_bar, &map_v, &map_vp, i, rows_cur);
 #pragma unroll
           for (int x = 0; x < kMaxBoxes; ++x) rows_cur[x] = rows_next[x];
         }
@@ -319,7 +356,87 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           if (i + 2 < n_kv) ok = issue_qk(i + 2);
         }
       }
-    } else {
+    } else if (warp >= 6) {
+      // ================= converter warps 8-11 (kF8): expand e4m3 tiles in place; warps 6, 7 only fill their warpgroup =================
+      if constexpr (kF8) {
+       if (warp >= 8) {
+        const int r = (tid - 256) >> 1;                      // row of the tile, 0..63; two threads per row
+        const int c0 = ((tid - 256) & 1) * 4;                // this thread's four 16-byte source chunks
+        // Exact expansion e4m3 -> T (every e4m3 value is a T value); the tensors' scalar scales are applied by
+        // the softmax threads (K: in the score scale of cached tiles; V: in the exponent of P), which costs
+        // them nothing per element.  Two ways to expand a byte pair, both exact, on different pipes:
+        //   * cvt.rn.f16x2.e4m3x2 (XU pipe, which the exponentials of the softmax warps on the same scheduler
+        //     need; for bf16 followed by two f16 -> f32 conversions and a byte permute that takes the high halves);
+        //   * integer: the bytes go to the high byte of each half, the 7 magnitude bits move down to T's
+        //     exponent/mantissa boundary, which gives a T number whose exponent bias is off by 2^8 (f16) or
+        //     2^120 (bf16), subnormals included, and one exact multiply corrects it (5 instructions per pair).
+        // Measured on 8 x 512 new tokens over 8 x 4096 cached (fp16 / bf16; the same shape with a 16-bit cache
+        // takes 363 us, the three-launch path - gather, packed prefill, append - 430 us): two converter warps with
+        // cvt 496 us (their two schedulers XU bound), with the integer path 752 us (issue bound); four warps, one
+        // per scheduler: cvt 518 / 554 us, half and half 562 / 588 us, integer 613 / 616 us.  Every variant loses to
+        // the separate gather: each of the 16 CTAs that share a (request, KV head) converts the same tile again,
+        // on schedulers whose issue slots and XU pipe the softmax already fills, while the gather kernel converts
+        // every byte once at HBM speed.  The variant therefore stays opt-in; what it saves is memory (no packed
+        // 16-bit copy of the cache).
+        constexpr int kCvtChunks = TB200_PF_F8_CVT_CHUNKS;
+        auto expand = [&](unsigned char* tile) {
+          const int sw = r & 7;
+          uint4 raw[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) raw[c] = *reinterpret_cast<const uint4*>(tile + kKvPanel + r * 128 + (((c0 + c) ^ sw) << 4));
+          __syncwarp();      // the row's other thread (the neighbouring lane) has its source too: the row may be overwritten
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            const int c = c0 + cc;
+            const uint32_t w[4] = {raw[cc].x, raw[cc].y, raw[cc].z, raw[cc].w};
+            uint32_t o16[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (cc < kCvtChunks) {
+                uint32_t h;
+                asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h) : "h"(uint16_t(w[j >> 1] >> ((j & 1) * 16))));
+                if constexpr (std::is_same<T, __half>::value) {
+                  o16[j] = h;
+                } else {
+                  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+                  o16[j] = __byte_perm(__float_as_uint(f.x), __float_as_uint(f.y), 0x7632);
+                }
+              } else {
+                const uint32_t x = (j & 1) ? __byte_perm(w[j >> 1], 0u, 0x3424) : __byte_perm(w[j >> 1], 0u, 0x1404);
+                if constexpr (std::is_same<T, __half>::value) {
+                  const uint32_t t = (x & 0x80008000u) | ((x >> 1) & 0x3f803f80u);
+                  asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(o16[j]) : "r"(t), "r"(0x5c005c00u));        // x 2^8
+                } else {
+                  const uint32_t t = (x & 0x80008000u) | ((x >> 4) & 0x07f007f0u);
+                  asm("mul.rn.bf16x2 %0, %1, %2;\n" : "=r"(o16[j]) : "r"(t), "r"(0x7b807b80u));      // x 2^120
+                }
+              }
+            }
+            // 16 source elements = output chunks 2c and 2c + 1 of the 256-byte row: panel c / 4, chunks (2c) % 8, + 1
+            unsigned char* orow = tile + (c >> 2) * kKvPanel + r * 128;
+            *reinterpret_cast<uint4*>(orow + ((((2 * c) & 7) ^ sw) << 4)) = make_uint4(o16[0], o16[1], o16[2], o16[3]);
+            *reinterpret_cast<uint4*>(orow + ((((2 * c + 1) & 7) ^ sw) << 4)) = make_uint4(o16[4], o16[5], o16[6], o16[7]);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        };
+        for (int i = 0; i < n_old; ++i) {
+          const int s = i & 1;
+          const uint32_t par = (i >> 1) & 1;
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(B_KRAW + s), par, s_abort, p.status, 401))) break;
+          expand(smem + SmemLayout::k + s * kKvBytes);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(B_KFULL + s));
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(B_VRAW + s), par, s_abort, p.status, 402))) break;
+          expand(smem + SmemLayout::v + s * kKvBytes);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(B_VFULL + s));
+        }
+       }
+      }
+    }
+   } else {
+    {
+      if constexpr (kF8) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kF8SoftmaxRegs));
       // ================= softmax / correction / epilogue (thread = row) =================
       const int row = tid;                                  // 0..127 == TMEM lane
       const uint32_t lane_addr = uint32_t(warp * 32) << 16;
@@ -341,17 +458,45 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           const int r = idx / kChunks, ch = idx % kChunks;
           const int pos = old_len + m0 + r;
           const int page = p.bt[(long long)b * p.bt_stride + (pos >> p.page_shift)];
-          const size_t dst = (size_t(page) * p.page_size + (pos & (p.page_size - 1))) * row_bytes + size_t(hk) * kHD * 2 + ch * 16;
+          const size_t dst_row = size_t(page) * p.page_size + (pos & (p.page_size - 1));
           const size_t src = size_t(q_row0 + r) * row_bytes + size_t(hk) * kHD * 2 + ch * 16;
           const uint4 kk = *reinterpret_cast<const uint4*>(static_cast<const char*>(p.k_new) + src);
           const uint4 vv = *reinterpret_cast<const uint4*>(static_cast<const char*>(p.v_new) + src);
-          *reinterpret_cast<uint4*>(static_cast<char*>(p.k_pages) + dst) = kk;
-          *reinterpret_cast<uint4*>(static_cast<char*>(p.v_pages) + dst) = vv;
+          if constexpr (kF8) {
+            // 8 elements -> 8 bytes: e4m3(x / scale), round to nearest even, saturating
+            const size_t dst = (dst_row * p.heads_kv + hk) * kHD + ch * 8;
+            const float ks = *p.k_scale, vs = *p.v_scale;
+            auto quant = [](const uint4& x, float scale) {
+              const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+              uint32_t out[2] = {0u, 0u};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = unpack2<T>(w[j]);
+                const uint32_t b0 = __nv_cvt_float_to_fp8(__fdiv_rn(f.x, scale), __NV_SATFINITE, __NV_E4M3);
+                const uint32_t b1 = __nv_cvt_float_to_fp8(__fdiv_rn(f.y, scale), __NV_SATFINITE, __NV_E4M3);
+                out[j >> 1] |= (b0 | (b1 << 8)) << ((j & 1) * 16);
+              }
+              return make_uint2(out[0], out[1]);
+            };
+            *reinterpret_cast<uint2*>(static_cast<unsigned char*>(p.k_pages) + dst) = quant(kk, ks);
+            *reinterpret_cast<uint2*>(static_cast<unsigned char*>(p.v_pages) + dst) = quant(vv, vs);
+          } else {
+            const size_t dst = dst_row * row_bytes + size_t(hk) * kHD * 2 + ch * 16;
+            *reinterpret_cast<uint4*>(static_cast<char*>(p.k_pages) + dst) = kk;
+            *reinterpret_cast<uint4*>(static_cast<char*>(p.v_pages) + dst) = vv;
+          }
         }
       }
       const uint32_t s_addr0 = tmem + lane_addr + kColS;
       const uint32_t o_addr = tmem + lane_addr + kColO;
       float m_run = -INFINITY, l_run = 0.f;   // m_run: the maximum O and l are currently scaled to
+      // e4m3 pages (kF8): the cached tiles hold the bare e4m3 values.  K's scalar scale multiplies their raw scores
+      // (and their maximum, to keep one running maximum in the units of the chunk's own tiles); V's is added, as
+      // log2, to the exponent of their P, so that P V comes out scaled, and their row sums are kept apart
+      // (l_cached, in units of v_scale) and divided by v_scale at the end.
+      float l_cached = 0.f, pre_t = pre;
+      const float k_sc = kF8 ? *p.k_scale : 1.f, v_sc = kF8 ? *p.v_scale : 1.f;
+      const float log2_v_sc = kF8 ? log2f(v_sc) : 0.f;
       constexpr bool kBf16 = TB200_PF_TRUNC && std::is_same<T, __nv_bfloat16>::value;
       constexpr float kTruncFix = kBf16 ? 0.0028150156f : 0.f;   // log2(1 + 2^-9)
       bool ok = true;
@@ -360,7 +505,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       auto prepare = [&](uint32_t (&r)[32], int key0, bool need_mask) {
         if (kSoftcap) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(cap * fast_tanh(__uint_as_float(r[e]) * pre));
+          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(cap * fast_tanh(__uint_as_float(r[e]) * pre_t));
         }
         if (need_mask) {
 #pragma unroll
@@ -379,6 +524,8 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tc_fence_after();
         if (tid == 0) TB200_STAMP(4, j);
         int k0 = j * kBN;                                   // first key of the tile inside its segment
+        const bool scaled_tile = kF8 && j < n_old;          // a cached tile of bare e4m3 values
+        if (kF8 && kSoftcap) pre_t = scaled_tile ? pre * k_sc : pre;
         bool need_mask;
         if (kPaged && j < n_old) {
           key_limit = 0x7fffffff; seg_len = old_len;        // cached tokens: visible to every row
@@ -411,6 +558,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tc_wait_ld(r1);
         tc_ld32(s_addr, r0);          // first chunk of pass 2, in flight during the decision below
         mx = chunk_max(r1, 1, mx);
+        if (kF8 && !kSoftcap && scaled_tile) mx *= k_sc;    // raw maxima of cached tiles -> units of the chunk's tiles
 
         if (tid == 0) TB200_STAMP(5, j);
         // ---- decide whether the running maximum moves (and O has to be rescaled) ----
@@ -420,6 +568,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           // 1 for a row that still has seen no key (avoids inf - inf), 0 for a row seeing its first
           const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2((m_run - m_new) * c);
           l_run *= alpha;
+          l_cached *= alpha;
           if (j > 0) {
             // PV_{j-1} was issued after QK_j and may still be adding into O: wait for it.  (It
             // depends only on P_{j-1}, which these warps handed over a tile ago.)
@@ -438,13 +587,14 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           m_run = m_new;
         }
         if (tid == 0) TB200_STAMP(6, j);
-        const float neg_mc = ((m_run == -INFINITY) ? 0.f : -m_run * c) + kTruncFix;
+        const float neg_mc = ((m_run == -INFINITY) ? 0.f : -m_run * c) + kTruncFix + (scaled_tile ? log2_v_sc : 0.f);
+        const float ck = (kF8 && !kSoftcap && scaled_tile) ? c * k_sc : c;   // multiplier of this tile's raw scores
 
         // ---- pass 2: p = 2^(s*c - m*c), row sum, P (16-bit) over the first 64 columns of S ----
         float lsum0 = 0.f, lsum1 = 0.f;
 #if TB200_PF_F32X2
         uint64_t lsum_a = 0, lsum_b = 0;                    // two (even key, odd key) pairs of partial sums
-        const uint64_t c2 = f2_pack(c, c), neg_mc2 = f2_pack(neg_mc, neg_mc);
+        const uint64_t c2 = f2_pack(ck, ck), neg_mc2 = f2_pack(neg_mc, neg_mc);
 #endif
         // Two tuning switches, both off: they measured slower or neutral on B200 (this pass is
         // bound by instruction latency, not by the MUFU pipe).  TB200_PF_POLY evaluates every second
@@ -465,8 +615,8 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const float p1 = fast_exp2(x1);
             if (e & 1) lsum_b = f2_add(lsum_b, f2_pack(p0, p1)); else lsum_a = f2_add(lsum_a, f2_pack(p0, p1));
 #else
-            const float x0 = fmaf(__uint_as_float(r[2 * e]), c, neg_mc);
-            const float x1 = fmaf(__uint_as_float(r[2 * e + 1]), c, neg_mc);
+            const float x0 = fmaf(__uint_as_float(r[2 * e]), ck, neg_mc);
+            const float x1 = fmaf(__uint_as_float(r[2 * e + 1]), ck, neg_mc);
             const float p0 = fast_exp2(x0);
             const float p1 = (kMasked || !TB200_PF_POLY) ? fast_exp2(x1) : exp2_poly(x1);
             lsum0 += p0;
@@ -492,7 +642,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #if TB200_PF_F32X2
         f2_unpack(f2_add(lsum_a, lsum_b), lsum0, lsum1);
 #endif
-        l_run += lsum0 + lsum1;
+        if (scaled_tile) l_cached += lsum0 + lsum1; else l_run += lsum0 + lsum1;
         if (tid == 0) TB200_STAMP(7, j);
         if (kPaged && k0 + kBN > seg_len) {
           // Ragged last tile of a segment: the V rows behind it are another request's tokens or
@@ -519,6 +669,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       // ---- epilogue: O / l -> global, LSE ----
       if (ok) ok = mbar_wait(bar(B_OFINAL), 0, s_abort, p.status, 303);
       ok = __all_sync(0xffffffffu, ok);
+      if (kF8) l_run += l_cached / v_sc;
       if (ok) {
         tc_fence_after();
         const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -546,6 +697,7 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
               l_run > 0.f ? m_run * c + log2f(l_run) - kTruncFix : -INFINITY;
       }
     }
+   }
   } else if (warp < 4) {
     // the whole row tile is masked: zeros, LSE = -inf
     const int q_idx = m0 + tid;
@@ -575,10 +727,22 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 // ---- host side ------------------------------------------------------------------------------
 
-template <typename T, bool kSoftcap, int HD, bool kPaged>
+template <typename T, bool kSoftcap, int HD, bool kPaged, bool kF8 = false>
 int launch_prefill(const PrefillMaps& m, const PrefillParams& p, cudaStream_t stream) {
-  auto kern = gqa_prefill_kernel<T, kSoftcap, HD, kPaged>;
+  auto kern = gqa_prefill_kernel<T, kSoftcap, HD, kPaged, kF8>;
   const int smem = SmemLayoutT<HD>::total + 1024;
+  if constexpr (kF8) {
+    // the softmax warpgroup's setmaxnreg.inc can only be served from the registers the CTA was launched with
+    static thread_local int launch_regs = -1;
+    if (launch_regs < 0) {
+      cudaFuncAttributes attr;
+      TB200_CUDA_CHECK(cudaFuncGetAttributes(&attr, kern));
+      launch_regs = attr.numRegs;
+    }
+    if (launch_regs < kF8LaunchRegs)
+      TB200_FAIL(TB200_ERR_UNSUPPORTED, "the e4m3-page prefill kernel was compiled with %d registers per thread, %d needed",
+                 launch_regs, kF8LaunchRegs);
+  }
   static thread_local bool configured[64] = {false};       // per device, for this instantiation
   int dev = 0;
   TB200_CUDA_CHECK(cudaGetDevice(&dev));
@@ -589,7 +753,7 @@ int launch_prefill(const PrefillMaps& m, const PrefillParams& p, cudaStream_t st
   const int n_m = (p.seqlen_q + kBM - 1) / kBM;
   const long long grid = (long long)n_m * p.heads * p.batch;
   if (grid > 0x7fffffffLL) TB200_FAIL(TB200_ERR_UNSUPPORTED, "problem too large for one launch");
-  kern<<<unsigned(grid), kThreads, smem, stream>>>(m.q, m.k, m.v, m.kp, m.vp, p);
+  kern<<<unsigned(grid), kF8 ? kThreadsF8 : kThreads, smem, stream>>>(m.q, m.k, m.v, m.kp, m.vp, p);
   TB200_CUDA_CHECK(cudaGetLastError());
   return TB200_OK;
 }
@@ -601,6 +765,14 @@ int dispatch_prefill(int dtype, const PrefillMaps& m, const PrefillParams& p, cu
                                : launch_prefill<__half, true, HD, kPaged>(m, p, s);
   return dtype == TB200_BF16 ? launch_prefill<__nv_bfloat16, false, HD, kPaged>(m, p, s)
                              : launch_prefill<__half, false, HD, kPaged>(m, p, s);
+}
+
+int dispatch_prefill_e4m3_pages(int dtype, const PrefillMaps& m, const PrefillParams& p, cudaStream_t s) {
+  if (p.softcap > 0.f)
+    return dtype == TB200_BF16 ? launch_prefill<__nv_bfloat16, true, 128, true, true>(m, p, s)
+                               : launch_prefill<__half, true, 128, true, true>(m, p, s);
+  return dtype == TB200_BF16 ? launch_prefill<__nv_bfloat16, false, 128, true, true>(m, p, s)
+                             : launch_prefill<__half, false, 128, true, true>(m, p, s);
 }
 
 }  // namespace
@@ -658,7 +830,9 @@ extern "C" int tb200_gqa_prefill(const void* q, const void* k, const void* v, vo
   return dim == 128 ? dispatch_prefill<128, false>(dtype, m, p, s) : dispatch_prefill<64, false>(dtype, m, p, s);
 }
 
-extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const void* v_new, void* k_pages,
+namespace {
+// k_scale / v_scale non-null: the pages hold e4m3 (one fp32 scale per tensor, on the device)
+int prefill_paged_impl(const void* q, const void* k_new, const void* v_new, void* k_pages,
                                        void* v_pages, void* o, float* lse, const int32_t* cu_seqlens_q,
                                        const int32_t* cu_seqlens_kv, const int32_t* cache_seqlens,
                                        const int32_t* block_table, int64_t block_table_stride, int dtype,
@@ -666,7 +840,9 @@ extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const v
                                        int heads_kv, int dim, int page_size,
                                        int64_t pool_tokens, int is_causal, float sm_scale, float softcap,
                                        int window_left, int window_right, int flags, void* workspace,
-                                       size_t workspace_bytes, void* stream) {
+                                       size_t workspace_bytes, void* stream, const float* k_scale,
+                                       const float* v_scale) {
+  const bool e4m3_pages = k_scale != nullptr;
   if (flags < 0) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "flags must be a combination of TB200_PREFILL_* values");
   if (window_left < -1 || window_right < -1)
     TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "window sizes must be -1 (unlimited) or >= 0");
@@ -712,8 +888,13 @@ extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const v
   PrefillParams p{};
   if (has_cache) {
     p.page_box = page_size < kBN ? page_size : kBN;
-    if ((st = make_map(&m.kp, k_pages, dtype, 1, pool_tokens, heads_kv, dim, p.page_box)) != TB200_OK) return st;
-    if ((st = make_map(&m.vp, v_pages, dtype, 1, pool_tokens, heads_kv, dim, p.page_box)) != TB200_OK) return st;
+    if (e4m3_pages) {
+      if ((st = make_map_e4m3(&m.kp, k_pages, pool_tokens, heads_kv, dim, p.page_box)) != TB200_OK) return st;
+      if ((st = make_map_e4m3(&m.vp, v_pages, pool_tokens, heads_kv, dim, p.page_box)) != TB200_OK) return st;
+    } else {
+      if ((st = make_map(&m.kp, k_pages, dtype, 1, pool_tokens, heads_kv, dim, p.page_box)) != TB200_OK) return st;
+      if ((st = make_map(&m.vp, v_pages, dtype, 1, pool_tokens, heads_kv, dim, p.page_box)) != TB200_OK) return st;
+    }
     p.page_size = page_size;
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
@@ -724,7 +905,43 @@ extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const v
   p.win_left = window_left; p.win_right = window_right;
   p.cu_q = cu_seqlens_q; p.cu_kv = cu_seqlens_kv; p.cache_lens = cache_seqlens; p.bt = block_table; p.bt_stride = block_table_stride;
   p.k_new = k_new; p.v_new = v_new; p.k_pages = k_pages; p.v_pages = v_pages; p.total_q = total_q;
+  p.k_scale = k_scale; p.v_scale = v_scale;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (e4m3_pages) return dispatch_prefill_e4m3_pages(dtype, m, p, s);
   if (dim == 256) return dispatch_prefill<256, true>(dtype, m, p, s);
   return dim == 128 ? dispatch_prefill<128, true>(dtype, m, p, s) : dispatch_prefill<64, true>(dtype, m, p, s);
+}
+}  // namespace
+
+extern "C" int tb200_gqa_prefill_paged(const void* q, const void* k_new, const void* v_new, void* k_pages,
+                                       void* v_pages, void* o, float* lse, const int32_t* cu_seqlens_q,
+                                       const int32_t* cu_seqlens_kv, const int32_t* cache_seqlens,
+                                       const int32_t* block_table, int64_t block_table_stride, int dtype,
+                                       int total_q, int total_kv, int batch, int max_seqlen_q, int heads,
+                                       int heads_kv, int dim, int page_size,
+                                       int64_t pool_tokens, int is_causal, float sm_scale, float softcap,
+                                       int window_left, int window_right, int flags, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+  return prefill_paged_impl(q, k_new, v_new, k_pages, v_pages, o, lse, cu_seqlens_q, cu_seqlens_kv, cache_seqlens,
+                            block_table, block_table_stride, dtype, total_q, total_kv, batch, max_seqlen_q, heads,
+                            heads_kv, dim, page_size, pool_tokens, is_causal, sm_scale, softcap, window_left,
+                            window_right, flags, workspace, workspace_bytes, stream, nullptr, nullptr);
+}
+
+extern "C" int tb200_gqa_prefill_paged_e4m3_cache(const void* q, const void* k_new, const void* v_new, void* k_pages,
+                                                  void* v_pages, const float* k_scale, const float* v_scale, void* o,
+                                                  float* lse, const int32_t* cu_seqlens_q,
+                                                  const int32_t* cache_seqlens, const int32_t* block_table,
+                                                  int64_t block_table_stride, int dtype, int total_q, int batch,
+                                                  int max_seqlen_q, int heads, int heads_kv, int dim, int page_size,
+                                                  int64_t pool_tokens, int is_causal, float sm_scale, float softcap,
+                                                  void* workspace, size_t workspace_bytes, void* stream) {
+  if (!k_scale || !v_scale) TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "k_scale and v_scale must be non-null (device pointers)");
+  if (!k_pages || !v_pages || !cache_seqlens || !block_table)
+    TB200_FAIL(TB200_ERR_BAD_ARGUMENT, "k_pages, v_pages, cache_seqlens and block_table must be non-null");
+  if (dim != 128) TB200_FAIL(TB200_ERR_UNSUPPORTED, "head dim %d (the fused e4m3-page prefill serves 128)", dim);
+  return prefill_paged_impl(q, k_new, v_new, k_pages, v_pages, o, lse, cu_seqlens_q, nullptr, cache_seqlens,
+                            block_table, block_table_stride, dtype, total_q, total_q, batch, max_seqlen_q, heads,
+                            heads_kv, dim, page_size, pool_tokens, is_causal, sm_scale, softcap, -1, -1, 0, workspace,
+                            workspace_bytes, stream, k_scale, v_scale);
 }

@@ -28,6 +28,8 @@ struct PrefillParams {
   const void* v_new;
   void* k_pages;               // [pool_tokens, heads_kv, HD]; null: nothing is appended
   void* v_pages;
+  const float* k_scale;        // e4m3 pages (fused variant): one fp32 scale per tensor, on the device
+  const float* v_scale;
   int page_size, page_shift, page_box;   // page_box = min(64, page_size): rows per TMA box of the pool maps
   int total_q;
 };
@@ -72,6 +74,22 @@ inline int make_map(CUtensorMap* map, const void* base, int dtype, long long bat
   if (st != TB200_OK) return st;
   cache[next] = Slot{key, *map, true};
   next = (next + 1) % kSlots;
+  return TB200_OK;
+}
+
+// e4m3 pool [tokens, heads, hd] (one byte per element) -> 4-D map (d, head, token, 1), box hd bytes x 1 x box_rows x 1
+// (hd = 128: one 128-byte swizzled row per token, the layout the converter warps of the fused kernel expand in place)
+inline int make_map_e4m3(CUtensorMap* map, const void* base, long long tokens, int heads, int hd, int box_rows) {
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (!enc) TB200_FAIL(TB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[4] = {cuuint64_t(hd), cuuint64_t(heads), cuuint64_t(tokens), 1};
+  cuuint64_t strides[3] = {cuuint64_t(hd), cuuint64_t(heads) * hd, cuuint64_t(tokens) * heads * hd};
+  cuuint32_t box[4] = {cuuint32_t(hd), 1, cuuint32_t(box_rows), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) TB200_FAIL(TB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
   return TB200_OK;
 }
 

@@ -134,6 +134,17 @@ __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
   __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// The two 16-bit values of a register as floats (inverse of pack2).
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t x);
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t x) {
+  return make_float2(__uint_as_float(x << 16), __uint_as_float(x & 0xffff0000u));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t x) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&x));
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
