@@ -169,6 +169,21 @@ def test_fixed_run_lengths_give_the_result_of_the_cost_model(tma):
         assert torch.equal(o, again)          # same split: bit-identical, whoever ran which run
 
 
+def test_many_short_segments_per_cta_are_bit_reproducible():
+    """Forced run lengths of 2 and 3 tiles make every CTA of the TMA kernel walk a dozen short segments, most of
+    them partial: 150 launches each must give the same bits (a race between the math warps at a segment
+    boundary showed up here as one lane off by up to 6e-3 in 1-2 % of the launches)."""
+    inp = W.make_paged_decode(72, 6, 32, 8, 128, 64, len_range=(2000, 9000), device="cuda")
+    want = decode(inp, out_dtype=torch.float32, config={"tma": True, "chunk_tiles": 4096})
+    for chunk in (2, 3):
+        cfg = {"tma": True, "chunk_tiles": chunk}
+        base = decode(inp, out_dtype=torch.float32, config=cfg).clone()
+        assert F.decode_last_kernel() == "tma"
+        torch.testing.assert_close(base, want, atol=2e-3, rtol=1e-2)
+        odd = sum(0 if torch.equal(decode(inp, out_dtype=torch.float32, config=cfg), base) else 1 for _ in range(150))
+        assert odd == 0, f"{odd} of 150 launches with runs of {chunk} tiles differ from the first"
+
+
 def test_contiguous_cache_through_the_tma_kernel():
     B, H, Hkv, S, D = 5, 32, 8, 3000, 128
     q, k, v = W.make_contiguous_decode(73, B, H, Hkv, S, D, torch.bfloat16, "cuda")

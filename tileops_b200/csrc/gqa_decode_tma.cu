@@ -530,6 +530,13 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_item_empty(slot));   // id and q rows are in registers
+      // The four math warps meet here once per item.  Without this barrier, launches whose CTAs walk many short
+      // segments (forced run lengths of 2-7 tiles) gave one (sequence, KV head) a result off by up to 6e-3 in 1-2 %
+      // of the launches (bit-identical otherwise; never seen in 1200 launches of the default partition, and gone
+      // with a two-stage ring as well); with it, 800 such launches were bit-identical.  Which access of two warps
+      // an item apart collides has not been identified: every shared buffer they touch is handed over through a
+      // barrier on paper.  The barrier costs nothing measurable (one mbarrier round per segment).
+      if (!math_sync()) break;
       resolve_pending();   // ticket / merge of the previous item, while the producer streams this one
       if (!alive) break;
 
