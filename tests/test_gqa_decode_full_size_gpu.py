@@ -171,11 +171,14 @@ def test_fixed_run_lengths_give_the_result_of_the_cost_model(tma):
 
 def test_many_short_segments_per_cta_are_bit_reproducible():
     """Forced run lengths of 2 and 3 tiles make every CTA of the TMA kernel walk a dozen short segments, most of
-    them partial: 150 launches each must give the same bits (a race between the math warps at a segment
-    boundary showed up here as one lane off by up to 6e-3 in 1-2 % of the launches)."""
-    inp = W.make_paged_decode(72, 6, 32, 8, 128, 64, len_range=(2000, 9000), device="cuda")
+    them partial: 150 launches each must give the same bits (a barrier of the math warps at which only one
+    lane per warp arrived let the last stores of the other lanes be read too early: one lane's last 16 head dims
+    came out as the previous segment's in 1-10 % of such launches).  Lengths one past a tile boundary make the
+    segments shortest."""
+    lens = [n // 64 * 64 + 1 for n in W.draw_lengths(72, 6, (2000, 9000))]
+    inp = W.make_paged_decode(72, 6, 32, 8, 128, 64, lens=lens, device="cuda")
     want = decode(inp, out_dtype=torch.float32, config={"tma": True, "chunk_tiles": 4096})
-    for chunk in (2, 3):
+    for chunk in (3, 7):
         cfg = {"tma": True, "chunk_tiles": chunk}
         base = decode(inp, out_dtype=torch.float32, config=cfg).clone()
         assert F.decode_last_kernel() == "tma"

@@ -225,9 +225,9 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     }
     for (int s = 0; s < kItemSlots; ++s) {
       mbar_init(bar_item_full(s), 1);
-      mbar_init(bar_item_empty(s), kWarps);
+      mbar_init(bar_item_empty(s), kThreads);   // every math thread arrives: an arrival orders only its own reads
     }
-    mbar_init(bar_math, kWarps);
+    mbar_init(bar_math, kThreads);   // every math thread arrives (see math_sync)
     s_misc[0] = 0;
     mbar_fence_init();
   }
@@ -407,14 +407,17 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       }
     }
 
-    // Barrier of the four math warps with a bounded wait (an mbarrier, one arrival per warp): a warp
-    // that has given up simply never arrives, and the others give up too instead of waiting forever
-    // at a hardware barrier.
+    // Barrier of the four math warps with a bounded wait (an mbarrier): a warp that has given up simply
+    // never arrives, and the others give up too instead of waiting forever at a hardware barrier.
+    // EVERY thread arrives: an arrival releases the arriving thread's own earlier stores, nobody else's.
+    // With one arrival per warp (lane 0 behind a __syncwarp) the other lanes' last shared-memory stores
+    // before the barrier could still be on their way when another warp, released by the barrier, read them:
+    // the 16 head dims a warp writes last into the merge area came out stale (another segment's values) for
+    // one (sequence, KV head) in 1-10 % of launches whose CTAs walk many short segments.
     uint32_t math_par = 0;
     bool alive = true;
     auto math_sync = [&]() -> bool {
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_math);
+      mbar_arrive(bar_math);
       const bool ok = mbar_wait_bounded(bar_math, math_par, s_abort, status, 603, limit);
       math_par ^= 1;
       if (!ok) alive = false;
@@ -528,15 +531,7 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
           }
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_item_empty(slot));   // id and q rows are in registers
-      // The four math warps meet here once per item.  Without this barrier, launches whose CTAs walk many short
-      // segments (forced run lengths of 2-7 tiles) gave one (sequence, KV head) a result off by up to 6e-3 in 1-2 %
-      // of the launches (bit-identical otherwise; never seen in 1200 launches of the default partition, and gone
-      // with a two-stage ring as well); with it, 800 such launches were bit-identical.  Which access of two warps
-      // an item apart collides has not been identified: every shared buffer they touch is handed over through a
-      // barrier on paper.  The barrier costs nothing measurable (one mbarrier round per segment).
-      if (!math_sync()) break;
+      mbar_arrive(bar_item_empty(slot));   // id and q rows are in registers (every thread: its own reads)
       resolve_pending();   // ticket / merge of the previous item, while the producer streams this one
       if (!alive) break;
 

@@ -417,6 +417,8 @@ gqa_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             *reinterpret_cast<uint4*>(orow + ((((2 * c) & 7) ^ sw) << 4)) = make_uint4(o16[0], o16[1], o16[2], o16[3]);
             *reinterpret_cast<uint4*>(orow + ((((2 * c + 1) & 7) ^ sw) << 4)) = make_uint4(o16[4], o16[5], o16[6], o16[7]);
           }
+          // every lane makes its own stores visible (CTA scope, then to the async proxy) before lane 0 arrives for the warp
+          __threadfence_block();
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         };
         for (int i = 0; i < n_old; ++i) {
