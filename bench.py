@@ -134,6 +134,9 @@ def time_steps(fn, steps: int, warmup: int, world: int, sampler=None, soak_s: fl
     if soak_s > 0:
         # the same number of soak steps on every rank (a step may hold an exchange that all ranks must run in
         # lockstep): the slowest rank's time for 10 steps sizes the soak
+        for _ in range(5):                   # first calls pay one-time costs (maps, attributes, workspaces)
+            fn()
+        torch.cuda.synchronize()
         t0 = time.perf_counter()
         for _ in range(10):
             fn()
