@@ -16,9 +16,10 @@
 //     entries (32 tiles per global read, one lane each);
 //   * warps 0-3 are the math warps of gqa_decode.cu (tokens on the MMA M dimension, q heads on N = 8,
 //     mma.sync.m16n8k16, movmatrix for P^T, FP8 expanded with cvt.rn.f16x2.e4m3x2), without a single
-//     load instruction or address computation for K/V; stages are handed over with mbarriers, one
-//     arrival per warp; the four warps meet once per item in an 8.7 KB area of its own, half of the
-//     head dims at a time.
+//     load instruction or address computation for K/V; stages go back to the producer through mbarriers
+//     (one arrival per warp, after the MMAs that consumed the stage); the four warps meet once per item in
+//     an 8.7 KB area of its own, half of the head dims at a time, at an mbarrier at which every thread
+//     arrives (an arrival releases only the arriving thread's stores).
 // Served layouts: 64-token tiles that are one copy (no block table, or page_size % 64 == 0) or two or four
 // copies of one whole page each (page_size 32 or 16); token rows of 128 or 256 bytes, up to 8 q heads per
 // KV head.  Everything else goes to gqa_decode.cu.
