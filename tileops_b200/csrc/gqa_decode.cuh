@@ -88,6 +88,27 @@ __device__ __forceinline__ void emit_out(const DecodeParams& p, int parity, size
     store_out<TO>(reinterpret_cast<TO*>(p.o) + row * dim + d, val);
   }
 }
+// Four consecutive head dims (d a multiple of 4) of one row.  Sharded: ONE 16-byte store per peer instead of four
+// scalar ones - stores to a peer are posted through a short queue, and at 8 ranks the scalar form made the decode
+// launch 22 us longer than the local decode - when the slot layout keeps the row 16-byte aligned (it does when
+// batch * heads is a multiple of 4; else the scalar form).
+template <typename TO>
+__device__ __forceinline__ void emit_out4(const DecodeParams& p, int parity, size_t row, int d, int dim, float4 v) {
+  if (p.world > 1) {
+    const size_t off = (size_t(parity) * p.world + p.rank) * size_t(p.slot_floats) + row * dim + d;
+    if ((off & 3) == 0) {
+      for (int r = 0; r < p.world; ++r) *reinterpret_cast<float4*>(p.peer_o[r] + off) = v;
+    } else {
+      for (int r = 0; r < p.world; ++r) {
+        float* dst = p.peer_o[r] + off;
+        dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+      }
+    }
+  } else {
+    TO* dst = reinterpret_cast<TO*>(p.o) + row * dim + d;
+    store_out<TO>(dst, v.x); store_out<TO>(dst + 1, v.y); store_out<TO>(dst + 2, v.z); store_out<TO>(dst + 3, v.w);
+  }
+}
 __device__ __forceinline__ void emit_lse(const DecodeParams& p, int parity, size_t row, int dim, float val) {
   if (p.world > 1) {
     const size_t off = (size_t(parity) * p.world + p.rank) * size_t(p.slot_floats) +
