@@ -42,6 +42,20 @@ WORKER = textwrap.dedent("""
     assert peer.peer_status() == 0
     del g
     peer._peer = None
+    # a slot whose size is no multiple of 16 bytes (batch * heads * (D + 1) floats with batch * heads = 18): the
+    # decode kernel then stores its result to the peers in 4-byte pieces instead of 16-byte ones
+    B2, H2, Hkv2 = 3, 6, 2
+    p0, p1 = shard_page_range(4096 // page, rank, world)
+    inp2 = W.make_paged_decode(6, B2, H2, Hkv2, D, page, lens=[4096, 1000, 130], device=dev, page_begin=p0, page_end=p1)
+    nccl2 = KVSequenceShardedPagedDecode(B2, H2, Hkv2, D, page)
+    peer2 = KVSequenceShardedPagedDecode(B2, H2, Hkv2, D, page)
+    peer2.enable_peer_exchange(dev)
+    args2 = (inp2.q, inp2.k, inp2.v, inp2.real_seqlen_kv, inp2.block_table)
+    for step in range(3):
+        inp2.q.mul_(0.9).add_(0.01 * step)
+        assert torch.equal(nccl2(*args2), peer2(*args2)), f"odd slot size, step {step}: fused exchange differs"
+    assert peer2.peer_status() == 0
+    peer2._peer = None
     torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()
