@@ -435,7 +435,8 @@ def test_workload_generator_shards_reproduce_the_full_problem():
         assert torch.equal(torch.cat(parts), logical)
 
 
-REFERENCE_SRC = os.environ.get("TILEOPS_SOURCE_TREE", os.path.join(os.sep, "root", "reference", "src"))
+# a TileOPs source tree: named by TILEOPS_SOURCE_TREE, else a checkout called "reference" beside this repository
+REFERENCE_SRC = os.environ.get("TILEOPS_SOURCE_TREE", os.path.join(os.path.dirname(ROOT), "reference", "src"))
 
 
 @pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE_SRC, "tileops", "backend")),
