@@ -735,9 +735,11 @@ __global__ void __launch_bounds__(kThreads, min_blocks(FP8, NT, WIDE)) gqa_decod
       if (p.world > 1) {
         // all CTAs of this launch have reported: every rank's copy of this rank's result is complete
         *p.step_counter = step;
+        // ONE system-scope fence, then relaxed flag stores: a release store per peer would be a fence per peer
+        // (eight in a row at eight ranks, on the critical path of the step)
         __threadfence_system();
         for (int r = 0; r < p.world; ++r)
-          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer_flag[r]), "r"(step) : "memory");
+          asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p.peer_flag[r]), "r"(step) : "memory");
       }
     }
   }

@@ -766,9 +766,11 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         __threadfence();
         if (p.world > 1) {
           *p.step_counter = step;
+          // ONE system-scope fence, then relaxed flag stores: a release store per peer would be a fence per
+          // peer (eight in a row at eight ranks, on the critical path of the step)
           __threadfence_system();
           for (int r = 0; r < p.world; ++r)
-            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer_flag[r]), "r"(step) : "memory");
+            asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p.peer_flag[r]), "r"(step) : "memory");
         }
       }
     }
