@@ -73,6 +73,31 @@ def test_reference_cases_dim64(q_lens, old_lens, heads, heads_kv, is_causal, dty
     _check(q_lens, old_lens, heads, heads_kv, 64, 64, dtype, is_causal=is_causal, pages_per_req=8)
 
 
+def _random_case(seed):
+    import random
+    rng = random.Random(4321 + seed)
+    dim = rng.choice([64, 128, 128, 256])
+    heads_kv = rng.choice([1, 2, 4])
+    heads = heads_kv * rng.choice([1, 2, 4, 8])
+    page = rng.choice([16, 32, 64, 128])
+    nb = rng.choice([1, 2, 3, 5])
+    q_lens = [rng.choice([1, 2, 63, 64, 65, 127, 128, 129, rng.randint(1, 300)]) for _ in range(nb)]
+    old_lens = [rng.choice([0, 1, 63, 64, 65, page, rng.randint(0, 700)]) for _ in range(nb)]
+    return dict(q_lens=q_lens, old_lens=old_lens, heads=heads, heads_kv=heads_kv, dim=dim, page=page,
+                dtype=rng.choice([torch.float16, torch.bfloat16]), is_causal=rng.random() < 0.75,
+                softcap=rng.choice([None, None, 20.0]), seed=seed)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_paged_prefill_matches_the_oracle(seed):
+    """Seeded random chunks over random caches (head dim 64 / 128 / 256, page 16 ... 128, ragged request and cache
+    lengths around the 64-key and 128-row tile edges, requests without a cache, NaN in every pool row that holds
+    no token): output against the oracle, appended rows bit for bit, nothing else in the pool touched."""
+    c = _random_case(seed)
+    _check(c["q_lens"], c["old_lens"], c["heads"], c["heads_kv"], c["dim"], c["page"], c["dtype"], is_causal=c["is_causal"],
+           softcap=c["softcap"], seed=c["seed"], pool_fill=float("nan"))
+
+
 @pytest.mark.parametrize("page", [16, 32, 64, 128, 256])
 def test_page_sizes(page):
     _check([32, 64], [48, 80], 8, 2, 64, page, torch.float16, pages_per_req=16)
