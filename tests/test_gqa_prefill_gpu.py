@@ -218,3 +218,43 @@ def test_a_timed_out_prefill_surfaces_at_the_next_call():
     torch.cuda.synchronize()
     assert F.prefill_status() == 0                            # cleared: the next call works again
     close(F.gqa_prefill(q, k, v), O.prefill_ref(q.cpu(), k.cpu(), v.cpu(), True))
+
+
+def _random_dense_case(seed):
+    import random
+    rng = random.Random(977 + seed)
+    dim = rng.choice([64, 128, 128, 256])
+    heads_kv = rng.choice([1, 2, 4])
+    heads = heads_kv * rng.choice([1, 2, 4, 8])
+    batch = rng.choice([1, 2, 3])
+    sq = rng.choice([1, 63, 64, 127, 128, 129, 200, rng.randint(1, 400)])
+    skv = sq + rng.choice([0, 0, 1, 64, rng.randint(0, 500)])       # bottom-right aligned when longer
+    mode = rng.choice(["causal", "causal", "full", "window"])
+    return dict(dim=dim, heads=heads, heads_kv=heads_kv, batch=batch, sq=sq, skv=skv, mode=mode,
+                wl=rng.choice([0, 7, 64, 200]), wr=rng.choice([-1, 0, 5]), softcap=rng.choice([None, None, 25.0]),
+                dtype=rng.choice([torch.float16, torch.bfloat16]))
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_dense_prefill_matches_the_oracle(seed):
+    """Seeded random dense problems: head dim 64 / 128 / 256, sequence lengths around the 128-row and 64-key tile
+    edges, K/V longer than Q (bottom-right aligned mask), causal / full / sliding window, softcap; output and
+    log2-domain LSE against the oracle."""
+    from tileops_b200 import functional as F
+    c = _random_dense_case(seed)
+    q, k, v = W.make_prefill(300 + seed, c["batch"], c["sq"], c["skv"], c["heads"], c["heads_kv"], c["dim"], c["dtype"], "cuda")
+    kw = dict(is_causal=c["mode"] == "causal", softcap=c["softcap"] or 0.0)
+    okw = dict(is_causal=c["mode"] == "causal", softcap=c["softcap"])
+    if c["mode"] == "window":
+        kw.update(window_size_left=c["wl"], window_size_right=c["wr"])
+        okw.update(window_left=c["wl"], window_right=c["wr"])
+    o, lse = F.gqa_prefill(q, k, v, return_lse=True, **kw)
+    want, want_lse = O.prefill_ref(q.cpu(), k.cpu(), v.cpu(), return_lse=True, **okw)
+    assert not torch.isnan(o).any(), c
+    tol = dict(atol=5e-3, rtol=1e-2) if c["dtype"] == torch.float16 else dict(atol=2e-2, rtol=1e-2)
+    finite = torch.isfinite(want_lse)                    # [B, H, Sq]; a row that sees no key: zeros, LSE -inf
+    rows = finite.transpose(1, 2)                        # [B, Sq, H]
+    torch.testing.assert_close(o.cpu().float()[rows], want.float()[rows], **tol)
+    assert torch.count_nonzero(o.cpu()[~rows]) == 0
+    torch.testing.assert_close(lse.cpu()[finite], want_lse[finite], atol=2e-3, rtol=1e-3)
+    assert torch.isinf(lse.cpu()[~finite]).all()
