@@ -568,7 +568,10 @@ gqa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
               *reinterpret_cast<uint4*>(smem + C::ring + stage * C::kStageBytes + C::kTensorBytes +
                                         (ch >> 3) * C::kPanelBytes + row * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
           }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // before the stage goes back to the TMA
+          // every lane completes its own stores (CTA scope, then towards the async proxy) before the warp goes on:
+          // lane 0 alone will hand the stage back to the TMA, and an arrival orders only the arriving thread's stores
+          __threadfence_block();
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
         }
 
