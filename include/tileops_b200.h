@@ -89,11 +89,11 @@ int tb200_version(void);
  * The kernel never blocks on another CTA: split-KV partials are merged by whichever CTA
  * finishes a (sequence, KV head) last.
  *
- * Two kernels serve this entry point.  Where every 64-token tile is contiguous in memory (no block
- * table, or page_size a multiple of 64), token rows are 128 or 256 bytes, q is 16-byte aligned and
- * a KV head has at most 8 q heads, a producer warp streams K/V tiles by TMA ahead of the math
- * warps, across work-item boundaries; every other layout is served by a kernel whose math warps
- * issue cp.async gathers themselves.  Waits inside the TMA kernel are bounded (about 0.5 s): if one
+ * Two kernels serve this entry point.  Where every 64-token tile is one contiguous piece or two / four
+ * whole pages (no block table, page_size a multiple of 64, or page_size 32 / 16), token rows are 128
+ * or 256 bytes, q is 16-byte aligned and a KV head has at most 8 q heads, a producer warp streams K/V
+ * tiles by TMA ahead of the math warps, across work-item boundaries; every other layout is served by a
+ * kernel whose math warps issue cp.async gathers themselves (tb200_gqa_decode_last_kernel tells which).  Waits inside the TMA kernel are bounded (about 0.5 s): if one
  * runs out the launch stops early and the int at byte offset 8 of the workspace is set to a
  * non-zero code (601 producer, 602 math warps); the outputs of that launch are then undefined and
  * the workspace must be zeroed again before its next use.
