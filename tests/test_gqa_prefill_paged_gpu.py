@@ -439,6 +439,13 @@ def test_fused_fp8_cache_prefill_at_head_dim_128(dtype, page, is_causal, softcap
         assert torch.equal(kpd.cpu().view(torch.uint8)[~live], kp.view(torch.uint8)[~live])      # nothing else moved
         outs[fused] = o
     torch.testing.assert_close(outs[True].float(), outs[False].float(), atol=4e-3, rtol=1e-2)
+    # the same choice through the kernel class's config= (the tuning surface of the operator layer)
+    from tileops_b200.kernels.gqa_prefill import GQAPrefillPagedFp8CacheSm100Kernel
+    kern = GQAPrefillPagedFp8CacheSm100Kernel(B, heads, heads_kv, W, page, dim, is_causal, dtype, softcap=softcap or 0.0,
+                                              config={"fused": True})
+    assert kern.config["fused"] is True
+    o2 = kern.forward(*dev, kp.cuda(), vp.cuda(), *meta, max(q_lens))
+    assert torch.equal(o2, outs[True])
 
 
 def test_fp8_cache_golden_vectors():
