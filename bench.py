@@ -346,7 +346,7 @@ def main():
     ap.add_argument("--nccl-exchange", action="store_true", help="long-context sharded step: NCCL all-gather instead of the fused exchange")
     ap.add_argument("--case", default=None,
                     choices=["decode_small", "decode_fp8_small", "prefill_small", "prefill_two_tile_small", "prefill_paged",
-                             "rope_small", "fp8_cache_small", "merge_small", "mma_issue"],
+                             "rope_small", "fp8_cache_small", "fp8_cache_fused", "merge_small", "mma_issue"],
                     help="run only a reduced case of one kernel (a few hundred MB on the device: the "
                          "size an ncu capture of all sections can handle) and print its timing")
     a = ap.parse_args()
@@ -488,6 +488,14 @@ def run_small_case(case: str, steps: int, warmup: int):
         args[3], args[4] = args[3].to(f8), args[4].to(f8)
         fn = lambda: F.gqa_prefill_paged_fp8_cache(*args[:10], args[10], page_size=page)  # noqa: E731
         work, unit = 2 * B * old * Hkv * D + 2 * B * n * Hkv * D * 3, "GB/s"
+    elif case == "fp8_cache_fused":
+        # the same workload through the one-launch variant (e4m3 pages expanded inside the prefill kernel)
+        B, H, Hkv, D, page, Wp, old, n = 8, 32, 8, 128, 64, 72, 4096, 512
+        args = list(W.make_paged_prefill(6, [n] * B, [old] * B, H, Hkv, D, page, Wp, torch.float16, device))
+        f8 = torch.float8_e4m3fn
+        args[3], args[4] = args[3].to(f8), args[4].to(f8)
+        fn = lambda: F.gqa_prefill_paged_fp8_cache(*args[:10], args[10], page_size=page, fused=True)  # noqa: E731
+        work, unit = 4 * B * H * D * (n * old + n * (n + 1) // 2), "TFLOP/s"
     elif case == "merge_small":
         # the cross-rank merge: 8 parts of 256 rows x 128 dims
         parts, rows, D = 8, 256, 128
