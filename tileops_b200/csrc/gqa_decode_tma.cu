@@ -80,11 +80,11 @@ struct TmaCfg {
   static constexpr int merge = qslots + kItemSlots * kQSlotBytes;
   static constexpr int ml = merge + kMergeBytes;
   static constexpr int scales = ml + kMlBytes;               // [kStages][4 copies][K, V] fp32 (FP8 only)
-  static constexpr int bars = scales + 128;                   // full[kStages], empty[kStages], item_full[2], item_empty[2], math
+  static constexpr int bars = scales + 256;                   // full[kStages], empty[kStages], item_full[2], item_empty[2], math
   static constexpr int misc = bars + 8 * (2 * kStages + 2 * kItemSlots + 1);  // 16 ints
   static constexpr int plan = misc + 64;                     // s_prefix [batch + 1], s_lens [batch]
   static_assert(kRowBytes == 128 || kRowBytes == 256, "token rows must be one or two 128-byte panels");
-  static_assert(kStages * 8 * 4 <= 128, "scale slots");
+  static_assert(kStages * 8 * 4 <= 256, "scale slots");
 };
 
 template <int D, bool FP8>
